@@ -1,0 +1,172 @@
+/*
+ * lux/gpu/qmatmul_ext.h -- weight-only group-quantized matmul, exported by
+ * libluxgpu_backend_cuda.so BESIDE the backend vtable.
+ *
+ * The luxcpp/gpu backend vtable has no quantized-matmul slot
+ * (luxcpp/webgpu src/webgpu_plugin.cpp:4022-4123), and the WebGPU plugin ships its
+ * kernel-level entry points as extra extern "C" symbols next to the vtable
+ * (src/webgpu_kernel_loader.cpp:205-291).  This header follows that convention:
+ * a host resolves these symbols with dlsym from the same handle it got
+ * lux_gpu_backend_init from.  Operands are LuxBackendBuffer handles created through
+ * the vtable; every function validates its arguments first and returns a
+ * LuxBackendError; nothing throws across the boundary
+ * (conventions of src/webgpu_plugin.cpp:1658-1660, 1721-1771).
+ *
+ * Arithmetic contract (what the kernels compute; the WGSL each rule replaces):
+ *   int4 element i of a little-endian u32 is (word >> 4i) & 0xF, i.e. byte j holds
+ *   element 2j in its LOW nibble ............. kernels/wgsl/gpu/quantized_nax.wgsl:125-132
+ *   int8 element i is byte i, sign-extended .. kernels/wgsl/gpu/quantized_nax.wgsl:143-151
+ *   dequantized weight = f32(q - zero_point) * scale, integer subtract first, one
+ *   multiply ................................. kernels/wgsl/gpu/quantized_nax.wgsl:312-330, 364-381
+ *   group index = (row*K + col) / group_size . kernels/wgsl/gpu/quantized_nax.wgsl:587-589
+ *   y = sum_k w*x accumulated in f32 ......... kernels/wgsl/gpu/quantized_nax.wgsl:577-621
+ *   SwiGLU = silu(gate) * up with `up` rows stored after the `gate` rows
+ *   .......................................... kernels/wgsl/steel/gemm/steel_gemm_fused.wgsl:91-94, 452-558
+ *
+ * Memory layout (row-major, K a multiple of group_size, G = K / group_size):
+ *   x       [M, K]            f32 | f16 | bf16
+ *   W int4  [N, K/2]  uint8   two values per byte, low nibble first
+ *   W int8  [N, K]    int8
+ *   scales  [N, G]            f32 | f16
+ *   zeros   [N, ceil(G/2)] uint8, 4-bit zero-points two per byte, low nibble first;
+ *           NULL means symmetric: zero-point 8 for int4 (quantized_nax.wgsl:105-112),
+ *           0 for int8
+ *   y       [M, N]            f32 | f16 | bf16     (y = x . dequant(W)^T)
+ */
+#ifndef LUX_GPU_QMATMUL_EXT_H
+#define LUX_GPU_QMATMUL_EXT_H
+
+#include "lux/gpu/backend_plugin.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum LuxQDType {
+    LUX_QDTYPE_F32  = 0,
+    LUX_QDTYPE_F16  = 1,
+    LUX_QDTYPE_BF16 = 2
+} LuxQDType;
+
+enum {
+    /* Enqueue on the context's stream and return without waiting.  The default is
+     * the vtable's behaviour: return after the GPU has finished
+     * (src/webgpu_plugin.cpp:1028-1050 blocks in dispatchCompute). */
+    LUX_QMATMUL_FLAG_NO_SYNC = 1u << 0,
+    /* W holds [gate ; up] stacked on the output axis (N = 2*I).  The kernel writes
+     * y[M, I] = silu(x.gate^T) * (x.up^T), both products kept in f32
+     * (steel_gemm_silu_mul, steel/gemm/steel_gemm_fused.wgsl:452-558). */
+    LUX_QMATMUL_FLAG_SWIGLU  = 1u << 1
+};
+
+typedef struct LuxQMatmulDesc {
+    uint32_t struct_size;   /* sizeof(LuxQMatmulDesc); lets the struct grow */
+    uint32_t M, N, K;       /* N counts weight rows (2*I with FLAG_SWIGLU) */
+    uint32_t bits;          /* 4 or 8 */
+    uint32_t group_size;    /* 128 for int4, 32 for int8 */
+    uint32_t x_dtype;       /* LuxQDType */
+    uint32_t scale_dtype;   /* LuxQDType */
+    uint32_t y_dtype;       /* LuxQDType */
+    uint32_t flags;
+} LuxQMatmulDesc;
+
+/* Which kernel a call was (or would be) routed to. */
+typedef enum LuxQMatmulRoute {
+    LUX_QROUTE_NONE        = 0,
+    LUX_QROUTE_GEMV_I8     = 1,   /* int8 g32, f32 in/out, streaming GEMV              */
+    LUX_QROUTE_SKINNY_I4   = 2,   /* int4 g128, M <= 32, streaming GEMV / skinny GEMM  */
+    LUX_QROUTE_GEMM_I4_TC  = 3    /* int4 g128, M >= 33, tcgen05 / TMEM GEMM           */
+} LuxQMatmulRoute;
+
+/* y = x . dequant(W)^T.  Replaces the role of matmul_nax_grouped
+ * (kernels/wgsl/gpu/quantized_nax.wgsl:550-626) dispatched the way op_matmul_f32 is
+ * (src/webgpu_plugin.cpp:1721-1771).  Supported combinations:
+ *   bits=8 group=32  x=f32        scales=f32 y=f32   zeros=NULL           any M (GEMV per row)
+ *   bits=4 group=128 x=f16|bf16   scales=f16 y=x     zeros NULL or given  any M
+ * Anything else returns LUX_BACKEND_ERROR_NOT_SUPPORTED (the reference's signal for
+ * "fall back", src/webgpu_plugin.cpp:2087-2092). */
+LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_qmatmul(
+    LuxBackendContext* ctx, const LuxQMatmulDesc* desc,
+    LuxBackendBuffer* x, LuxBackendBuffer* w, LuxBackendBuffer* scales,
+    LuxBackendBuffer* zeros, LuxBackendBuffer* y);
+
+/* Same computation with HOST activations, following the reference's host-pointer op
+ * convention (src/webgpu_plugin.cpp:1117-1198: caller owns host memory, the plugin
+ * owns the transient device memory): copies x_host in, runs, copies y back, waits.
+ * Weights, scales and zeros stay device buffers (they are model state). */
+LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_qmatmul_host(
+    LuxBackendContext* ctx, const LuxQMatmulDesc* desc,
+    const void* x_host, LuxBackendBuffer* w, LuxBackendBuffer* scales,
+    LuxBackendBuffer* zeros, void* y_host);
+
+/* Reports the route lux_cuda_qmatmul would take; never launches. */
+LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_qmatmul_route(
+    const LuxQMatmulDesc* desc, int has_zeros, int* route_out);
+
+/* out[N, K] = f32(q - zp) * scale, written as f32, or rounded once more to
+ * f16/bf16 (round-to-nearest-even) when desc->y_dtype says so; desc->M and x_dtype
+ * are ignored.  Replaces dequantize_nax_int4_asym / dequantize_nax_int8_group
+ * (kernels/wgsl/gpu/quantized_nax.wgsl:312-330, 364-386). */
+LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_qdequant(
+    LuxBackendContext* ctx, const LuxQMatmulDesc* desc,
+    LuxBackendBuffer* w, LuxBackendBuffer* scales, LuxBackendBuffer* zeros,
+    LuxBackendBuffer* out);
+
+/* out[n] = integer (q - zp) as int8, one per weight: the unpack step alone
+ * (unpack_nax_int4_asym_x8 / unpack_nax_int8_x4, quantized_nax.wgsl:125-151). */
+LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_qunpack(
+    LuxBackendContext* ctx, const LuxQMatmulDesc* desc,
+    LuxBackendBuffer* w, LuxBackendBuffer* zeros, LuxBackendBuffer* out_i8);
+
+/* Llama-style FFN on one GPU or one tensor-parallel shard:
+ *   h[M, I] = silu(x.gate^T) * (x.up^T)    W_gate_up [2*I, K]  (gate rows, then up rows)
+ *   y[M, H] = h . dequant(W_down)^T        W_down    [H, I]
+ * int4 g128, f16 or bf16 activations.  `h` is caller-provided scratch of M*I elements.
+ * On a shard, I is the local intermediate size and y is the PARTIAL sum the caller
+ * all-reduces. */
+typedef struct LuxQMlpDesc {
+    uint32_t struct_size;
+    uint32_t M, K, I, H;    /* K: model dim in, I: local intermediate, H: model dim out */
+    uint32_t group_size;    /* 128 */
+    uint32_t act_dtype;     /* LUX_QDTYPE_F16 | LUX_QDTYPE_BF16 */
+    uint32_t flags;         /* LUX_QMATMUL_FLAG_NO_SYNC */
+} LuxQMlpDesc;
+
+LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_qmlp(
+    LuxBackendContext* ctx, const LuxQMlpDesc* desc, LuxBackendBuffer* x,
+    LuxBackendBuffer* w_gate_up, LuxBackendBuffer* s_gate_up, LuxBackendBuffer* z_gate_up,
+    LuxBackendBuffer* w_down, LuxBackendBuffer* s_down, LuxBackendBuffer* z_down,
+    LuxBackendBuffer* h_scratch, LuxBackendBuffer* y);
+
+/* -- interop needed by a host that already owns CUDA state (one process per GPU) ---- */
+
+/* Run this context's work on an existing stream (a cudaStream_t passed as void*;
+ * NULL restores the context's own stream).  The reference has one implicit queue per
+ * context (src/webgpu_plugin.cpp:584-622); this is its CUDA counterpart. */
+LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_context_set_stream(LuxBackendContext* ctx, void* stream);
+LUX_GPU_PLUGIN_EXPORT void* lux_cuda_context_get_stream(LuxBackendContext* ctx);
+
+/* Wrap device memory the caller owns as a non-owning LuxBackendBuffer; buffer_free
+ * releases only the handle.  Same handle layout as buffer_alloc
+ * (WGPUBackendBuffer{buffer,size}, src/webgpu_plugin.cpp:516-519). */
+LUX_GPU_PLUGIN_EXPORT LuxBackendBuffer* lux_cuda_buffer_wrap(LuxBackendContext* ctx, void* device_ptr, size_t bytes);
+LUX_GPU_PLUGIN_EXPORT void*  lux_cuda_buffer_device_ptr(LuxBackendBuffer* buf);
+LUX_GPU_PLUGIN_EXPORT size_t lux_cuda_buffer_size(LuxBackendBuffer* buf);
+
+/* Number of kernel launches this library has issued since load (all contexts). */
+LUX_GPU_PLUGIN_EXPORT uint64_t lux_cuda_launch_count(void);
+
+/* Benchmark / tuning hook: overrides one launch heuristic (value 0 restores the
+ * default).  Keys: gemv_i4_warps, gemv_i4_row_tiles, gemv_i8_warps, gemm_tc_bn,
+ * gemm_tc_stages, gemm_tc_splitk.  Unknown keys return INVALID_ARGUMENT.  Process-wide;
+ * not part of the drop-in surface. */
+LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_tune_set(const char* key, int value);
+
+/* Status word of the last device-side bounded wait that gave up (0 = none). */
+LUX_GPU_PLUGIN_EXPORT uint32_t lux_cuda_last_device_status(LuxBackendContext* ctx);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* LUX_GPU_QMATMUL_EXT_H */

@@ -1,0 +1,242 @@
+"""ctypes front end of the CPU oracle (oracle/qmatmul_oracle.c).
+
+TEST INFRASTRUCTURE ONLY: imported by tests/, by ``__graft_entry__.smoke`` and by the
+CPU-baseline legs of ``bench.py``; the shipped library never touches it.
+
+PARITY UNPINNED: luxcpp/webgpu has no golden vectors for its quantized kernels, so the
+oracle is pinned only by known-answer cases derived by hand from the WGSL text
+(tests/golden/).
+
+Arrays are numpy; f16 tensors are ``np.float16``; bf16 tensors are ``np.uint16`` bit
+patterns (numpy has no bf16 type).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+F32, F16, BF16 = 0, 1, 2
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "libqmatmul_oracle.so")
+_lib = None
+
+
+def build(force: bool = False) -> str:
+    """Compile the oracle with oracle/Makefile if the shared object is missing."""
+    if force or not os.path.exists(_LIB_PATH):
+        subprocess.check_call(["make", "-C", _HERE, "-s"] + (["-B"] if force else []))
+    return _LIB_PATH
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        build()
+        L = C.CDLL(_LIB_PATH)
+        u32, i32, vp, f32 = C.c_uint32, C.c_int32, C.c_void_p, C.c_float
+        L.orc_unpack_int4_asym_x8.argtypes = [u32, i32, C.POINTER(i32)]
+        L.orc_unpack_int4_sym_x8.argtypes = [u32, C.POINTER(i32)]
+        L.orc_unpack_int8_x4.argtypes = [u32, C.POINTER(i32)]
+        L.orc_pack_int4_asym_x8.argtypes = [C.POINTER(i32), i32]
+        L.orc_pack_int4_asym_x8.restype = u32
+        L.orc_f16_bits_to_f32.argtypes = [u32]
+        L.orc_f16_bits_to_f32.restype = f32
+        L.orc_f32_to_f16_bits_wgsl.argtypes = [f32]
+        L.orc_f32_to_f16_bits_wgsl.restype = u32
+        L.orc_f32_to_f16_rne.argtypes = [f32]
+        L.orc_f32_to_f16_rne.restype = u32
+        L.orc_f32_to_bf16_rne.argtypes = [f32]
+        L.orc_f32_to_bf16_rne.restype = u32
+        L.orc_bf16_bits_to_f32.argtypes = [u32]
+        L.orc_bf16_bits_to_f32.restype = f32
+        L.orc_silu.argtypes = [f32]
+        L.orc_silu.restype = f32
+        L.orc_qunpack.argtypes = [i32, i32, i32, i32, vp, vp, vp]
+        L.orc_qdequant.argtypes = [i32, i32, i32, i32, vp, vp, i32, vp, vp, i32]
+        L.orc_qmatmul.argtypes = [i32, i32, i32, i32, i32, vp, i32, vp, vp, i32, vp, vp, i32, i32, i32, i32]
+        L.orc_swiglu.argtypes = [i32, i32, vp, i32, vp, i32]
+        L.orc_num_procs.restype = i32
+        _lib = L
+    return _lib
+
+
+# -- scalar helpers -------------------------------------------------------------------
+
+def unpack_int4_asym_x8(word: int, zero_point: int) -> list[int]:
+    out = (C.c_int32 * 8)()
+    lib().orc_unpack_int4_asym_x8(word & 0xFFFFFFFF, zero_point, out)
+    return list(out)
+
+
+def unpack_int4_sym_x8(word: int) -> list[int]:
+    out = (C.c_int32 * 8)()
+    lib().orc_unpack_int4_sym_x8(word & 0xFFFFFFFF, out)
+    return list(out)
+
+
+def unpack_int8_x4(word: int) -> list[int]:
+    out = (C.c_int32 * 4)()
+    lib().orc_unpack_int8_x4(word & 0xFFFFFFFF, out)
+    return list(out)
+
+
+def pack_int4_asym_x8(vals, zero_point: int) -> int:
+    arr = (C.c_int32 * 8)(*[int(v) for v in vals])
+    return int(lib().orc_pack_int4_asym_x8(arr, zero_point))
+
+
+def f16_bits_to_f32(bits: int) -> float:
+    return float(lib().orc_f16_bits_to_f32(bits))
+
+
+def f32_to_f16_bits_wgsl(v: float) -> int:
+    return int(lib().orc_f32_to_f16_bits_wgsl(v))
+
+
+def f32_to_f16_rne(v: float) -> int:
+    return int(lib().orc_f32_to_f16_rne(v))
+
+
+def f32_to_bf16_rne(v: float) -> int:
+    return int(lib().orc_f32_to_bf16_rne(v))
+
+
+def silu(v: float) -> float:
+    return float(lib().orc_silu(v))
+
+
+# -- array helpers --------------------------------------------------------------------
+
+def dtype_code(a: np.ndarray, bf16: bool = False) -> int:
+    if a.dtype == np.float32:
+        return F32
+    if a.dtype == np.float16:
+        return F16
+    if a.dtype == np.uint16:
+        return BF16
+    raise TypeError(f"unsupported dtype {a.dtype}")
+
+
+def _np_out(shape, code):
+    return np.empty(shape, {F32: np.float32, F16: np.float16, BF16: np.uint16}[code])
+
+
+def _ptr(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def bf16_to_f32(a: np.ndarray) -> np.ndarray:
+    return (a.astype(np.uint32) << 16).view(np.float32)
+
+
+def f32_to_bf16(a: np.ndarray) -> np.ndarray:
+    """Round-to-nearest-even f32 -> bf16 bit patterns (finite inputs)."""
+    u = np.ascontiguousarray(a, np.float32).view(np.uint32)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def to_f32(a: np.ndarray) -> np.ndarray:
+    return bf16_to_f32(a) if a.dtype == np.uint16 else a.astype(np.float32)
+
+
+def qunpack(w: np.ndarray, zeros, bits: int, group: int) -> np.ndarray:
+    N = w.shape[0]
+    K = w.shape[1] * (2 if bits == 4 else 1)
+    w = np.ascontiguousarray(w).view(np.uint8)
+    out = np.empty((N, K), np.int8)
+    rc = lib().orc_qunpack(N, K, bits, group, _ptr(w), _ptr(zeros), _ptr(out))
+    assert rc == 0, rc
+    return out
+
+
+def qdequant(w, scales, zeros, bits: int, group: int, out_code: int = F32) -> np.ndarray:
+    N = w.shape[0]
+    K = w.shape[1] * (2 if bits == 4 else 1)
+    w = np.ascontiguousarray(w).view(np.uint8)
+    scales = np.ascontiguousarray(scales)
+    out = _np_out((N, K), out_code)
+    rc = lib().orc_qdequant(N, K, bits, group, _ptr(w), _ptr(scales), dtype_code(scales),
+                            _ptr(zeros), _ptr(out), out_code)
+    assert rc == 0, rc
+    return out
+
+
+def qmatmul(x, w, scales, zeros, bits: int, group: int, y_code: int | None = None,
+            w_round: int = F32, acc_mode: int = 0, threads: int = 0) -> np.ndarray:
+    """y[M,N] = x[M,K] . dequant(W[N,K])^T; see orc_qmatmul for the modes."""
+    x = np.ascontiguousarray(x)
+    M, K = x.shape
+    N = w.shape[0]
+    assert w.shape[1] * (2 if bits == 4 else 1) == K
+    w = np.ascontiguousarray(w).view(np.uint8)
+    scales = np.ascontiguousarray(scales)
+    if zeros is not None:
+        zeros = np.ascontiguousarray(zeros, np.uint8)
+    xc = dtype_code(x)
+    if y_code is None:
+        y_code = xc
+    y = _np_out((M, N), y_code)
+    rc = lib().orc_qmatmul(M, N, K, bits, group, _ptr(x), xc, _ptr(w), _ptr(scales),
+                           dtype_code(scales), _ptr(zeros), _ptr(y), y_code, w_round,
+                           acc_mode, threads)
+    assert rc == 0, rc
+    return y
+
+
+def swiglu(gu: np.ndarray, h_code: int | None = None) -> np.ndarray:
+    gu = np.ascontiguousarray(gu)
+    M, two_i = gu.shape
+    code = dtype_code(gu)
+    if h_code is None:
+        h_code = code
+    h = _np_out((M, two_i // 2), h_code)
+    lib().orc_swiglu(M, two_i // 2, _ptr(gu), code, _ptr(h), h_code)
+    return h
+
+
+def mlp(x, gate_up, down, group: int = 128, fused: bool = False, w_round: int = F32,
+        acc_mode: int = 0, threads: int = 0) -> np.ndarray:
+    """Llama FFN: y = (silu(x.Wg^T) * (x.Wu^T)) . Wd^T on int4 weights.
+
+    gate_up / down are (w, scales, zeros) triples; gate_up stacks gate rows then up rows.
+    fused=False rounds gate_up's output to the activation dtype before SwiGLU (two
+    separate "f32 accumulate, 16-bit output" layers); fused=True keeps gate and up in
+    f32 until after SwiGLU (one rounding fewer), which is what a fused epilogue does.
+    """
+    code = dtype_code(x)
+    gu = qmatmul(x, *gate_up, bits=4, group=group, y_code=(F32 if fused else code),
+                 w_round=w_round, acc_mode=acc_mode, threads=threads)
+    h = swiglu(gu, h_code=code)
+    return qmatmul(h, *down, bits=4, group=group, y_code=code, w_round=w_round,
+                   acc_mode=acc_mode, threads=threads)
+
+
+def tp_mlp(x, shards, group: int = 128, fused: bool = True, w_round: int = F32) -> np.ndarray:
+    """Tensor-parallel FFN: each shard is (gate_up_triple, down_triple); partial outputs
+    are narrowed to the activation dtype per shard (what each GPU hands to the
+    all-reduce) and summed in f32 in rank order, then narrowed once."""
+    code = dtype_code(x)
+    total = None
+    for gate_up, down in shards:
+        part = to_f32(mlp(x, gate_up, down, group=group, fused=fused, w_round=w_round))
+        total = part if total is None else total + part
+    if code == F16:
+        return total.astype(np.float16)
+    if code == BF16:
+        return f32_to_bf16(total)
+    return total
+
+
+def rel_l2(a: np.ndarray, ref: np.ndarray) -> float:
+    a = to_f32(a).astype(np.float64)
+    ref = to_f32(ref).astype(np.float64)
+    den = np.linalg.norm(ref)
+    return float(np.linalg.norm(a - ref) / (den if den > 0 else 1.0))
+
+
+def num_procs() -> int:
+    return int(lib().orc_num_procs())

@@ -1,0 +1,105 @@
+// Shared declarations of libluxgpu_backend_cuda.so: the context and buffer structs
+// behind the opaque LuxBackend* handles, error mapping and launch bookkeeping.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+
+#include <atomic>
+#include <cstdint>
+#include <cstdio>
+#include <mutex>
+#include <string>
+
+#include "lux/gpu/backend_plugin.h"
+#include "lux/gpu/qmatmul_ext.h"
+
+namespace luxcuda {
+
+// Counterpart of WGPUBackendBuffer{buffer,size} (luxcpp/webgpu src/webgpu_plugin.cpp:516-519).
+struct Buffer {
+    void*  ptr;
+    size_t size;
+    int    device;
+    bool   owned;    // false for lux_cuda_buffer_wrap handles
+};
+
+// Counterpart of WGPUBackendContext (src/webgpu_plugin.cpp:584-622): one device, one
+// queue.  The reference keeps a 256-byte uniform buffer per context for kernel
+// parameters; CUDA passes parameters by value, so the per-context device state here is
+// the status word for bounded device-side waits and the staging used by host-pointer ops.
+struct Context {
+    int            device = 0;
+    cudaStream_t   own_stream = nullptr;
+    cudaStream_t   stream = nullptr;        // own_stream unless lux_cuda_context_set_stream
+    cudaDeviceProp prop{};
+    std::string    name;
+    uint32_t*      d_status = nullptr;      // device status word (0 = ok)
+    uint32_t*      h_status = nullptr;      // pinned mirror
+    void*          h_stage = nullptr;       // pinned staging for host-pointer ops
+    size_t         h_stage_bytes = 0;
+    void*          d_stage = nullptr;       // device staging for host-pointer ops
+    size_t         d_stage_bytes = 0;
+    uint32_t       last_status = 0;
+    std::mutex     mu;                      // guards the staging buffers
+    int            sm_count = 148;
+};
+
+inline Context* as_ctx(LuxBackendContext* c) { return reinterpret_cast<Context*>(c); }
+inline Buffer*  as_buf(LuxBackendBuffer* b) { return reinterpret_cast<Buffer*>(b); }
+
+extern std::atomic<uint64_t> g_launches;
+inline void count_launch(unsigned n = 1) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+// Maps a CUDA error to the plugin's error vocabulary, logging in the reference's
+// stderr style ("[lux-webgpu] ...", src/webgpu_plugin.cpp:695).
+inline LuxBackendError map_cuda(cudaError_t e, const char* what) {
+    if (e == cudaSuccess) return LUX_BACKEND_OK;
+    std::fprintf(stderr, "[lux-cuda] %s: %s\n", what, cudaGetErrorString(e));
+    if (e == cudaErrorMemoryAllocation) return LUX_BACKEND_ERROR_OUT_OF_MEMORY;
+    if (e == cudaErrorInvalidValue || e == cudaErrorInvalidDevice) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    return LUX_BACKEND_ERROR_INTERNAL;
+}
+
+#define LUX_CUDA_TRY(expr)                                                   \
+    do {                                                                     \
+        cudaError_t _e = (expr);                                             \
+        if (_e != cudaSuccess) return ::luxcuda::map_cuda(_e, #expr);        \
+    } while (0)
+
+// Checks the launch, and unless `no_sync` waits for the stream like the reference's
+// dispatchCompute does (src/webgpu_plugin.cpp:1028-1050).
+LuxBackendError finish_op(Context* ctx, bool no_sync, const char* what);
+
+// Tunables a benchmark may override (0 = use the built-in heuristic).
+struct Tunables {
+    int gemv_i4_warps = 0;       // warps per CTA of the int4 skinny kernel
+    int gemv_i4_row_tiles = 0;   // 16-row tiles per CTA
+    int gemv_i8_warps = 0;
+    int gemm_tc_bn = 0;          // N tile of the tcgen05 GEMM
+    int gemm_tc_stages = 0;
+    int gemm_tc_splitk = 0;
+};
+extern Tunables g_tune;
+
+// ---- kernel launchers (defined in the .cu file named after each kernel family) ------
+
+struct QArgs {
+    int M, N, K, G;              // G = K / group
+    const void* x;
+    const uint8_t* w;
+    const void* scales;
+    const uint8_t* zeros;        // may be null
+    void* y;
+    int x_dtype, scale_dtype, y_dtype;
+    bool swiglu;
+};
+
+LuxBackendError launch_qgemv_i8(Context* ctx, const QArgs& a);
+LuxBackendError launch_qskinny_i4(Context* ctx, const QArgs& a);
+LuxBackendError launch_qgemm_i4_tc(Context* ctx, const QArgs& a);
+LuxBackendError launch_qdequant(Context* ctx, const QArgs& a, int bits);
+LuxBackendError launch_qunpack(Context* ctx, const QArgs& a, int bits);
+
+}  // namespace luxcuda
