@@ -17,6 +17,32 @@ pytestmark = pytest.mark.gpu
 TOL_F32 = 1e-3
 TOL_16 = 5e-3
 
+# The int4 decode path has two kernels computing the same thing: 1 = register-staged
+# lux_qskinny_i4_g128 (any shape), 2 = bulk-copy ring lux_qgemv_i4_g128_stream (batch <= 16,
+# at least 8 groups per row).  0 lets the library choose.
+I4_KERNELS = [0, 1, 2]
+
+
+def _stream_supported(M, K, swiglu=False):
+    """Mirror of the ring kernel's shape rule: batch <= 16, >= 8 groups per row, and room in
+    227 KB of shared memory for the staged activations plus at least three minimal stages."""
+    if M > 16 or K // 128 < 8:
+        return False
+    mt, nacc = (1 if M <= 8 else 2), (2 if swiglu else 1)
+    fixed = M * (2 * K + 64) + 2 * 8 * nacc * mt * 32 * 16 + 2048
+    return fixed + 3 * (16 * (8 * 64 + 64) + 16) <= 227 * 1024
+
+
+class _kernel:
+    def __init__(self, backend, which):
+        self.backend, self.which = backend, which
+
+    def __enter__(self):
+        self.backend.tune("gemv_i4_kernel", self.which)
+
+    def __exit__(self, *exc):
+        self.backend.tune("gemv_i4_kernel", 0)
+
 
 def _run(ctx, x, layer, flags=0):
     L = ctx.upload_layer(layer)
@@ -81,9 +107,11 @@ def test_int8_gemv_shapes(ctx, N, K, M):
 
 # -- config 2: int4 g128 GEMV, f16 ---------------------------------------------------------
 
-def test_config2_int4_gemv(ctx):
+@pytest.mark.parametrize("kernel", I4_KERNELS)
+def test_config2_int4_gemv(ctx, backend, kernel):
     x, layer = synth.config2()
-    y = _run(ctx, x, layer)
+    with _kernel(backend, kernel):
+        y = _run(ctx, x, layer)
     ref = orc.qmatmul(x, *layer.triple, bits=4, group=128)
     err = orc.rel_l2(y, ref)
     assert err < TOL_16, err
@@ -96,11 +124,36 @@ def test_config2_int4_gemv(ctx):
     (64, 4096, 8, False), (48, 2048, 9, False), (80, 1024, 16, False), (32, 512, 17, True),
     (64, 8192, 32, False), (40, 14336, 16, False), (16, 28672, 1, False),
 ])
-def test_int4_skinny_shapes(ctx, N, K, M, symmetric):
+@pytest.mark.parametrize("kernel", I4_KERNELS)
+def test_int4_skinny_shapes(ctx, backend, N, K, M, symmetric, kernel):
     x = synth.activations(M, K, "f16", 24, f"i4.{N}.{K}.{M}")
     layer = synth.int4_layer(N, K, 24, f"i4.{N}.{K}", symmetric=symmetric)
-    y = _run(ctx, x, layer)
+    with _kernel(backend, kernel):
+        if kernel == 2 and not _stream_supported(M, K):
+            with pytest.raises(B.BackendError) as e:
+                _run(ctx, x, layer)
+            assert e.value.code == B.NOT_SUPPORTED
+            return
+        y = _run(ctx, x, layer)
     ref = orc.qmatmul(x, *layer.triple, bits=4, group=128)
+    assert orc.rel_l2(y, ref) < TOL_16
+    assert ctx.last_device_status() == 0
+
+
+@pytest.mark.parametrize("cg,stages", [(1, 3), (2, 5), (4, 2), (4, 64)])
+def test_int4_stream_ring_shapes(ctx, backend, cg, stages):
+    """Every ring geometry (groups per stage, ring depth) gives the same answer."""
+    x = synth.activations(5, 2048, "f16", 28, "ring.x")
+    layer = synth.int4_layer(1000, 2048, 28, "ring")
+    ref = orc.qmatmul(x, *layer.triple, bits=4, group=128)
+    backend.tune("gemv_stream_cg", cg)
+    backend.tune("gemv_stream_stages", stages)
+    try:
+        with _kernel(backend, 2):
+            y = _run(ctx, x, layer)
+    finally:
+        backend.tune("gemv_stream_cg", 0)
+        backend.tune("gemv_stream_stages", 0)
     assert orc.rel_l2(y, ref) < TOL_16
 
 
@@ -113,7 +166,8 @@ def test_int4_skinny_launch_shapes(ctx, backend, wpc, rt):
     backend.tune("gemv_i4_warps", wpc)
     backend.tune("gemv_i4_row_tiles", rt)
     try:
-        y = _run(ctx, x, layer)
+        with _kernel(backend, 1):
+            y = _run(ctx, x, layer)
     finally:
         backend.tune("gemv_i4_warps", 0)
         backend.tune("gemv_i4_row_tiles", 0)
@@ -124,20 +178,28 @@ def test_int4_skinny_launch_shapes(ctx, backend, wpc, rt):
 
 @pytest.mark.parametrize("name", list(synth.SWEEP_LAYERS))
 @pytest.mark.parametrize("M", [1, 4, 16])
-def test_config4_sweep_streaming(ctx, name, M):
+@pytest.mark.parametrize("kernel", [1, 2])
+def test_config4_sweep_streaming(ctx, backend, name, M, kernel):
     x, layer = synth.config4(name, M)
-    y = _run(ctx, x, layer)
+    if kernel == 2 and not _stream_supported(M, layer.K):
+        pytest.skip("activations too large for the ring kernel's shared memory")
+    with _kernel(backend, kernel):
+        y = _run(ctx, x, layer)
     ref = orc.qmatmul(x, *layer.triple, bits=4, group=128)
     assert orc.rel_l2(y, ref) < TOL_16
 
 
 # -- SwiGLU epilogue and the FFN ------------------------------------------------------------
 
-@pytest.mark.parametrize("M", [1, 8, 20])
-def test_swiglu_epilogue_streaming(ctx, M):
-    gate_up, _ = synth.mlp_layers(512, 384, 128, 26, "sw")
-    x = synth.activations(M, 512, "f16", 26, "sw.x")
-    h = _run(ctx, x, gate_up, flags=B.FLAG_SWIGLU)
+@pytest.mark.parametrize("M", [1, 8, 12, 20])
+@pytest.mark.parametrize("kernel", [1, 2])
+def test_swiglu_epilogue_streaming(ctx, backend, M, kernel):
+    gate_up, _ = synth.mlp_layers(1024, 384, 128, 26, "sw")
+    x = synth.activations(M, 1024, "f16", 26, "sw.x")
+    if kernel == 2 and not _stream_supported(M, 1024, swiglu=True):
+        pytest.skip("ring kernel covers batch <= 16")
+    with _kernel(backend, kernel):
+        h = _run(ctx, x, gate_up, flags=B.FLAG_SWIGLU)
     gu = orc.qmatmul(x, *gate_up.triple, bits=4, group=128, y_code=orc.F32)
     ref = orc.swiglu(gu, h_code=orc.F16)
     assert orc.rel_l2(h, ref) < TOL_16

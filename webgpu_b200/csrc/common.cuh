@@ -77,6 +77,9 @@ struct Tunables {
     int gemv_i4_warps = 0;       // warps per CTA of the int4 skinny kernel
     int gemv_i4_row_tiles = 0;   // 16-row tiles per CTA
     int gemv_i8_warps = 0;
+    int gemv_i4_kernel = 0;      // 0 auto, 1 lux_qskinny_i4_g128, 2 lux_qgemv_i4_g128_stream
+    int gemv_stream_cg = 0;      // stream kernel: groups per stage / 8 (1, 2 or 4)
+    int gemv_stream_stages = 0;  // stream kernel: ring depth cap
     int gemm_tc_bn = 0;          // N tile of the tcgen05 GEMM
     int gemm_tc_stages = 0;
     int gemm_tc_splitk = 0;
@@ -98,6 +101,7 @@ struct QArgs {
 
 LuxBackendError launch_qgemv_i8(Context* ctx, const QArgs& a);
 LuxBackendError launch_qskinny_i4(Context* ctx, const QArgs& a);
+LuxBackendError launch_qgemv_i4_stream(Context* ctx, const QArgs& a);   // NOT_SUPPORTED if the shape does not fit
 LuxBackendError launch_qgemm_i4_tc(Context* ctx, const QArgs& a);
 LuxBackendError launch_qdequant(Context* ctx, const QArgs& a, int bits);
 LuxBackendError launch_qunpack(Context* ctx, const QArgs& a, int bits);

@@ -335,7 +335,7 @@ lux_qgemm_i4_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     }
                 }
             }
-            ok = mbar_wait(full_ld(s), ph, abort_flag);
+            ok = __all_sync(0xffffffffu, mbar_wait(full_ld(s), ph, abort_flag));   // warp-uniform outcome
             if (!ok) break;
             const unsigned char* qs = q_ring + (size_t)s * Q_BYTES;
             unsigned char* bs = b_ring + (size_t)s * B_BYTES;
@@ -362,7 +362,7 @@ lux_qgemm_i4_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         }
 
         // =============================== epilogue =======================================
-        if (ok) ok = mbar_wait(acc_full, 0u, abort_flag);
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(acc_full, 0u, abort_flag));
         if (ok) {
             tc_fence_after();
             const int quad = warp & 3;                          // TMEM lanes this warp may read

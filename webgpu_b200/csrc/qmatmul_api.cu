@@ -77,7 +77,15 @@ LuxBackendError bind_weights(Checked& c, Buffer* w, Buffer* scales, Buffer* zero
 LuxBackendError dispatch(Context* ctx, const Checked& c) {
     switch (c.route) {
         case LUX_QROUTE_GEMV_I8:    return launch_qgemv_i8(ctx, c.a);
-        case LUX_QROUTE_SKINNY_I4:  return launch_qskinny_i4(ctx, c.a);
+        case LUX_QROUTE_SKINNY_I4: {
+            // Both kernels compute the same thing; the bulk-copy ring kernel is the fast
+            // path for batch <= 16, the register-staged one covers every other shape.
+            if (g_tune.gemv_i4_kernel != 1) {
+                LuxBackendError e = launch_qgemv_i4_stream(ctx, c.a);
+                if (e != LUX_BACKEND_ERROR_NOT_SUPPORTED || g_tune.gemv_i4_kernel == 2) return e;
+            }
+            return launch_qskinny_i4(ctx, c.a);
+        }
         case LUX_QROUTE_GEMM_I4_TC: return launch_qgemm_i4_tc(ctx, c.a);
         default:                    return LUX_BACKEND_ERROR_NOT_SUPPORTED;
     }
@@ -242,6 +250,8 @@ LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_tune_set(const char* key, int val
     struct { const char* k; int* v; } table[] = {
         {"gemv_i4_warps", &g_tune.gemv_i4_warps},   {"gemv_i4_row_tiles", &g_tune.gemv_i4_row_tiles},
         {"gemv_i8_warps", &g_tune.gemv_i8_warps},   {"gemm_tc_bn", &g_tune.gemm_tc_bn},
+        {"gemv_i4_kernel", &g_tune.gemv_i4_kernel}, {"gemv_stream_cg", &g_tune.gemv_stream_cg},
+        {"gemv_stream_stages", &g_tune.gemv_stream_stages},
         {"gemm_tc_stages", &g_tune.gemm_tc_stages}, {"gemm_tc_splitk", &g_tune.gemm_tc_splitk},
     };
     for (auto& t : table)
