@@ -158,7 +158,7 @@ LUX_GPU_PLUGIN_EXPORT uint64_t lux_cuda_launch_count(void);
 
 /* Benchmark / tuning hook: overrides one launch heuristic (value 0 restores the
  * default).  Keys: gemv_i4_kernel (1 register-staged, 2 bulk-copy ring), gemv_i4_warps,
- * gemv_i4_row_tiles, gemv_stream_cg, gemv_stream_stages, gemv_i8_warps, gemm_tc_bn,
+ * gemv_i4_row_tiles, gemv_stream_warps, gemv_stream_cg, gemv_stream_stages, gemv_i8_warps, gemm_tc_bn,
  * gemm_tc_stages, gemm_tc_splitk.  Unknown keys return INVALID_ARGUMENT.  Process-wide;
  * not part of the drop-in surface. */
 LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_tune_set(const char* key, int value);

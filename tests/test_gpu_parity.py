@@ -23,14 +23,18 @@ TOL_16 = 5e-3
 I4_KERNELS = [0, 1, 2]
 
 
-def _stream_supported(M, K, swiglu=False):
-    """Mirror of the ring kernel's shape rule: batch <= 16, >= 8 groups per row, and room in
-    227 KB of shared memory for the staged activations plus at least three minimal stages."""
-    if M > 16 or K // 128 < 8:
+def _stream_supported(M, K, n_out=16, swiglu=False):
+    """Mirror of the ring kernel's shape rule: batch <= 16, an even number (>= 8) of groups
+    per row, output rows a multiple of the 16-row tile, and room in 227 KB of shared memory
+    for the staged activations, eight scale blocks and at least three minimal stages."""
+    G = K // 128
+    if M > 16 or G < 8 or G % 2 or n_out % 16:
         return False
+    cw = 16 if G >= 16 else 8
     mt, nacc = (1 if M <= 8 else 2), (2 if swiglu else 1)
-    fixed = M * (2 * K + 64) + 2 * 8 * nacc * mt * 32 * 16 + 2048
-    return fixed + 3 * (16 * (8 * 64 + 64) + 16) <= 227 * 1024
+    meta = (32 * G + 15) // 16 * 16 + (16 * ((G + 1) // 2) + 15) // 16 * 16
+    fixed = 1024 + M * (2 * K + 64) + 2 * cw * nacc * mt * 32 * 16 + 8 * meta + 1024
+    return fixed + 3 * (cw * 1024 + 16) <= 227 * 1024
 
 
 class _kernel:
@@ -129,7 +133,7 @@ def test_int4_skinny_shapes(ctx, backend, N, K, M, symmetric, kernel):
     x = synth.activations(M, K, "f16", 24, f"i4.{N}.{K}.{M}")
     layer = synth.int4_layer(N, K, 24, f"i4.{N}.{K}", symmetric=symmetric)
     with _kernel(backend, kernel):
-        if kernel == 2 and not _stream_supported(M, K):
+        if kernel == 2 and not _stream_supported(M, K, N):
             with pytest.raises(B.BackendError) as e:
                 _run(ctx, x, layer)
             assert e.value.code == B.NOT_SUPPORTED
@@ -140,21 +144,24 @@ def test_int4_skinny_shapes(ctx, backend, N, K, M, symmetric, kernel):
     assert ctx.last_device_status() == 0
 
 
-@pytest.mark.parametrize("cg,stages", [(1, 3), (2, 5), (4, 2), (4, 64)])
-def test_int4_stream_ring_shapes(ctx, backend, cg, stages):
-    """Every ring geometry (groups per stage, ring depth) gives the same answer."""
-    x = synth.activations(5, 2048, "f16", 28, "ring.x")
-    layer = synth.int4_layer(1000, 2048, 28, "ring")
+@pytest.mark.parametrize("warps,cg,stages", [(8, 1, 3), (8, 2, 5), (8, 4, 2), (8, 4, 64), (16, 1, 1), (16, 2, 4), (16, 1, 64)])
+def test_int4_stream_ring_shapes(ctx, backend, warps, cg, stages):
+    """Every ring geometry (consumer warps, groups per stage, ring depth) gives the same answer."""
+    x = synth.activations(5, 2560, "f16", 28, "ring.x")
+    layer = synth.int4_layer(1008, 2560, 28, "ring")
     ref = orc.qmatmul(x, *layer.triple, bits=4, group=128)
+    backend.tune("gemv_stream_warps", warps)
     backend.tune("gemv_stream_cg", cg)
     backend.tune("gemv_stream_stages", stages)
     try:
         with _kernel(backend, 2):
             y = _run(ctx, x, layer)
     finally:
+        backend.tune("gemv_stream_warps", 0)
         backend.tune("gemv_stream_cg", 0)
         backend.tune("gemv_stream_stages", 0)
     assert orc.rel_l2(y, ref) < TOL_16
+    assert ctx.last_device_status() == 0
 
 
 @pytest.mark.parametrize("wpc,rt", [(1, 1), (2, 2), (4, 4), (8, 1), (8, 4)])
@@ -181,7 +188,7 @@ def test_int4_skinny_launch_shapes(ctx, backend, wpc, rt):
 @pytest.mark.parametrize("kernel", [1, 2])
 def test_config4_sweep_streaming(ctx, backend, name, M, kernel):
     x, layer = synth.config4(name, M)
-    if kernel == 2 and not _stream_supported(M, layer.K):
+    if kernel == 2 and not _stream_supported(M, layer.K, layer.N):
         pytest.skip("activations too large for the ring kernel's shared memory")
     with _kernel(backend, kernel):
         y = _run(ctx, x, layer)
@@ -196,7 +203,7 @@ def test_config4_sweep_streaming(ctx, backend, name, M, kernel):
 def test_swiglu_epilogue_streaming(ctx, backend, M, kernel):
     gate_up, _ = synth.mlp_layers(1024, 384, 128, 26, "sw")
     x = synth.activations(M, 1024, "f16", 26, "sw.x")
-    if kernel == 2 and not _stream_supported(M, 1024, swiglu=True):
+    if kernel == 2 and not _stream_supported(M, 1024, 384, swiglu=True):
         pytest.skip("ring kernel covers batch <= 16")
     with _kernel(backend, kernel):
         h = _run(ctx, x, gate_up, flags=B.FLAG_SWIGLU)

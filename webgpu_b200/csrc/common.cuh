@@ -80,6 +80,7 @@ struct Tunables {
     int gemv_i4_kernel = 0;      // 0 auto, 1 lux_qskinny_i4_g128, 2 lux_qgemv_i4_g128_stream
     int gemv_stream_cg = 0;      // stream kernel: groups per stage / 8 (1, 2 or 4)
     int gemv_stream_stages = 0;  // stream kernel: ring depth cap
+    int gemv_stream_warps = 0;   // stream kernel: consumer warps (8 or 16)
     int gemm_tc_bn = 0;          // N tile of the tcgen05 GEMM
     int gemm_tc_stages = 0;
     int gemm_tc_splitk = 0;
@@ -105,5 +106,10 @@ LuxBackendError launch_qgemv_i4_stream(Context* ctx, const QArgs& a);   // NOT_S
 LuxBackendError launch_qgemm_i4_tc(Context* ctx, const QArgs& a);
 LuxBackendError launch_qdequant(Context* ctx, const QArgs& a, int bits);
 LuxBackendError launch_qunpack(Context* ctx, const QArgs& a, int bits);
+
+// Encodes a tiled uint8 tensor map (CUtensorMap, 128 bytes, 64-byte aligned) through the
+// driver entry point; dims/box innermost first, strides_bytes for dimensions 1..rank-1.
+bool encode_tensor_map_u8(void* map, int rank, const void* base, const uint64_t* dims, const uint64_t* strides_bytes,
+                          const uint32_t* box, bool swizzle128);
 
 }  // namespace luxcuda

@@ -31,7 +31,7 @@ struct Entry {
 
 const Entry kTable[] = {
     {"lux_qgemv_i8_g32_f32",       luxcuda::kernel_addr_qgemv_i8,           256, 1, 1},
-    {"lux_qgemv_i4_g128_stream",   luxcuda::kernel_addr_qgemv_i4_stream,    288, 1, 1},
+    {"lux_qgemv_i4_g128_stream",   luxcuda::kernel_addr_qgemv_i4_stream,    544, 1, 1},
     {"lux_qskinny_i4_g128",        luxcuda::kernel_addr_qskinny_i4,         128, 1, 1},
     {"lux_qskinny_i4_g128_swiglu", luxcuda::kernel_addr_qskinny_i4_swiglu,  128, 1, 1},
     {"lux_qdequant_i4_g128",       luxcuda::kernel_addr_qdequant_i4,        256, 1, 1},

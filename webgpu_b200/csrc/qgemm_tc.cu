@@ -75,6 +75,11 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
         ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
 }
+// Plain (untiled) bulk copy global -> shared: 16-byte aligned addresses, size a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -199,11 +204,13 @@ struct GemmParams {
     int M, Nout, K, G, ZS;
     int up_row_offset;        // SWIGLU: weight row of `up` = weight row of `gate` + this
     int stages;
+    int meta_smem;            // 1: the CTA's scales / zero-points are bulk-copied to shared memory
+    int meta_zeros_off;       // offset of the zero-points inside the shared-memory block
 };
 
 // Dynamic shared memory, all offsets from a 1024-byte aligned base:
 //   [A ring: stages x 16 KB][B ring: stages x NB*128 B][packed ring: stages x NB*32 B]
-//   [barriers + tmem slot: 256 B]
+//   [barriers + tmem slot: 256 B][scales NB x G f16, zero-points NB x ZS bytes (if meta_smem)]
 // NB = BN (or 2*BN with SwiGLU: gate rows then up rows).
 template <int BN, bool SWIGLU, bool BF16>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -224,9 +231,10 @@ lux_qgemm_i4_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     unsigned char* b_ring = a_ring + (size_t)S * A_BYTES;
     unsigned char* q_ring = b_ring + (size_t)S * B_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(q_ring + (size_t)S * Q_BYTES);
-    // bars[0..S) full_ld, [S..2S) full_b, [2S..3S) empty, [3S] acc_full
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * S + 1);
+    // bars[0..S) full_ld, [S..2S) full_b, [2S..3S) empty, [3S] acc_full, [3S+1] meta_full
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * S + 2);
     volatile uint32_t* abort_flag = tmem_slot + 1;
+    unsigned char* meta = reinterpret_cast<unsigned char*>(bars) + 512;      // 16-byte aligned
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.x * BN;            // first output column (weight row) of this tile
@@ -238,6 +246,7 @@ lux_qgemm_i4_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     auto full_b = [&](int s) { return bar0 + 8u * (uint32_t)(S + s); };
     auto empty = [&](int s) { return bar0 + 8u * (uint32_t)(2 * S + s); };
     const uint32_t acc_full = bar0 + 8u * (uint32_t)(3 * S);
+    const uint32_t meta_full = bar0 + 8u * (uint32_t)(3 * S + 1);
 
     if (tid == 0) {
         for (int s = 0; s < S; s++) {
@@ -246,6 +255,7 @@ lux_qgemm_i4_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             mbar_init(empty(s), 1);
         }
         mbar_init(acc_full, 1);
+        mbar_init(meta_full, 1);
         *abort_flag = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -261,9 +271,23 @@ lux_qgemm_i4_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     if (warp == 0) {
         // =============================== TMA producer ===================================
         if (lane == 0) {
+            if (p.meta_smem) {
+                // The tile's scales [rows, G] and zero-points [rows, ZS] are contiguous row
+                // blocks: fetch them once, before the weight stream starts.
+                const uint32_t sb = (uint32_t)(BN * p.G * 2), zb = p.zeros ? (uint32_t)(BN * p.ZS) : 0u;
+                mbar_expect_tx(meta_full, (SWIGLU ? 2u : 1u) * (sb + zb));
+                bulk_g2s(smem_u32(meta), p.scales + (size_t)n0 * p.G, sb, meta_full);
+                if (SWIGLU) bulk_g2s(smem_u32(meta + sb), p.scales + (size_t)(n0 + p.up_row_offset) * p.G, sb, meta_full);
+                if (p.zeros) {
+                    bulk_g2s(smem_u32(meta + p.meta_zeros_off), p.zeros + (size_t)n0 * p.ZS, zb, meta_full);
+                    if (SWIGLU)
+                        bulk_g2s(smem_u32(meta + p.meta_zeros_off + zb), p.zeros + (size_t)(n0 + p.up_row_offset) * p.ZS,
+                                 zb, meta_full);
+                }
+            }
+            int s = 0;
+            uint32_t ph = 0;
             for (int kb = 0; kb < KB; kb++) {
-                const int s = kb % S;
-                const uint32_t ph = (uint32_t)(kb / S) & 1u;
                 if (!mbar_wait(empty(s), ph ^ 1u, abort_flag)) break;
                 mbar_expect_tx(full_ld(s), A_BYTES + Q_BYTES);
                 tma_load_2d(smem_u32(a_ring + (size_t)s * A_BYTES), &map_x, kb * BK, m0, full_ld(s));
@@ -271,6 +295,7 @@ lux_qgemm_i4_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 if (SWIGLU)
                     tma_load_2d(smem_u32(q_ring + (size_t)s * Q_BYTES + BN * 32), &map_w, kb * (BK / 2),
                                 n0 + p.up_row_offset, full_ld(s));
+                if (++s == S) { s = 0; ph ^= 1u; }
             }
         }
     } else if (warp == 1) {
@@ -278,9 +303,9 @@ lux_qgemm_i4_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc(BF16, NB);
             bool ok = true;
+            int s = 0;
+            uint32_t ph = 0;
             for (int kb = 0; kb < KB && ok; kb++) {
-                const int s = kb % S;
-                const uint32_t ph = (uint32_t)(kb / S) & 1u;
                 ok = mbar_wait(full_ld(s), ph, abort_flag) && mbar_wait(full_b(s), ph, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
@@ -293,6 +318,7 @@ lux_qgemm_i4_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                              (kb | k) != 0 ? 1u : 0u);
                 }
                 umma_commit(empty(s));        // stage reusable once these MMAs have read it
+                if (++s == S) { s = 0; ph ^= 1u; }
             }
             if (ok) umma_commit(acc_full);    // accumulators complete
         }
@@ -305,21 +331,30 @@ lux_qgemm_i4_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         bool ok = true;
         // per-unit constants, refreshed when the group changes (every second block)
         uint32_t zc[UPT], sc_a[UPT], sc_b[UPT];
+        int s = 0;
+        uint32_t ph = 0;
+        if (p.meta_smem) ok = __all_sync(0xffffffffu, mbar_wait(meta_full, 0u, abort_flag));
+        const __half* meta_s = reinterpret_cast<const __half*>(meta);
+        const unsigned char* meta_z = meta + p.meta_zeros_off;
         for (int kb = 0; kb < KB && ok; kb++) {
-            const int s = kb % S;
-            const uint32_t ph = (uint32_t)(kb / S) & 1u;
             if ((kb & 1) == 0) {
                 const int g = kb >> 1;
 #pragma unroll
                 for (int u = 0; u < UPT; u++) {
                     const int unit = dq + u * DQ_THREADS;
-                    const int r = unit >> 1;
-                    int wrow = n0 + (SWIGLU && r >= BN ? r - BN + p.up_row_offset : r);
-                    const int limit = SWIGLU ? p.Nout + p.up_row_offset : p.Nout;
-                    wrow = min(wrow, limit - 1);
-                    const __half sh = __ldg(p.scales + (size_t)wrow * p.G + g);
+                    const int r = min(unit >> 1, NB - 1);
+                    __half sh;
                     uint32_t zp = 8u;
-                    if (p.zeros) zp = (__ldg(p.zeros + (size_t)wrow * p.ZS + (g >> 1)) >> ((g & 1) * 4)) & 0xFu;
+                    if (p.meta_smem) {
+                        sh = meta_s[(size_t)r * p.G + g];
+                        if (p.zeros) zp = ((uint32_t)meta_z[(size_t)r * p.ZS + (g >> 1)] >> ((g & 1) * 4)) & 0xFu;
+                    } else {
+                        int wrow = n0 + (SWIGLU && r >= BN ? r - BN + p.up_row_offset : r);
+                        const int limit = SWIGLU ? p.Nout + p.up_row_offset : p.Nout;
+                        wrow = min(wrow, limit - 1);
+                        sh = __ldg(p.scales + (size_t)wrow * p.G + g);
+                        if (p.zeros) zp = (__ldg(p.zeros + (size_t)wrow * p.ZS + (g >> 1)) >> ((g & 1) * 4)) & 0xFu;
+                    }
                     if (BF16) {
                         const uint32_t sbits = __float_as_uint(__half2float(sh));
                         const uint32_t hi = sbits & 0xFFFF0000u;                    // top 8 significand bits
@@ -359,6 +394,7 @@ lux_qgemm_i4_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             fence_proxy_async_smem();          // generic-proxy stores -> visible to the tensor core
             __syncwarp();
             if (lane == 0) mbar_arrive(full_b(s));
+            if (++s == S) { s = 0; ph ^= 1u; }
         }
 
         // =============================== epilogue =======================================
@@ -446,6 +482,27 @@ bool encode_2d(CUtensorMap* map, CUtensorMapDataType dt, size_t esz, const void*
     return r == CUDA_SUCCESS;
 }
 
+}  // namespace
+
+// Generic tiled tensor-map encoder shared with the other TMA-fed kernels.  dims/box are
+// innermost first; strides_bytes has rank-1 entries (dimension 0 is dense).
+bool encode_tensor_map_u8(void* map, int rank, const void* base, const uint64_t* dims, const uint64_t* strides_bytes,
+                          const uint32_t* box, bool swizzle128) {
+    auto fn = get_encode_fn();
+    if (!fn) return false;
+    cuuint64_t d[5], st[4];
+    cuuint32_t b[5], es[5];
+    for (int i = 0; i < rank; i++) { d[i] = dims[i]; b[i] = box[i]; es[i] = 1; }
+    for (int i = 0; i + 1 < rank; i++) st[i] = strides_bytes[i];
+    CUresult r = fn(reinterpret_cast<CUtensorMap*>(map), CU_TENSOR_MAP_DATA_TYPE_UINT8, (cuuint32_t)rank,
+                    const_cast<void*>(base), d, st, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+namespace {
+
 template <int BN, bool SW, bool BF16>
 cudaError_t launch_inst(const CUtensorMap& mx, const CUtensorMap& mw, GemmParams p, dim3 grid, size_t smem, cudaStream_t st) {
     auto kfn = lux_qgemm_i4_tc<BN, SW, BF16>;
@@ -474,11 +531,20 @@ LuxBackendError launch_qgemm_i4_tc(Context* ctx, const QArgs& a) {
     bn = (bn >= 128 && !a.swiglu) ? 128 : (a.swiglu ? (bn >= 128 ? 128 : 64) : 64);
     const int nb = a.swiglu ? 2 * bn : bn;
     const size_t stage_bytes = (size_t)BM * 128 + (size_t)nb * 128 + (size_t)nb * 32;
+    // Scales and zero-points of the CTA's rows go to shared memory when every block is a
+    // 16-byte aligned, 16-byte multiple copy and the table leaves room for >= 3 stages.
+    const int zs = (a.G + 1) / 2;
+    const size_t meta_scale_bytes = (size_t)nb * a.G * 2;
+    const size_t meta_bytes = meta_scale_bytes + (a.zeros ? (size_t)nb * zs : 0);
+    const size_t budget = 226 * 1024;
+    bool meta_smem = nout % bn == 0 && ((size_t)bn * a.G * 2) % 16 == 0 && ((size_t)bn * zs) % 16 == 0 &&
+                     (!a.swiglu || (((size_t)nout * a.G * 2) % 16 == 0 && ((size_t)nout * zs) % 16 == 0)) &&
+                     1024 + 3 * stage_bytes + 512 + meta_bytes <= budget;
+    const size_t tail = 512 + (meta_smem ? meta_bytes : 0);
     int stages = g_tune.gemm_tc_stages > 0 ? g_tune.gemm_tc_stages : 6;
-    const size_t budget = 220 * 1024;
-    while (stages > 2 && 1024 + (size_t)stages * stage_bytes + 512 > budget) stages--;
+    while (stages > 2 && 1024 + (size_t)stages * stage_bytes + tail > budget) stages--;
     stages = std::min(stages, std::max(2, a.K / BK));
-    const size_t smem = 1024 + (size_t)stages * stage_bytes + 512;
+    const size_t smem = 1024 + (size_t)stages * stage_bytes + tail;
 
     CUtensorMap mx, mw;
     if (!encode_2d(&mx, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.x,
@@ -500,6 +566,8 @@ LuxBackendError launch_qgemm_i4_tc(Context* ctx, const QArgs& a) {
     p.ZS = (a.G + 1) / 2;
     p.up_row_offset = a.swiglu ? nout : 0;
     p.stages = stages;
+    p.meta_smem = meta_smem ? 1 : 0;
+    p.meta_zeros_off = (int)meta_scale_bytes;
 
     dim3 grid((nout + bn - 1) / bn, (a.M + BM - 1) / BM);
     cudaError_t e;
