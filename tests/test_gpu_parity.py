@@ -23,17 +23,22 @@ TOL_16 = 5e-3
 I4_KERNELS = [0, 1, 2]
 
 
-def _stream_supported(M, K, n_out=16, swiglu=False):
+def _stream_supported(M, K, n_out=16, swiglu=False, sms=148):
     """Mirror of the ring kernel's shape rule: batch <= 16, an even number (>= 8) of groups
     per row, output rows a multiple of the 16-row tile, and room in 227 KB of shared memory
-    for the staged activations, eight scale blocks and at least three minimal stages."""
+    for the staged activations, their group sums, eight scale blocks, one batch of partial
+    sums and at least three minimal stages."""
     G = K // 128
     if M > 16 or G < 8 or G % 2 or n_out % 16:
         return False
     cw = 16 if G >= 16 else 8
     mt, nacc = (1 if M <= 8 else 2), (2 if swiglu else 1)
     meta = (32 * G + 15) // 16 * 16 + (16 * ((G + 1) // 2) + 15) // 16 * 16
-    fixed = 1024 + M * (2 * K + 64) + 2 * cw * nacc * mt * 32 * 16 + 8 * meta + 1024
+    tiles = n_out // 16
+    per_cta = -(-tiles // min(sms, tiles))
+    part_tile = cw * nacc * mt * 8 * ((min(M, 8) + 1) // 2) * 16
+    part = max(1, min(per_cta, 16384 // part_tile)) * part_tile
+    fixed = 1024 + M * (2 * K + 64) + G * 8 * mt * 8 + part + 8 * meta + 1024
     return fixed + 3 * (cw * 1024 + 16) <= 227 * 1024
 
 

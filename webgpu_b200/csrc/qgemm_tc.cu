@@ -39,7 +39,8 @@ constexpr int BM = 128;              // batch rows per CTA (UMMA M)
 constexpr int BK = 64;               // K per pipeline stage: one 128-byte swizzle row
 constexpr int NUM_DQ_WARPS = 8;
 constexpr int NUM_THREADS = (2 + NUM_DQ_WARPS) * 32;
-constexpr uint32_t WAIT_LIMIT = 1u << 20;
+// one try_wait may suspend for a few microseconds; 2^15 of them bound a wait to ~0.1 s
+constexpr uint32_t WAIT_LIMIT = 1u << 15;
 
 // ---- PTX wrappers ----------------------------------------------------------------------
 
@@ -69,6 +70,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
     *abort_flag = 1u;
     return false;
+}
+// Warp-level wait: lane 0 polls (32 lanes polling the same barrier word are served one by
+// one), the outcome is broadcast, and __syncwarp orders the other lanes' later reads after
+// lane 0's acquire.  Must be called by a converged warp.
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, int lane) {
+    bool ok = true;
+    if (lane == 0) ok = mbar_wait(bar, parity, abort_flag);
+    __syncwarp();
+    return __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
     asm volatile(
@@ -333,7 +343,7 @@ lux_qgemm_i4_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         uint32_t zc[UPT], sc_a[UPT], sc_b[UPT];
         int s = 0;
         uint32_t ph = 0;
-        if (p.meta_smem) ok = __all_sync(0xffffffffu, mbar_wait(meta_full, 0u, abort_flag));
+        if (p.meta_smem) ok = warp_wait(meta_full, 0u, abort_flag, lane);
         const __half* meta_s = reinterpret_cast<const __half*>(meta);
         const unsigned char* meta_z = meta + p.meta_zeros_off;
         for (int kb = 0; kb < KB && ok; kb++) {
@@ -370,7 +380,7 @@ lux_qgemm_i4_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     }
                 }
             }
-            ok = __all_sync(0xffffffffu, mbar_wait(full_ld(s), ph, abort_flag));   // warp-uniform outcome
+            ok = warp_wait(full_ld(s), ph, abort_flag, lane);   // warp-uniform outcome
             if (!ok) break;
             const unsigned char* qs = q_ring + (size_t)s * Q_BYTES;
             unsigned char* bs = b_ring + (size_t)s * B_BYTES;
@@ -398,7 +408,7 @@ lux_qgemm_i4_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         }
 
         // =============================== epilogue =======================================
-        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(acc_full, 0u, abort_flag));
+        if (ok) ok = warp_wait(acc_full, 0u, abort_flag, lane);
         if (ok) {
             tc_fence_after();
             const int quad = warp & 3;                          // TMEM lanes this warp may read

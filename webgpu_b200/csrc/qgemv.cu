@@ -114,7 +114,19 @@ __global__ void __launch_bounds__(256) lux_qskinny_i4_g128(const SkinnyParams p)
 
     const int tile0 = blockIdx.x * RT;
     const size_t row_bytes = (size_t)p.K >> 1;
-    const float zero4[4] = {0.f, 0.f, 0.f, 0.f};
+
+    // Ask L2 for this CTA's packed rows right away: the DRAM fetch then overlaps the staging
+    // of x below, and the streaming loads further down find their lines in L2.
+    {
+        const int rows = RT * 16 * NACC;
+        const int lines_per_row = (int)(row_bytes >> 7);               // 128-byte lines (K % 256 may leave a tail)
+        for (int i = tid; i < rows * lines_per_row; i += nthreads) {
+            const int rr = i / lines_per_row, ln = i - rr * lines_per_row;
+            const int a = rr / (RT * 16), r = rr - a * (RT * 16);
+            const int row = min(tile0 * 16 + r, p.Nout - 1) + a * p.up_row_offset;
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(p.w + (size_t)row * row_bytes + (size_t)ln * 128));
+        }
+    }
 
     for (int c0 = 0; c0 < p.G; c0 += p.kc_groups) {
         const int c1 = min(c0 + p.kc_groups, p.G);
@@ -218,7 +230,6 @@ __global__ void __launch_bounds__(256) lux_qskinny_i4_g128(const SkinnyParams p)
                                 mma16816(acc[mt], a4, a5, a6, a7, xv.z, xv.w, acc[mt]);
                             }
                         }
-                        (void)zero4;
 #pragma unroll
                         for (int mt = 0; mt < MT; mt++) {
                             res[r][a][mt][0] = fmaf(fsa[u], acc[mt][0], res[r][a][mt][0]);
@@ -463,7 +474,7 @@ LuxBackendError launch_qskinny_i4(Context* ctx, const QArgs& a) {
     // Warps per CTA split K; enough of them that every SM has ~16+ warps of loads in
     // flight even when there are few row tiles, but never more warps than groups.
     int wpc = g_tune.gemv_i4_warps;
-    if (wpc <= 0) wpc = (tiles >= sms * 4) ? 4 : 8;
+    if (wpc <= 0) wpc = (tiles * 2 >= sms * 5) ? 4 : 8;
     wpc = std::max(1, std::min({wpc, 8, a.G}));
     // x chunk: keep the staged activations within ~64 KB so several CTAs fit per SM.
     const int budget = 64 * 1024;

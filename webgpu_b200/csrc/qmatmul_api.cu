@@ -78,13 +78,18 @@ LuxBackendError dispatch(Context* ctx, const Checked& c) {
     switch (c.route) {
         case LUX_QROUTE_GEMV_I8:    return launch_qgemv_i8(ctx, c.a);
         case LUX_QROUTE_SKINNY_I4: {
-            // Both kernels compute the same thing; the bulk-copy ring kernel is the fast
-            // path for batch <= 16, the register-staged one covers every other shape.
-            if (g_tune.gemv_i4_kernel != 1) {
-                LuxBackendError e = launch_qgemv_i4_stream(ctx, c.a);
+            // Both kernels compute the same thing.  Measured on B200: the TMA ring kernel wins
+            // for batches of 4..16 and for big layers (long rows or many megabytes of weights);
+            // the register-staged kernel wins for batch 1..3 on small layers and covers every
+            // shape the ring kernel does not take.
+            const QArgs& a = c.a;
+            const size_t wbytes = (size_t)a.N * a.K / 2;
+            const bool prefer_ring = a.M >= 4 || a.K >= 8192 || wbytes >= ((size_t)40 << 20);
+            if (g_tune.gemv_i4_kernel == 2 || (g_tune.gemv_i4_kernel == 0 && prefer_ring)) {
+                LuxBackendError e = launch_qgemv_i4_stream(ctx, a);
                 if (e != LUX_BACKEND_ERROR_NOT_SUPPORTED || g_tune.gemv_i4_kernel == 2) return e;
             }
-            return launch_qskinny_i4(ctx, c.a);
+            return launch_qskinny_i4(ctx, a);
         }
         case LUX_QROUTE_GEMM_I4_TC: return launch_qgemm_i4_tc(ctx, c.a);
         default:                    return LUX_BACKEND_ERROR_NOT_SUPPORTED;
