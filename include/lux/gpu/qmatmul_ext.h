@@ -138,6 +138,25 @@ LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_qmlp(
     LuxBackendBuffer* w_down, LuxBackendBuffer* s_down, LuxBackendBuffer* z_down,
     LuxBackendBuffer* h_scratch, LuxBackendBuffer* y);
 
+/* The FFN above for callers that must not allocate device memory.  NO COUNTERPART IN THE
+ * REFERENCE: luxcpp/webgpu has no allocation-free variant of any op.
+ *
+ * Who needs it: a host that gave all device memory to its own arena at start-up (a later
+ * cudaMalloc would fail or fragment it), and latency-critical decode loops, where
+ * cudaMalloc / cudaFree synchronise the whole device.  Instead of a caller-provided `h`,
+ * the SwiGLU output goes to a fixed array inside this library's device image
+ * (LUX_QMLP_NOALLOC_MAX_BYTES, held by every GPU that loads the library until exit).
+ * Rules: M * I * 2 bytes must fit that array, else INVALID_ARGUMENT; every call on a device
+ * shares the one array, so calls that overlap on the GPU race; the first call on a device
+ * resolves the array's address and should be made outside any stream capture.  It calls no
+ * cudaMalloc, cudaFree or other allocating routine. */
+#define LUX_QMLP_NOALLOC_MAX_BYTES (1u << 20)
+LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_qmlp_noalloc(
+    LuxBackendContext* ctx, const LuxQMlpDesc* desc, LuxBackendBuffer* x,
+    LuxBackendBuffer* w_gate_up, LuxBackendBuffer* s_gate_up, LuxBackendBuffer* z_gate_up,
+    LuxBackendBuffer* w_down, LuxBackendBuffer* s_down, LuxBackendBuffer* z_down,
+    LuxBackendBuffer* y);
+
 /* -- interop needed by a host that already owns CUDA state (one process per GPU) ---- */
 
 /* Run this context's work on an existing stream (a cudaStream_t passed as void*;

@@ -37,6 +37,7 @@ ERROR_NAMES = {
 CAP_TENSOR_OPS, CAP_MATMUL, CAP_CUSTOM_KERNELS = 1 << 0, 1 << 1, 1 << 4
 
 F32, F16, BF16 = 0, 1, 2
+NOALLOC_MAX_BYTES = 1 << 20          # LUX_QMLP_NOALLOC_MAX_BYTES
 FLAG_NO_SYNC, FLAG_SWIGLU = 1, 2
 ROUTE_NONE, ROUTE_GEMV_I8, ROUTE_SKINNY_I4, ROUTE_GEMM_I4_TC = range(4)
 
@@ -102,7 +103,7 @@ class KernelAttributes(C.Structure):
 EXPORTED_SYMBOLS = [
     "lux_gpu_backend_init",
     "lux_cuda_qmatmul", "lux_cuda_qmatmul_host", "lux_cuda_qmatmul_route", "lux_cuda_qdequant",
-    "lux_cuda_qunpack", "lux_cuda_qmlp", "lux_cuda_context_set_stream", "lux_cuda_context_get_stream",
+    "lux_cuda_qunpack", "lux_cuda_qmlp", "lux_cuda_qmlp_noalloc", "lux_cuda_context_set_stream", "lux_cuda_context_get_stream",
     "lux_cuda_buffer_wrap", "lux_cuda_buffer_device_ptr", "lux_cuda_buffer_size",
     "lux_cuda_launch_count", "lux_cuda_tune_set", "lux_cuda_last_device_status",
     "lux_cuda_kernel_get", "lux_cuda_kernel_destroy", "lux_cuda_kernel_entry_point",
@@ -185,6 +186,7 @@ class Backend:
         L.lux_cuda_qdequant.argtypes = [_vp, C.POINTER(QMatmulDesc), _vp, _vp, _vp, _vp]
         L.lux_cuda_qunpack.argtypes = [_vp, C.POINTER(QMatmulDesc), _vp, _vp, _vp]
         L.lux_cuda_qmlp.argtypes = [_vp, C.POINTER(QMlpDesc)] + [_vp] * 9
+        L.lux_cuda_qmlp_noalloc.argtypes = [_vp, C.POINTER(QMlpDesc)] + [_vp] * 8
         L.lux_cuda_context_set_stream.argtypes = [_vp, _vp]
         L.lux_cuda_context_get_stream.argtypes = [_vp]
         L.lux_cuda_context_get_stream.restype = _vp
@@ -422,6 +424,16 @@ class Context:
         _check(self.backend.lib.lux_cuda_qmlp(self.handle, C.byref(d), x.handle, gate_up.w.handle,
                                               gate_up.scales.handle, z(gate_up), down.w.handle, down.scales.handle,
                                               z(down), h.handle, y.handle), "lux_cuda_qmlp")
+
+    def qmlp_noalloc(self, x: Buffer, gate_up: DeviceQLayer, down: DeviceQLayer, y: Buffer, M: int,
+                     act_dtype: int, flags: int = 0) -> None:
+        """The FFN with the library's built-in scratch instead of a caller-provided one
+        (for callers that must not allocate); M * I * 2 bytes must fit NOALLOC_MAX_BYTES."""
+        d = QMlpDesc(C.sizeof(QMlpDesc), M, gate_up.K, gate_up.N // 2, down.N, gate_up.group, act_dtype, flags)
+        z = lambda L: L.zeros.handle if L.zeros else None
+        _check(self.backend.lib.lux_cuda_qmlp_noalloc(self.handle, C.byref(d), x.handle, gate_up.w.handle,
+                                                      gate_up.scales.handle, z(gate_up), down.w.handle,
+                                                      down.scales.handle, z(down), y.handle), "lux_cuda_qmlp_noalloc")
 
     def last_device_status(self) -> int:
         return int(self.backend.lib.lux_cuda_last_device_status(self.handle))
