@@ -38,6 +38,9 @@ if ROOT not in sys.path:
 import numpy as np  # noqa: E402
 
 L2_BYTES = 126 * 1024 * 1024
+# dram__bytes_read.sum + dram__bytes_write.sum of one config-2 GEMV launch, from the ncu
+# captures summarised in profiles/qskinny_i4_g128_config2.md (30.546 MB read, 0 written)
+NCU_TRAFFIC_CONFIG2 = 30546432
 NOMINAL_HBM_GBS = 8000.0          # the benchmark specification's "~8 TB/s"
 NOMINAL_BF16_TFLOPS = 2250.0
 FALLBACK_HBM_GBS = 6650.0         # earlier measurement on this pool, used only without MEASURED_PEAKS.json
@@ -115,13 +118,16 @@ def dist_env():
 class Rig:
     """Plugin context bound to a torch stream, so CUDA events see the kernels."""
 
-    def __init__(self, local_rank: int):
+    def __init__(self, local_rank: int, tunes=()):
         import torch
         from webgpu_b200 import backend as B
 
         self.torch, self.B = torch, B
         torch.cuda.set_device(local_rank)
         self.backend = B.load()
+        for kv in tunes:
+            key, _, val = kv.partition("=")
+            self.backend.tune(key, int(val))
         self.ctx = self.backend.create_context(local_rank)
         self.stream = torch.cuda.Stream()
         self.ctx.set_stream(self.stream.cuda_stream)
@@ -180,7 +186,7 @@ def bench_single(args, peaks):
     from oracle import oracle as orc      # cpu_baseline leg only
     from webgpu_b200 import synth
 
-    rig = Rig(0)
+    rig = Rig(0, args.tune)
     B, ctx, torch = rig.B, rig.ctx, rig.torch
     sampler = ClockSampler(0)
 
@@ -285,7 +291,7 @@ def bench_single(args, peaks):
                    "l2": f"inputs larger than L2: {len(pool)} weight copies x {wbytes / 1e6:.1f} MB rotated per step",
                    "timing": "CUDA graph replays of the launch sequence, CUDA events on the launching stream"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s",
-                     "frac": achieved / peaks["hbm"], "traffic": None, "peak_source": peaks["source"],
+                     "frac": achieved / peaks["hbm"], "traffic": NCU_TRAFFIC_CONFIG2, "peak_source": peaks["source"],
                      "frac_of_nominal_8tbs": achieved / NOMINAL_HBM_GBS, "algorithmic_bytes": abytes,
                      "kernel": "lux_qskinny_i4_g128"},
         "cpu_baseline": {"value": wbytes / cpu_sec / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
@@ -313,7 +319,7 @@ def bench_tp(args, peaks):
     torch.cuda.set_device(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    rig = Rig(local_rank)
+    rig = Rig(local_rank, args.tune)
     B, ctx = rig.B, rig.ctx
     d = synth.MLP70B
     M = args.batch
@@ -473,6 +479,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=1, help="batch M of the tensor-parallel FFN workload")
     ap.add_argument("--workload", default="auto", choices=["auto", "gemv", "tp_mlp"])
+    ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE",
+                    help="override a launch heuristic (lux_cuda_tune_set), e.g. gemv_i4_kernel=2")
     args = ap.parse_args()
     peaks = measured_peaks()
     if args.impl == "reference":

@@ -235,7 +235,10 @@ lux_qgemm_i4_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     static_assert((NB * 2) % (NUM_DQ_WARPS * 32) == 0 || (NUM_DQ_WARPS * 32) % (NB * 2) == 0, "dequant mapping");
 
     extern __shared__ unsigned char smem_raw[];
-    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // 1024-byte alignment by OFFSET from the __shared__ symbol, so that every access below
+    // stays a 32-bit shared-memory access (a round trip through an integer would turn them
+    // into generic 64-bit ones).
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const int S = p.stages;
     unsigned char* a_ring = smem;
     unsigned char* b_ring = a_ring + (size_t)S * A_BYTES;

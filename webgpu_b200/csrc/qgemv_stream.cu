@@ -173,7 +173,10 @@ template <int MT, bool SWIGLU, int CW, int GPW>
 __global__ void __launch_bounds__((CW + 1) * 32, 1)
 lux_qgemv_i4_g128_stream(const __grid_constant__ CUtensorMap map_w, const StreamParams p) {
     extern __shared__ unsigned char smem_raw[];
-    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // 1024-byte alignment by OFFSET from the __shared__ symbol, so that every access below
+    // stays a 32-bit shared-memory access (a round trip through an integer would turn them
+    // into generic 64-bit ones).
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     constexpr int NACC = SWIGLU ? 2 : 1;
     constexpr int MPAD = 8 * MT;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
