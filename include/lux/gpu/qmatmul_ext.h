@@ -176,8 +176,9 @@ LUX_GPU_PLUGIN_EXPORT size_t lux_cuda_buffer_size(LuxBackendBuffer* buf);
 LUX_GPU_PLUGIN_EXPORT uint64_t lux_cuda_launch_count(void);
 
 /* Benchmark / tuning hook: overrides one launch heuristic (value 0 restores the
- * default).  Keys: gemv_i4_kernel (1 register-staged, 2 bulk-copy ring), gemv_i4_warps,
- * gemv_i4_row_tiles, gemv_stream_warps, gemv_stream_cg, gemv_stream_stages, gemv_i8_warps, gemm_tc_bn,
+ * default).  Keys: gemv_i4_kernel (1 register-staged, 2 bulk-copy ring, 3 warp-autonomous
+ * units), gemv_i4_warps, gemv_i4_row_tiles, gemv_stream_warps, gemv_stream_cg, gemv_stream_stages,
+ * gemv_units_ks, gemv_units_stages, gemv_units_cg, gemv_units_pre, gemv_units_fx, gemv_i8_warps, gemm_tc_bn,
  * gemm_tc_stages, gemm_tc_splitk.  Unknown keys return INVALID_ARGUMENT.  Process-wide;
  * not part of the drop-in surface. */
 LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_tune_set(const char* key, int value);

@@ -19,8 +19,50 @@ TOL_16 = 5e-3
 
 # The int4 decode path has two kernels computing the same thing: 1 = register-staged
 # lux_qskinny_i4_g128 (any shape), 2 = bulk-copy ring lux_qgemv_i4_g128_stream (batch <= 16,
-# at least 8 groups per row).  0 lets the library choose.
-I4_KERNELS = [0, 1, 2]
+# at least 8 groups per row), 3 = warp-autonomous lux_qgemv_i4_g128_units (batch <= 16, group
+# count a multiple of 4).  0 lets the library choose.
+I4_KERNELS = [0, 1, 2, 3]
+
+
+def _units_supported(M, K, n_out=16, swiglu=False, sms=148, f16_variant=False):
+    """Mirror of the units kernel's shape rule: batch <= 16, an even group count, output rows a
+    multiple of the 16-row tile, and room in 227 KB of shared memory for the staged
+    activations, their group sums, the CTA's scale / zero-point tables, the partial-sum slots,
+    the unit table and two chunks of FIFO per warp."""
+    G = K // 128
+    if M > 16 or G < 2 or G % 2 or n_out % 16:
+        return False
+    mt, nacc = (1 if M <= 8 else 2), (2 if swiglu else 1)
+    cg = 2 if G % 4 else 4
+    tiles = n_out // 16
+    per_cta = -(-tiles // min(sms, tiles))
+    best, KS = 1e30, 0
+    for ks in range(cg, min(G, 32) + 1, cg):
+        if G % ks:
+            continue
+        cost = -(-(per_cta * nacc * (G // ks)) // 16) * (ks + 0.25)
+        if cost < best - 1e-9:
+            best, KS = cost, ks
+    if not KS:
+        return False
+    cap = per_cta * nacc * (G // KS)
+    rows = per_cta * 16 * nacc
+    tmax = (min(M, 8) + 1) // 2
+    zs = (G + 1) // 2
+    meta = rows * G * 2 + ((rows * zs + 15) & ~15) + cap * 16
+    if M <= 2 and not f16_variant:      # block-fixed-point variant: three byte planes of x
+        fixed = G * 3 * M * 128 + G * 64 + meta + cap * 16 * M * 4 + 16 * 8 * 8 + 16 + 1024   # + barriers, slack
+    else:
+        fixed = M * (2 * K + 64) + G * 8 * mt * 8 + meta + cap * mt * 8 * tmax * 16
+    return fixed + 2 * 16 * cg * 1024 <= 227 * 1024
+
+
+def _kernel_supported(kernel, M, K, n_out, swiglu=False):
+    if kernel == 2:
+        return _stream_supported(M, K, n_out, swiglu)
+    if kernel == 3:
+        return _units_supported(M, K, n_out, swiglu)
+    return True
 
 
 def _stream_supported(M, K, n_out=16, swiglu=False, sms=148):
@@ -138,7 +180,7 @@ def test_int4_skinny_shapes(ctx, backend, N, K, M, symmetric, kernel):
     x = synth.activations(M, K, "f16", 24, f"i4.{N}.{K}.{M}")
     layer = synth.int4_layer(N, K, 24, f"i4.{N}.{K}", symmetric=symmetric)
     with _kernel(backend, kernel):
-        if kernel == 2 and not _stream_supported(M, K, N):
+        if not _kernel_supported(kernel, M, K, N):
             with pytest.raises(B.BackendError) as e:
                 _run(ctx, x, layer)
             assert e.value.code == B.NOT_SUPPORTED
@@ -169,6 +211,82 @@ def test_int4_stream_ring_shapes(ctx, backend, warps, cg, stages):
     assert ctx.last_device_status() == 0
 
 
+@pytest.mark.parametrize("cg,ks,stages,pre", [(4, 4, 2, 1), (4, 8, 3, 3), (4, 12, 1, 1), (4, 24, 8, 2), (2, 2, 6, 1),
+                                              (2, 6, 2, 2), (2, 8, 3, 1)])
+@pytest.mark.parametrize("M,fx", [(1, 1), (1, 2), (2, 1), (2, 2), (3, 0), (11, 0)])
+def test_int4_units_geometries(ctx, backend, cg, ks, stages, pre, M, fx):
+    """Every chunk size, K-slice width, FIFO depth and pre-request count of the units kernel
+    gives the same answer, in both arithmetic variants (fx 1: block fixed point + int8 mma,
+    fx 2: f16 mma).  24 groups per row; 63 tiles, so the FIFO wraps many times."""
+    x = synth.activations(M, 3072, "f16", 29, "units.x")
+    layer = synth.int4_layer(1008, 3072, 29, "units")
+    ref = orc.qmatmul(x, *layer.triple, bits=4, group=128)
+    tunes = {"gemv_units_cg": cg, "gemv_units_ks": ks, "gemv_units_stages": stages, "gemv_units_pre": pre,
+             "gemv_units_fx": fx}
+    for k, v in tunes.items():
+        backend.tune(k, v)
+    try:
+        with _kernel(backend, 3):
+            y = _run(ctx, x, layer)
+    finally:
+        for k in tunes:
+            backend.tune(k, 0)
+    assert orc.rel_l2(y, ref) < TOL_16
+    assert ctx.last_device_status() == 0
+
+
+@pytest.mark.parametrize("M", [1, 2])
+def test_int4_units_fixed_point_ranges(ctx, backend, M):
+    """Block fixed point per group of 128 activations: groups of all zeros, of f16 denormals,
+    of large values, and groups mixing magnitudes 2^12 apart must all agree with
+    the oracle (elements more than 2^11 below their group's maximum lose low bits, at most
+    2^-23 of that maximum each)."""
+    K, N = 2048, 256
+    rng = np.random.default_rng(77)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    x[:, 0:128] = 0.0                                            # an all-zero group
+    x[:, 128:256] *= 3e-7                                        # f16 denormals
+    x[:, 256:384] = np.sign(x[:, 256:384]) * 30000.0             # large: the products still fit f16
+    x[:, 384:512] *= np.where(np.arange(128) % 7 == 0, 4096.0, 1.0)   # mixed magnitudes
+    x[:, 512:640] = -x[:, 512:640] * 1e-3
+    x = x.astype(np.float16)
+    layer = synth.int4_layer(N, K, 78, "fxr")
+    ref = orc.qmatmul(x, *layer.triple, bits=4, group=128)
+    assert np.isfinite(ref).all()
+    with _kernel(backend, 3):
+        y = _run(ctx, x, layer)
+    assert orc.rel_l2(y, ref) < TOL_16
+    # without the huge group, the small groups must be resolved on their own
+    x2 = x.copy()
+    x2[:, 256:384] = 0
+    ref2 = orc.qmatmul(x2, *layer.triple, bits=4, group=128)
+    with _kernel(backend, 3):
+        y2 = _run(ctx, x2, layer)
+    assert orc.rel_l2(y2, ref2) < TOL_16
+
+
+def test_int4_units_fixed_point_nonfinite(ctx, backend):
+    """An infinity or NaN among the activations makes every output non-finite, as it does in
+    the oracle (each output multiplies every activation)."""
+    x = synth.activations(1, 1024, "f16", 5, "nf.x").copy()
+    x[0, 300] = np.float16(np.inf)
+    layer = synth.int4_layer(64, 1024, 5, "nf")
+    with _kernel(backend, 3):
+        y = _run(ctx, x, layer)
+    assert not np.isfinite(y.astype(np.float32)).any()
+
+
+def test_int4_units_many_tiles_per_cta(ctx, backend):
+    """More tiles than SMs (CTAs own several tiles, unevenly), symmetric weights (no zero-point
+    tensor) and a group count that only allows two-group chunks."""
+    x = synth.activations(2, 128 * 6, "f16", 31, "units2.x")
+    layer = synth.int4_layer(16 * 500, 128 * 6, 31, "units2", symmetric=True)
+    ref = orc.qmatmul(x, *layer.triple, bits=4, group=128)
+    with _kernel(backend, 3):
+        y = _run(ctx, x, layer)
+    assert orc.rel_l2(y, ref) < TOL_16
+
+
 @pytest.mark.parametrize("wpc,rt", [(1, 1), (2, 2), (4, 4), (8, 1), (8, 4)])
 def test_int4_skinny_launch_shapes(ctx, backend, wpc, rt):
     """Every warps-per-CTA / row-tiles-per-CTA combination gives the same answer."""
@@ -190,11 +308,11 @@ def test_int4_skinny_launch_shapes(ctx, backend, wpc, rt):
 
 @pytest.mark.parametrize("name", list(synth.SWEEP_LAYERS))
 @pytest.mark.parametrize("M", [1, 4, 16])
-@pytest.mark.parametrize("kernel", [1, 2])
+@pytest.mark.parametrize("kernel", [1, 2, 3])
 def test_config4_sweep_streaming(ctx, backend, name, M, kernel):
     x, layer = synth.config4(name, M)
-    if kernel == 2 and not _stream_supported(M, layer.K, layer.N):
-        pytest.skip("activations too large for the ring kernel's shared memory")
+    if not _kernel_supported(kernel, M, layer.K, layer.N):
+        pytest.skip("activations too large for this kernel's shared memory")
     with _kernel(backend, kernel):
         y = _run(ctx, x, layer)
     ref = orc.qmatmul(x, *layer.triple, bits=4, group=128)
@@ -204,12 +322,12 @@ def test_config4_sweep_streaming(ctx, backend, name, M, kernel):
 # -- SwiGLU epilogue and the FFN ------------------------------------------------------------
 
 @pytest.mark.parametrize("M", [1, 8, 12, 20])
-@pytest.mark.parametrize("kernel", [1, 2])
+@pytest.mark.parametrize("kernel", [1, 2, 3])
 def test_swiglu_epilogue_streaming(ctx, backend, M, kernel):
     gate_up, _ = synth.mlp_layers(1024, 384, 128, 26, "sw")
     x = synth.activations(M, 1024, "f16", 26, "sw.x")
-    if kernel == 2 and not _stream_supported(M, 1024, 384, swiglu=True):
-        pytest.skip("ring kernel covers batch <= 16")
+    if not _kernel_supported(kernel, M, 1024, 384, swiglu=True):
+        pytest.skip("this kernel covers batch <= 16")
     with _kernel(backend, kernel):
         h = _run(ctx, x, gate_up, flags=B.FLAG_SWIGLU)
     gu = orc.qmatmul(x, *gate_up.triple, bits=4, group=128, y_code=orc.F32)

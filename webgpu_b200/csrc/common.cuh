@@ -77,10 +77,15 @@ struct Tunables {
     int gemv_i4_warps = 0;       // warps per CTA of the int4 skinny kernel
     int gemv_i4_row_tiles = 0;   // 16-row tiles per CTA
     int gemv_i8_warps = 0;
-    int gemv_i4_kernel = 0;      // 0 auto, 1 lux_qskinny_i4_g128, 2 lux_qgemv_i4_g128_stream
+    int gemv_i4_kernel = 0;      // 0 auto, 1 lux_qskinny_i4_g128, 2 lux_qgemv_i4_g128_stream, 3 lux_qgemv_i4_g128_units
     int gemv_stream_cg = 0;      // stream kernel: groups per stage / 8 (1, 2 or 4)
     int gemv_stream_stages = 0;  // stream kernel: ring depth cap
     int gemv_stream_warps = 0;   // stream kernel: consumer warps (8 or 16)
+    int gemv_units_ks = 0;       // units kernel: groups per unit (a multiple of the chunk that divides K/128)
+    int gemv_units_stages = 0;   // units kernel: cap on the FIFO depth per warp (chunks)
+    int gemv_units_cg = 0;       // units kernel: groups per chunk (2 or 4)
+    int gemv_units_pre = 0;      // units kernel: chunks requested per warp before its loop starts (default 1)
+    int gemv_units_fx = 0;       // units kernel, batch <= 2: 0/1 block-fixed-point int8 variant, 2 f16 variant
     int gemm_tc_bn = 0;          // N tile of the tcgen05 GEMM
     int gemm_tc_stages = 0;
     int gemm_tc_splitk = 0;
@@ -103,6 +108,7 @@ struct QArgs {
 LuxBackendError launch_qgemv_i8(Context* ctx, const QArgs& a);
 LuxBackendError launch_qskinny_i4(Context* ctx, const QArgs& a);
 LuxBackendError launch_qgemv_i4_stream(Context* ctx, const QArgs& a);   // NOT_SUPPORTED if the shape does not fit
+LuxBackendError launch_qgemv_i4_units(Context* ctx, const QArgs& a);    // NOT_SUPPORTED if the shape does not fit
 LuxBackendError launch_qgemm_i4_tc(Context* ctx, const QArgs& a);
 LuxBackendError launch_qdequant(Context* ctx, const QArgs& a, int bits);
 LuxBackendError launch_qunpack(Context* ctx, const QArgs& a, int bits);

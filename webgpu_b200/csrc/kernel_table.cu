@@ -15,6 +15,8 @@ const void* kernel_addr_qskinny_i4();
 const void* kernel_addr_qskinny_i4_swiglu();
 const void* kernel_addr_qgemv_i8();
 const void* kernel_addr_qgemv_i4_stream();
+const void* kernel_addr_qgemv_i4_units();
+const void* kernel_addr_qgemv_i4_units_fx();
 const void* kernel_addr_qdequant_i4();
 const void* kernel_addr_qdequant_i8();
 const void* kernel_addr_qgemm_i4_tc_bf16();
@@ -32,6 +34,8 @@ struct Entry {
 const Entry kTable[] = {
     {"lux_qgemv_i8_g32_f32",       luxcuda::kernel_addr_qgemv_i8,           256, 1, 1},
     {"lux_qgemv_i4_g128_stream",   luxcuda::kernel_addr_qgemv_i4_stream,    544, 1, 1},
+    {"lux_qgemv_i4_g128_units",    luxcuda::kernel_addr_qgemv_i4_units,     512, 1, 1},
+    {"lux_qgemv_i4_g128_units_fx", luxcuda::kernel_addr_qgemv_i4_units_fx,  512, 1, 1},
     {"lux_qskinny_i4_g128",        luxcuda::kernel_addr_qskinny_i4,         128, 1, 1},
     {"lux_qskinny_i4_g128_swiglu", luxcuda::kernel_addr_qskinny_i4_swiglu,  128, 1, 1},
     {"lux_qdequant_i4_g128",       luxcuda::kernel_addr_qdequant_i4,        256, 1, 1},

@@ -1,0 +1,993 @@
+// lux_qgemv_i4_g128_units -- int4 g128 decode GEMV (batch M <= 16), warp-autonomous version.
+//
+// Measurements of the other int4 kernels on B200 showed that neither HBM nor the unpack + mma
+// arithmetic limits them: the time goes into the short serial sections between pieces of
+// work (barrier waits, scale look-ups, hand-offs), which run at tens of cycles per
+// instruction when sixteen warps reach them together, into issuing many small TMA copies
+// (~130 cycles each, one at a time per SM), and into memory sitting idle whenever less than
+// the bandwidth-delay product (~60 KB per SM) is in flight.  This kernel has no barrier
+// and no cross-thread hand-off inside its loop:
+//
+//   * one persistent CTA per SM owns a contiguous range of 16-row tiles; a tile is cut along
+//     K into U units of KS groups, and every (tile, gate/up, unit) is handled by ONE warp
+//     from start to finish;
+//   * the warp streams its units in chunks of CG groups (2 or 4) through a PRIVATE FIFO in
+//     shared memory filled with per-lane 16-byte cp.async copies.  Each lane copies exactly
+//     the bytes it will later read back itself (its 32 nibbles of rows g and g+8 of every
+//     group), so cp.async.wait_group is the only synchronisation, the layout is free of bank
+//     conflicts by construction, and the FIFOs together hold ~190 KB per SM in flight --
+//     for a 4096 x 14336 layer that is the SM's whole share, requested in the first microsecond;
+//   * x is staged once per CTA in shared memory in mma-fragment order together with its
+//     per-group sums; the CTA's scales and zero-points are staged once too, so the loop makes
+//     no dependent global load.  These are requested BEFORE the weights: requests are served
+//     roughly in order, and an x request queued behind 190 KB of weights arrives 4 us late.  The zero-point is folded out of the inner loop exactly as in
+//     the ring kernel (sum (n - zp) x = acc - (1024 + zp) sum x + 960 sum_{odd k} x);
+//   * a unit's partial result goes to its own slot in shared memory; after the last unit the
+//     CTA meets once (__syncthreads) and adds the U partials of every output in a fixed order.
+//
+// Two arithmetic variants share this structure:
+//
+//   lux_qgemv_i4_g128_units     (batch 1..16)  nibbles -> f16 with the lop3 magic-number trick,
+//       mma.m16n8k16.f16 with f32 accumulation: the arithmetic of lux_qskinny_i4_g128.
+//   lux_qgemv_i4_g128_units_fx  (batch 1..2)   the integer pipe of an SM sub-core issues one
+//       lop3 per TWO cycles, and at 5 integer ops per 8 nibbles the unpack above -- not HBM, not
+//       the tensor pipe -- bounds the f16 variant.  This one spends 2 ops per 8 nibbles: the
+//       bytes (w & 0x0f0f0f0f) and (w & 0xf0f0f0f0) ARE the low and 16 x the high nibbles as u8,
+//       fed to mma.m16n8k32.u8.s8 (half as many mma).  The activations are converted once per
+//       CTA to block fixed point: per group of 128, X = rint(x * 2^(22-E)) with 2^E just above
+//       the group's largest |x| (every f16 within 2^-11 of that magnitude is represented
+//       exactly; the absolute error is at most 2^(E-23)), split into three signed bytes
+//       X = d0 + 256 d1 + 65536 d2 that ride in three of the eight B columns.  The int32
+//       accumulators are exact; sum (n - zp) X is formed in integers, scaled by
+//       2^(E-22) 256^plane and the group's f16 scale in f32, and the three planes are added
+//       at the end of a unit.
+//
+// Both compute matmul_nax_grouped (luxcpp/webgpu kernels/wgsl/gpu/quantized_nax.wgsl:568-626)
+// in a different summation order.
+#include "common.cuh"
+
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include <algorithm>
+
+namespace luxcuda {
+
+namespace {
+
+constexpr int UW = 16;                          // warps per CTA
+constexpr int MAX_STAGES = 8;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t mask, uint32_t orv) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(mask), "r"(orv));
+    return d;
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+// 16-byte asynchronous copy global -> shared, bypassing L1 (the data is read once)
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// wait until at most n of this thread's most recent copy groups are still pending
+__device__ __forceinline__ void cp_async_wait(int n) {
+#define LUX_WAIT_CASE(N) case N: asm volatile("cp.async.wait_group " #N ";" ::: "memory"); break;
+    switch (n) {
+        LUX_WAIT_CASE(0) LUX_WAIT_CASE(1) LUX_WAIT_CASE(2) LUX_WAIT_CASE(3) LUX_WAIT_CASE(4) LUX_WAIT_CASE(5)
+        LUX_WAIT_CASE(6) LUX_WAIT_CASE(7) LUX_WAIT_CASE(8) LUX_WAIT_CASE(9) LUX_WAIT_CASE(10) LUX_WAIT_CASE(11)
+        LUX_WAIT_CASE(12) LUX_WAIT_CASE(13) LUX_WAIT_CASE(14) LUX_WAIT_CASE(15) LUX_WAIT_CASE(16) LUX_WAIT_CASE(17)
+        LUX_WAIT_CASE(18) LUX_WAIT_CASE(19) LUX_WAIT_CASE(20) LUX_WAIT_CASE(21) LUX_WAIT_CASE(22) LUX_WAIT_CASE(23)
+        LUX_WAIT_CASE(24) LUX_WAIT_CASE(25) LUX_WAIT_CASE(26) LUX_WAIT_CASE(27) LUX_WAIT_CASE(28)
+        // waiting for more than was asked is always safe
+        default: asm volatile("cp.async.wait_group 28;" ::: "memory"); break;
+    }
+#undef LUX_WAIT_CASE
+}
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// D(s32) += A(u8, 16x32) * B(s8, 32x8)
+__device__ __forceinline__ void mma16832_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                              uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float silu_f32(float x) { return x / (1.0f + __expf(-x)); }
+
+// Optional timeline for kernel development: built only with -DLUX_STREAM_TRACE.
+#ifdef LUX_STREAM_TRACE
+__device__ unsigned long long g_units_trace[32 * 64];
+#define TRACE_DECL int tr_i = 0
+#define TRACE(tag)                                                                   \
+    do {                                                                             \
+        if (blockIdx.x == 0 && lane == 0 && tr_i < 64) g_units_trace[warp * 64 + tr_i++] = ((unsigned long long)(tag) << 56) | (clock64() & 0xFFFFFFFFFFFFFFull); \
+    } while (0)
+#else
+#define TRACE_DECL
+#define TRACE(tag)
+#endif
+
+struct UnitsParams {
+    const __half* x;        // [M, K]
+    const uint8_t* w;       // [Nw, K/2]
+    const __half* scales;   // [Nw, G]
+    const uint8_t* zeros;   // [Nw, ZS] or null
+    __half* y;              // [M, Nout]
+    int M, Nout, K, G, ZS;
+    int up_row_offset;
+    int tiles_base, tiles_rem;   // CTA b owns tiles [b*base + min(b, rem), +base + (b < rem))
+    int U, KS;              // units per (tile, gate/up) and groups per unit (U * KS == G, KS % CG == 0)
+    int S;                  // FIFO depth in chunks (per warp)
+    int S0;                 // chunks requested before the loop starts (the rest ramp up inside it)
+    int xstride;            // bytes between batch rows of the staged x
+    int tmax;               // lanes t < tmax hold live batch columns
+    int units_cap;          // partial-sum slots available per CTA
+    int rows_cap;           // weight rows (gate + up) whose scales / zero-points are staged per CTA
+    uint32_t* status;       // device status word for a wait that gave up (may be null)
+};
+
+// Shared memory: [x staged: M * xstride][xsum: G * 8*MT * 8][scales: rows_cap * G f16]
+// [zero-points: rows_cap * ZS bytes, padded to 16][partials: units_cap x MT x 8*tmax float4]
+// [unit table: units_cap x int4][FIFOs: UW x S x CG KB]
+template <int MT, bool SWIGLU, bool M1, int CG>
+__global__ void __launch_bounds__(UW * 32, 1) lux_qgemv_i4_g128_units(const UnitsParams p) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    constexpr int NACC = SWIGLU ? 2 : 1;
+    constexpr int MPAD = 8 * MT;
+    constexpr int CHUNK = CG * 1024;                    // bytes: 16 rows x CG groups x 64
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int slot4 = MT * 8 * p.tmax;                  // float4 per unit
+    TRACE_DECL;
+    TRACE(1);
+
+    unsigned char* xs = smem;
+    float2* xsum = reinterpret_cast<float2*>(xs + (size_t)p.M * p.xstride);
+    __half* ssm = reinterpret_cast<__half*>(xsum + (size_t)p.G * MPAD);
+    unsigned char* zsm = reinterpret_cast<unsigned char*>(ssm + (size_t)p.rows_cap * p.G);
+    float4* part = reinterpret_cast<float4*>(zsm + (((size_t)p.rows_cap * p.ZS + 15) & ~(size_t)15));
+    int4* utab = reinterpret_cast<int4*>(part + (size_t)p.units_cap * slot4);
+    unsigned char* fifo = reinterpret_cast<unsigned char*>(utab + p.units_cap) + (size_t)warp * p.S * CHUNK;
+    const uint32_t fifo_lane = smem_u32(fifo) + lane * 16;
+
+    // contiguous, balanced range of tiles for this CTA (split computed on the host)
+    const int b = (int)blockIdx.x;
+    const int tile_lo = b * p.tiles_base + min(b, p.tiles_rem);
+    const int ntiles = p.tiles_base + (b < p.tiles_rem ? 1 : 0);
+    const int upt = NACC * p.U;                          // units per tile
+    const int nunits = ntiles * upt;
+    const int NC = p.KS / CG;                            // chunks per unit
+    // this warp's units: warp, warp + UW, ...  -> flat chunk sequence q = 0 .. my_chunks-1
+    const int my_units = nunits > warp ? (nunits - warp + UW - 1) / UW : 0;
+    const int my_chunks = my_units * NC;
+    const size_t row_bytes = (size_t)p.K >> 1;
+    const int rows_half = ntiles * 16;                   // staged rows per gate / up half
+
+    // Unit table: {first weight row, first group, first staged row} of every unit of this
+    // CTA, so that the hot loop never divides.  Entry ul is written by the warp that owns it.
+    for (int ul = warp + lane * UW; ul < nunits; ul += 32 * UW) {
+        const int tl = ul / upt, rem = ul - tl * upt;
+        const int a = rem / p.U, k = rem - a * p.U;
+        utab[ul] = make_int4((tile_lo + tl) * 16 + a * p.up_row_offset, k * p.KS, a * rows_half + tl * 16, 0);
+    }
+    __syncwarp();
+
+    // ---- copy group 0, requested before any weight so that it is served first: x, scattered
+    // 16 bytes at a time to the positions of the mma-fragment order (chunk (t, j) of a group
+    // goes to slot (j, t)), and this CTA's scales and zero-points (contiguous rows per half)
+    {
+        const uint32_t xs_s = smem_u32(xs);
+        for (int m = 0; m < p.M; m++) {
+            const __half* xrow = p.x + (size_t)m * p.K;
+            for (int c = tid; c < p.G * 16; c += UW * 32) {
+                const int grp = c >> 4, cc = c & 15, tt = cc >> 2, j = cc & 3;
+                cp_async16(xs_s + m * p.xstride + grp * 256 + (j * 4 + tt) * 16, xrow + c * 8);
+            }
+        }
+        const int sc16 = rows_half * p.G / 8;            // 16-byte pieces of scales per half
+        const int zp16 = rows_half * p.ZS / 16;
+        for (int a = 0; a < NACC; a++) {
+            const size_t row0 = (size_t)tile_lo * 16 + (size_t)a * p.up_row_offset;
+            const unsigned char* ssrc = reinterpret_cast<const unsigned char*>(p.scales + row0 * p.G);
+            const uint32_t sdst = smem_u32(ssm + (size_t)a * rows_half * p.G);
+            for (int i = tid; i < sc16; i += UW * 32) cp_async16(sdst + i * 16, ssrc + (size_t)i * 16);
+            if (p.zeros) {
+                const unsigned char* zsrc = p.zeros + row0 * p.ZS;
+                const uint32_t zdst = smem_u32(zsm + (size_t)a * rows_half * p.ZS);
+                for (int i = tid; i < zp16; i += UW * 32) cp_async16(zdst + i * 16, zsrc + (size_t)i * 16);
+            }
+        }
+        if (!p.zeros)                                     // symmetric: every zero-point is 8
+            for (int i = tid; i < (NACC * rows_half * p.ZS + 3) / 4; i += UW * 32)
+                reinterpret_cast<uint32_t*>(zsm)[i] = 0x88888888u;
+        cp_async_commit();
+    }
+
+    // A cursor walks this warp's chunks in order: unit index ui (0,1,..), chunk ci inside it.
+    struct Cursor { int ui, ci; };
+    auto advance = [&](Cursor& c) { if (++c.ci == NC) { c.ci = 0; ++c.ui; } };
+    // request one chunk into FIFO slot `slot`: lane (g, t) copies bytes [t*16, +16) of rows g and
+    // g+8 of each group -- piece k of the slot is one 16-byte column of 32 lanes
+    auto issue_chunk = [&](const Cursor& c, int slot) {
+        const int4 u = utab[warp + c.ui * UW];
+        const int gi0 = u.y + c.ci * CG;
+        const unsigned char* pa = p.w + (size_t)(u.x + g) * row_bytes + (size_t)gi0 * 64 + t * 16;
+        const unsigned char* pb = pa + 8 * row_bytes;
+        const uint32_t dst = fifo_lane + slot * CHUNK;
+#pragma unroll
+        for (int k = 0; k < CG; k++) {
+            cp_async16(dst + (2 * k) * 512, pa + k * 64);
+            cp_async16(dst + (2 * k + 1) * 512, pb + k * 64);
+        }
+    };
+
+    // every warp's group-0 requests go out before any warp's weight requests
+    TRACE(10);
+    __syncthreads();
+    TRACE(11);
+    // Start the FIFO with S0 chunks; it ramps up to S inside the loop.  (A warp whose copy
+    // requests exceed what the SM can keep in flight stalls on the request itself, so asking
+    // for everything here would keep every warp from computing until most of it had landed.)
+    // One copy group per chunk: chunk q has landed when at most issued-1-q groups are pending.
+    Cursor cload{0, 0}, ccur{0, 0};
+    int issued = 0, islot = 0;
+    for (int s0 = 0; s0 < p.S0 && issued < my_chunks; s0++) {
+        issue_chunk(cload, islot);
+        cp_async_commit();
+        advance(cload);
+        issued++;
+        if (++islot == p.S) islot = 0;
+    }
+
+    // ---- group 0 has landed: every thread puts the 16-byte pieces of x it copied into
+    // fragment order in place (the same walk as above), and the per-group sums are formed ------
+    for (int i = tid; i < p.G * MPAD; i += UW * 32)
+        if ((i % MPAD) >= p.M) xsum[i] = make_float2(0.f, 0.f);
+    TRACE(12);
+    cp_async_wait(issued);
+    TRACE(13);
+    for (int m = 0; m < p.M; m++) {
+        unsigned char* xdst = xs + (size_t)m * p.xstride;
+        for (int c = tid; c < p.G * 16; c += UW * 32) {
+            const int grp = c >> 4, cc = c & 15, tt = cc >> 2, j = cc & 3;
+            uint4* slot16 = reinterpret_cast<uint4*>(xdst + grp * 256 + (j * 4 + tt) * 16);
+            const uint4 s4 = *slot16;
+            uint4 d;
+            d.x = prmt(s4.x, s4.z, 0x5410);
+            d.y = prmt(s4.x, s4.z, 0x7632);
+            d.z = prmt(s4.y, s4.w, 0x5410);
+            d.w = prmt(s4.y, s4.w, 0x7632);
+            *slot16 = d;
+            const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&s4.x));
+            const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&s4.y));
+            const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&s4.z));
+            const float2 f3 = __half22float2(*reinterpret_cast<const __half2*>(&s4.w));
+            float se = (f0.x + f1.x) + (f2.x + f3.x), so = (f0.y + f1.y) + (f2.y + f3.y);
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) {
+                se += __shfl_xor_sync(0xffffffffu, se, o);
+                so += __shfl_xor_sync(0xffffffffu, so, o);
+            }
+            if (cc == 0) xsum[grp * MPAD + m] = make_float2(se + so, 960.0f * so);
+        }
+    }
+    TRACE(2);
+    __syncthreads();
+    TRACE(3);
+
+    int xm_off[MT];
+    bool xm_live[MT];
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++) {
+        xm_live[mt] = mt * 8 + g < p.M;
+        xm_off[mt] = min(mt * 8 + g, p.M - 1) * p.xstride + t * 16;
+    }
+    float res[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) res[mt][i] = 0.0f;
+
+    int slot = 0;
+    for (int q = 0; q < my_chunks; q++) {
+        cp_async_wait(issued - 1 - q);
+        uint4 wq[2 * CG];
+        {
+            const unsigned char* src = fifo + slot * CHUNK + lane * 16;
+#pragma unroll
+            for (int k = 0; k < 2 * CG; k++) wq[k] = *reinterpret_cast<const uint4*>(src + k * 512);
+        }
+        if (++slot == p.S) slot = 0;
+        // chunk q's slot is free again (this lane has read back everything it copied): request
+        // up to two more chunks while the FIFO has room
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            if (issued < my_chunks && issued - (q + 1) < p.S) {
+                issue_chunk(cload, islot);
+                cp_async_commit();
+                advance(cload);
+                issued++;
+                if (++islot == p.S) islot = 0;
+            }
+        }
+
+        const int4 u4 = utab[warp + ccur.ui * UW];
+        const int gi0 = u4.y + ccur.ci * CG;
+        float acc[CG][MT][4];
+#pragma unroll
+        for (int u = 0; u < CG; u++)
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) acc[u][mt][i] = 0.0f;
+#pragma unroll
+        for (int u = 0; u < CG; u++) {
+            const uint32_t wqa[4] = {wq[2 * u].x, wq[2 * u].y, wq[2 * u].z, wq[2 * u].w};
+            const uint32_t wqb[4] = {wq[2 * u + 1].x, wq[2 * u + 1].y, wq[2 * u + 1].z, wq[2 * u + 1].w};
+            const unsigned char* xg = xs + (gi0 + u) * 256;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                uint32_t va = wqa[j], vb = wqb[j];
+                const uint32_t a0 = lop3_and_or(va, 0x000f000fu, 0x64006400u);   // 1024 + (n0, n4)
+                const uint32_t a1 = lop3_and_or(vb, 0x000f000fu, 0x64006400u);
+                const uint32_t a2 = lop3_and_or(va, 0x00f000f0u, 0x54005400u);   //   64 + (n1, n5)
+                const uint32_t a3 = lop3_and_or(vb, 0x00f000f0u, 0x54005400u);
+                va >>= 8; vb >>= 8;
+                const uint32_t a4 = lop3_and_or(va, 0x000f000fu, 0x64006400u);   // 1024 + (n2, n6)
+                const uint32_t a5 = lop3_and_or(vb, 0x000f000fu, 0x64006400u);
+                const uint32_t a6 = lop3_and_or(va, 0x00f000f0u, 0x54005400u);   //   64 + (n3, n7)
+                const uint32_t a7 = lop3_and_or(vb, 0x00f000f0u, 0x54005400u);
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++) {
+                    uint4 xv = make_uint4(0u, 0u, 0u, 0u);
+                    if (xm_live[mt]) xv = *reinterpret_cast<const uint4*>(xg + xm_off[mt] + j * 64);
+                    mma16816(acc[u][mt], a0, a1, a2, a3, xv.x, xv.y);
+                    mma16816(acc[u][mt], a4, a5, a6, a7, xv.z, xv.w);
+                }
+            }
+        }
+        // scales and zero-points of rows g / g+8 for the CG groups, from the staged copy
+        const int mra = u4.z + g, mrb = mra + 8;
+        float fsa[CG], fsb[CG];
+        uint32_t za, zb;
+        if (CG == 4) {
+            const uint2 sa = *reinterpret_cast<const uint2*>(ssm + (size_t)mra * p.G + gi0);
+            const uint2 sb = *reinterpret_cast<const uint2*>(ssm + (size_t)mrb * p.G + gi0);
+            const float2 a01 = __half22float2(*reinterpret_cast<const __half2*>(&sa.x));
+            const float2 a23 = __half22float2(*reinterpret_cast<const __half2*>(&sa.y));
+            const float2 b01 = __half22float2(*reinterpret_cast<const __half2*>(&sb.x));
+            const float2 b23 = __half22float2(*reinterpret_cast<const __half2*>(&sb.y));
+            fsa[0] = a01.x; fsa[1] = a01.y; fsa[CG - 2] = a23.x; fsa[CG - 1] = a23.y;
+            fsb[0] = b01.x; fsb[1] = b01.y; fsb[CG - 2] = b23.x; fsb[CG - 1] = b23.y;
+            za = *reinterpret_cast<const unsigned short*>(zsm + (size_t)mra * p.ZS + (gi0 >> 1));
+            zb = *reinterpret_cast<const unsigned short*>(zsm + (size_t)mrb * p.ZS + (gi0 >> 1));
+        } else {
+            const float2 a01 = __half22float2(*reinterpret_cast<const __half2*>(ssm + (size_t)mra * p.G + gi0));
+            const float2 b01 = __half22float2(*reinterpret_cast<const __half2*>(ssm + (size_t)mrb * p.G + gi0));
+            fsa[0] = a01.x; fsa[1] = a01.y;
+            fsb[0] = b01.x; fsb[1] = b01.y;
+            za = zsm[(size_t)mra * p.ZS + (gi0 >> 1)];
+            zb = zsm[(size_t)mrb * p.ZS + (gi0 >> 1)];
+        }
+#pragma unroll
+        for (int u = 0; u < CG; u++) {
+            const uint32_t zpa = (za >> (4 * u)) & 0xFu, zpb = (zb >> (4 * u)) & 0xFu;
+            const float ca = -__uint_as_float(0x44800000u | (zpa << 13));       // -(1024 + zp), exact
+            const float cb = -__uint_as_float(0x44800000u | (zpb << 13));
+            if (M1) {
+                // batch 1: only column 0 (accumulators 0 and 2 of lanes t = 0) is live
+                const float2 xq = xsum[(gi0 + u) * MPAD];
+                res[0][0] = fmaf(fsa[u], fmaf(ca, xq.x, acc[u][0][0] + xq.y), res[0][0]);
+                res[0][2] = fmaf(fsb[u], fmaf(cb, xq.x, acc[u][0][2] + xq.y), res[0][2]);
+            } else {
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++) {
+                    const float4 xq = *reinterpret_cast<const float4*>(xsum + (gi0 + u) * MPAD + mt * 8 + 2 * t);
+                    res[mt][0] = fmaf(fsa[u], fmaf(ca, xq.x, acc[u][mt][0] + xq.y), res[mt][0]);
+                    res[mt][1] = fmaf(fsa[u], fmaf(ca, xq.z, acc[u][mt][1] + xq.w), res[mt][1]);
+                    res[mt][2] = fmaf(fsb[u], fmaf(cb, xq.x, acc[u][mt][2] + xq.y), res[mt][2]);
+                    res[mt][3] = fmaf(fsb[u], fmaf(cb, xq.z, acc[u][mt][3] + xq.w), res[mt][3]);
+                }
+            }
+        }
+        // end of a unit: drop its partial sums into its slot
+        if (ccur.ci == NC - 1) {
+            const int ul = warp + ccur.ui * UW;
+            if (t < p.tmax) {
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++)
+                    part[(size_t)ul * slot4 + mt * 8 * p.tmax + g * p.tmax + t] =
+                        make_float4(res[mt][0], res[mt][1], res[mt][2], res[mt][3]);
+            }
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) res[mt][i] = 0.0f;
+        }
+        advance(ccur);
+        TRACE(5);
+    }
+
+    // ---- every unit of the CTA is done: add the U partials of each output -------------------
+    TRACE(7);
+    __syncthreads();
+    const int nout = ntiles * 16 * MPAD;                     // (tile, row, batch column)
+    for (int o = tid; o < nout; o += UW * 32) {
+        const int m = o % MPAD, r = (o / MPAD) & 15, tl = o / (16 * MPAD);
+        if (m >= p.M) continue;
+        const int mt = m >> 3, tt = (m & 7) >> 1;
+        const int comp = ((r >> 3) << 1) | (m & 1);           // float4 component: row half, column parity
+        const int lane_slot = mt * 8 * p.tmax + (r & 7) * p.tmax + tt;
+        float sum[NACC];
+#pragma unroll
+        for (int a = 0; a < NACC; a++) {
+            const float* v0 = reinterpret_cast<const float*>(part + (size_t)((tl * NACC + a) * p.U) * slot4 + lane_slot) + comp;
+            float acc1 = 0.0f;
+            for (int k = 0; k < p.U; k++) acc1 += v0[(size_t)k * slot4 * 4];         // fixed order: deterministic
+            sum[a] = acc1;
+        }
+        const float out = SWIGLU ? silu_f32(sum[0]) * sum[NACC - 1] : sum[0];
+        p.y[(size_t)m * p.Nout + (tile_lo + tl) * 16 + r] = __float2half_rn(out);
+    }
+    TRACE(9);
+}
+
+// ---- block-fixed-point variant, batch MM = 1 or 2 ------------------------------------------------
+// Here the FIFOs are filled by TMA instead of cp.async: per-lane copies stall the REQUESTING warp
+// once the SM's load queue is full, which kept the compute warps from computing while the
+// memory pipe was busy.  One elected lane per warp asks for a whole chunk (one 3-D box:
+// 128 bytes x 16 rows x CG/2 lines, 128-byte swizzle) that completes on a per-slot mbarrier
+// of its own warp; nothing is shared between warps.  Every barrier wait is bounded; a wait that
+// gives up sets a flag, every warp leaves its loop, and the status word reports it.
+//
+// Shared memory: [FIFOs: UW x S x CG KB, 1024-byte aligned]
+// [xq: G x (3 planes x MM) x 128 signed bytes, each 128 in B-fragment order]
+// [xmeta: G x 8 columns x {coef, digit sum}; column = plane (MM = 1) or 2 plane + m (MM = 2)]
+// [scales][zero-points][partials: units_cap x 16 rows x MM float][unit table][barriers][flag]
+//
+// B-fragment order of one (group, plane, batch row): lane column t' = k >> 5 owns 32 bytes; inside,
+// byte ((h*2 + jp)*2 + b)*4 + i holds k = 32t' + 16jp + 8b + 2i + h.  With the weights of lane
+// (g, t) being words j = 0..3 = nibbles k = 32t + 8j + (0..7) of its two rows, the mma for
+// (parity h, word pair jp) takes a0/a1 = word 2jp of the two rows masked to parity h, a2/a3 =
+// word 2jp+1, and b0/b1 = bytes [(h*2+jp)*8, +8) of the lane's 32.
+//
+// Fragment row g reads tile row rho(g) = (g >> 1) | ((g & 1) << 2) (and rho(g) + 8): with the
+// swizzle keyed by row % 8, a quarter-warp's two rows then land in different bank groups.
+constexpr uint32_t WAIT_LIMIT = 1u << 15;      // one try_wait may suspend for microseconds: ~0.1 s in all
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+    for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if ((it & 31u) == 31u && *abort_flag) return false;
+    }
+    *abort_flag = 1u;
+    return false;
+}
+// lane 0 polls, the outcome is broadcast; must be called by a converged warp
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, int lane) {
+    bool ok = true;
+    if (lane == 0) ok = mbar_wait(bar, parity, abort_flag);
+    __syncwarp();
+    return __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar,
+                                            uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%2, %3, %4}], [%5], %6;"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar), "l"(policy) : "memory");
+}
+__device__ __forceinline__ int rho(int g) { return (g >> 1) | ((g & 1) << 2); }
+
+template <int MM, bool SWIGLU, int CG>
+__global__ void __launch_bounds__(UW * 32, 1)
+lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const UnitsParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    // 1024-byte alignment by OFFSET from the __shared__ symbol (keeps 32-bit shared addressing)
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    constexpr int NACC = SWIGLU ? 2 : 1;
+    constexpr int CHUNK = CG * 1024;
+    constexpr int XG = 3 * MM * 128;                    // bytes of xq per group
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    TRACE_DECL;
+    TRACE(1);
+
+    unsigned char* fifo = smem + (size_t)warp * p.S * CHUNK;
+    unsigned char* xq = smem + (size_t)UW * p.S * CHUNK;
+    float4* xmeta = reinterpret_cast<float4*>(xq + (size_t)p.G * XG);
+    __half* ssm = reinterpret_cast<__half*>(xmeta + (size_t)p.G * 4);
+    unsigned char* zsm = reinterpret_cast<unsigned char*>(ssm + (size_t)p.rows_cap * p.G);
+    float* part = reinterpret_cast<float*>(zsm + (((size_t)p.rows_cap * p.ZS + 15) & ~(size_t)15));
+    int4* utab = reinterpret_cast<int4*>(part + (size_t)p.units_cap * 16 * MM);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(utab + p.units_cap);
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + UW * MAX_STAGES);
+    const uint32_t bar0 = smem_u32(bars + warp * MAX_STAGES);          // this warp's barriers
+
+    const int b = (int)blockIdx.x;
+    const int tile_lo = b * p.tiles_base + min(b, p.tiles_rem);
+    const int ntiles = p.tiles_base + (b < p.tiles_rem ? 1 : 0);
+    const int upt = NACC * p.U;
+    const int nunits = ntiles * upt;
+    const int NC = p.KS / CG;
+    const int my_units = nunits > warp ? (nunits - warp + UW - 1) / UW : 0;
+    const int my_chunks = my_units * NC;
+    const int rows_half = ntiles * 16;
+
+    // the first 16 bytes of x this thread converts: requested before anything else
+    const int npieces = p.M * p.G * 16;                  // 16-byte pieces of x, (m, group, 16th)
+    uint4 x_first = make_uint4(0u, 0u, 0u, 0u);
+    if (tid < npieces) x_first = __ldg(reinterpret_cast<const uint4*>(p.x) + tid);
+
+    // ---- this CTA's scales and zero-points (one cp.async group), requested before the weights:
+    // small copies queued behind the weight stream would arrive microseconds later ------------
+    {
+        const int sc16 = rows_half * p.G / 8;
+        const int zp16 = rows_half * p.ZS / 16;
+        for (int a = 0; a < NACC; a++) {
+            const size_t row0 = (size_t)tile_lo * 16 + (size_t)a * p.up_row_offset;
+            const unsigned char* ssrc = reinterpret_cast<const unsigned char*>(p.scales + row0 * p.G);
+            const uint32_t sdst = smem_u32(ssm + (size_t)a * rows_half * p.G);
+            for (int i = tid; i < sc16; i += UW * 32) cp_async16(sdst + i * 16, ssrc + (size_t)i * 16);
+            if (p.zeros) {
+                const unsigned char* zsrc = p.zeros + row0 * p.ZS;
+                const uint32_t zdst = smem_u32(zsm + (size_t)a * rows_half * p.ZS);
+                for (int i = tid; i < zp16; i += UW * 32) cp_async16(zdst + i * 16, zsrc + (size_t)i * 16);
+            }
+        }
+        cp_async_commit();
+    }
+
+    if (lane == 0) {
+        if (warp == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+            *abort_flag = 0u;
+        }
+        for (int s0 = 0; s0 < p.S; s0++) mbar_init(bar0 + 8u * (uint32_t)s0, 1u);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    for (int ul = warp + lane * UW; ul < nunits; ul += 32 * UW) {
+        const int tl = ul / upt, rem = ul - tl * upt;
+        const int a = rem / p.U, k = rem - a * p.U;
+        utab[ul] = make_int4((tile_lo + tl) * 16 + a * p.up_row_offset, k * p.KS, a * rows_half + tl * 16, 0);
+    }
+    __syncwarp();
+
+    // A cursor walks this warp's chunks in order: unit index ui (0, 1, ..), chunk ci inside it.
+    struct Cursor { int ui, ci; };
+    auto advance = [&](Cursor& c) { if (++c.ci == NC) { c.ci = 0; ++c.ui; } };
+    Cursor cload{0, 0}, ccur{0, 0};
+    int issued = 0;
+    uint64_t policy = 0;
+    if (lane == 0) asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    // lane 0 only: ask for the next chunk into FIFO slot `slot` (the slot's barrier is armed first)
+    auto issue_chunk = [&](int slot) {
+        const int4 u = utab[warp + cload.ui * UW];
+        const uint32_t bar = bar0 + 8u * (uint32_t)slot;
+        mbar_expect_tx(bar, (uint32_t)CHUNK);
+        tma_load_3d(smem_u32(fifo + (size_t)slot * CHUNK), &map_w, 0, u.x, (u.y + cload.ci * CG) >> 1, bar, policy);
+        advance(cload);
+        issued++;
+    };
+    // the first chunk now; the rest of the FIFO once x is converted (see below)
+    if (lane == 0 && my_chunks > 0) issue_chunk(0);
+    TRACE(10);
+
+    if (!p.zeros)                                         // symmetric: every zero-point is 8
+        for (int i = tid; i < (NACC * rows_half * p.ZS + 3) / 4; i += UW * 32)
+            reinterpret_cast<uint32_t*>(zsm)[i] = 0x88888888u;
+    // D columns without a plane behind them get coefficient 0 (their accumulators hold garbage);
+    // columns with one are written below by other threads, hence the barrier
+    for (int i = tid; i < p.G * 4; i += UW * 32) xmeta[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    __syncthreads();
+    TRACE(11);
+
+    // ---- x -> block fixed point, three signed byte planes in B-fragment order -----------------
+    for (int c = tid; c < npieces; c += UW * 32) {
+        const uint4 s4 = c == tid ? x_first : __ldg(reinterpret_cast<const uint4*>(p.x) + c);
+        const int m = c / (p.G * 16), cg16 = c - m * p.G * 16;
+        const int grp = cg16 >> 4, l16 = cg16 & 15;
+        float v[8];
+        {
+            const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&s4.x));
+            const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&s4.y));
+            const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&s4.z));
+            const float2 f3 = __half22float2(*reinterpret_cast<const __half2*>(&s4.w));
+            v[0] = f0.x; v[1] = f0.y; v[2] = f1.x; v[3] = f1.y; v[4] = f2.x; v[5] = f2.y; v[6] = f3.x; v[7] = f3.y;
+        }
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
+        // an f16 is inf / NaN exactly when its exponent field is all ones (NaN does not survive fmaxf)
+        unsigned bad = 0;
+        {
+            const uint32_t w4[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+                bad |= (unsigned)((w4[i] & 0x7C00u) == 0x7C00u) | (unsigned)((w4[i] & 0x7C000000u) == 0x7C000000u);
+        }
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) {
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            bad |= __shfl_xor_sync(0xffffffffu, bad, o);
+        }
+        // amax = f * 2^E with f in [0.5, 1): biased exponent eb = E + 126.  x * 2^(22-E) is exact.
+        const unsigned eb = __float_as_uint(amax) >> 23;
+        const float up = (amax > 0.0f && !bad) ? __uint_as_float((275u - eb) << 23) : 0.0f;   // 2^(22-E)
+        float down = amax > 0.0f ? __uint_as_float((eb - 21u) << 23) : 0.0f;                 // 2^(E-22)
+        if (bad) down = __uint_as_float(0x7FC00000u);    // inf / NaN in the group: the outputs are NaN
+        // X + 0x808080 has bytes d0+128, d1+128, d2+128 (X = d0 + 256 d1 + 65536 d2, digits in
+        // [-128, 127]); flipping the top bit of each turns them into the digits as signed bytes
+        uint32_t e[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) e[i] = (uint32_t)(__float2int_rn(v[i] * up) + 0x808080) ^ 0x808080u;
+        // byte transpose: word h of plane pl holds the digits of k = 2i + h, i = 0..3
+        uint32_t pw[3][2];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const uint32_t a01 = prmt(e[h], e[2 + h], 0x5140), a23 = prmt(e[4 + h], e[6 + h], 0x5140);
+            const uint32_t c01 = prmt(e[h], e[2 + h], 0x0062), c23 = prmt(e[4 + h], e[6 + h], 0x0062);
+            pw[0][h] = prmt(a01, a23, 0x5410);
+            pw[1][h] = prmt(a01, a23, 0x7632);
+            pw[2][h] = prmt(c01, c23, 0x5410);
+        }
+        // this thread's 8 k are 32t' + 16jp + 8b + (2i + h)
+        const int tq = l16 >> 2, jp = (l16 >> 1) & 1, bb = l16 & 1;
+#pragma unroll
+        for (int pl = 0; pl < 3; pl++) {
+            int dsum = __dp4a((int)pw[pl][0], 0x01010101, __dp4a((int)pw[pl][1], 0x01010101, 0));
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) dsum += __shfl_xor_sync(0xffffffffu, dsum, o);
+            unsigned char* dst = xq + (size_t)grp * XG + (pl * MM + m) * 128 + tq * 32;
+            *reinterpret_cast<uint32_t*>(dst + ((0 * 2 + jp) * 2 + bb) * 4) = pw[pl][0];
+            *reinterpret_cast<uint32_t*>(dst + ((1 * 2 + jp) * 2 + bb) * 4) = pw[pl][1];
+            if (l16 == 0) {
+                // lane t reads one float4 = {coef, digit sum} of its columns 2t and 2t+1
+                float* xm = reinterpret_cast<float*>(xmeta + grp * 4) + (MM == 1 ? 2 * pl : 4 * pl + 2 * m);
+                xm[0] = down * (pl == 0 ? 1.0f : pl == 1 ? 256.0f : 65536.0f);
+                xm[1] = __int_as_float(dsum);
+            }
+        }
+    }
+    TRACE(12);
+    // fill the rest of the FIFO (the async engine queues the requests: nothing stalls here)
+    if (lane == 0)
+        for (int s0 = 1; s0 < p.S && issued < my_chunks; s0++) issue_chunk(s0);
+    cp_async_wait(0);                                    // the scales and zero-points have landed
+    TRACE(2);
+    __syncthreads();
+    TRACE(3);
+
+    // lanes of column g >= 3*MM multiply garbage that nobody reads: point them at a valid column
+    const int col = min(g, 3 * MM - 1);
+    const int xcol_off = col * 128 + t * 32;
+    const int rg = rho(g);                               // tile row behind fragment row g
+    float res[2][2];                                     // [row half][column 2t / 2t+1 of the lane]
+    res[0][0] = res[0][1] = res[1][0] = res[1][1] = 0.0f;
+    constexpr int MAGIC = 0x4B400000;                    // float 1.5 * 2^23: MAGIC + i reads as 12582912 + i
+
+    int slot = 0;
+    uint32_t ph = 0;
+    bool ok = true;
+    for (int q = 0; q < my_chunks; q++) {
+        ok = warp_wait(bar0 + 8u * (uint32_t)slot, ph, abort_flag, lane);
+        if (!ok) break;
+        TRACE(4);
+        uint4 wq[2 * CG];
+        {
+            const unsigned char* st = fifo + (size_t)slot * CHUNK + rg * 128;
+#pragma unroll
+            for (int u = 0; u < CG; u++) {
+                // line u/2, rows rg and rg+8, logical 16-byte piece (u%2)*4 + t, swizzled by row%8
+                const unsigned char* ln = st + (u >> 1) * 2048 + (((((u & 1) << 2) | t) ^ rg) << 4);
+                wq[2 * u] = *reinterpret_cast<const uint4*>(ln);
+                wq[2 * u + 1] = *reinterpret_cast<const uint4*>(ln + 1024);
+            }
+        }
+        // every lane has read the slot: hand it back to the async engine for the next chunk
+        __syncwarp();
+        if (lane == 0 && issued < my_chunks) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            issue_chunk(slot);
+        }
+        if (++slot == p.S) { slot = 0; ph ^= 1u; }
+
+        const int4 u4 = utab[warp + ccur.ui * UW];
+        const int gi0 = u4.y + ccur.ci * CG;
+        const int mra = u4.z + rg, mrb = mra + 8;
+        float fsa[CG], fsb[CG];
+        uint32_t za, zb;
+        if (CG == 4) {
+            const uint2 sa = *reinterpret_cast<const uint2*>(ssm + (size_t)mra * p.G + gi0);
+            const uint2 sb = *reinterpret_cast<const uint2*>(ssm + (size_t)mrb * p.G + gi0);
+            const float2 a01 = __half22float2(*reinterpret_cast<const __half2*>(&sa.x));
+            const float2 a23 = __half22float2(*reinterpret_cast<const __half2*>(&sa.y));
+            const float2 b01 = __half22float2(*reinterpret_cast<const __half2*>(&sb.x));
+            const float2 b23 = __half22float2(*reinterpret_cast<const __half2*>(&sb.y));
+            fsa[0] = a01.x; fsa[1] = a01.y; fsa[CG - 2] = a23.x; fsa[CG - 1] = a23.y;
+            fsb[0] = b01.x; fsb[1] = b01.y; fsb[CG - 2] = b23.x; fsb[CG - 1] = b23.y;
+            za = *reinterpret_cast<const unsigned short*>(zsm + (size_t)mra * p.ZS + (gi0 >> 1));
+            zb = *reinterpret_cast<const unsigned short*>(zsm + (size_t)mrb * p.ZS + (gi0 >> 1));
+        } else {
+            const float2 a01 = __half22float2(*reinterpret_cast<const __half2*>(ssm + (size_t)mra * p.G + gi0));
+            const float2 b01 = __half22float2(*reinterpret_cast<const __half2*>(ssm + (size_t)mrb * p.G + gi0));
+            fsa[0] = a01.x; fsa[1] = a01.y;
+            fsb[0] = b01.x; fsb[1] = b01.y;
+            za = zsm[(size_t)mra * p.ZS + (gi0 >> 1)];
+            zb = zsm[(size_t)mrb * p.ZS + (gi0 >> 1)];
+        }
+#pragma unroll
+        for (int u = 0; u < CG; u++) {
+            TRACE(20 + u);
+            const uint4 qa = wq[2 * u], qb = wq[2 * u + 1];
+            const unsigned char* xg = xq + (size_t)(gi0 + u) * XG + xcol_off;
+            const uint4 xlo = *reinterpret_cast<const uint4*>(xg);          // even k: word pairs 0, 1
+            const uint4 xhi = *reinterpret_cast<const uint4*>(xg + 16);     // odd k
+            // the accumulators start at MAGIC, so that they can be read as floats afterwards
+            int lo[4] = {MAGIC, MAGIC, MAGIC, MAGIC}, hi[4] = {MAGIC, MAGIC, MAGIC, MAGIC};
+            constexpr uint32_t ML = 0x0f0f0f0fu, MH = 0xf0f0f0f0u;
+            mma16832_u8s8(lo, qa.x & ML, qb.x & ML, qa.y & ML, qb.y & ML, xlo.x, xlo.y);
+            mma16832_u8s8(hi, qa.x & MH, qb.x & MH, qa.y & MH, qb.y & MH, xhi.x, xhi.y);
+            mma16832_u8s8(lo, qa.z & ML, qb.z & ML, qa.w & ML, qb.w & ML, xlo.z, xlo.w);
+            mma16832_u8s8(hi, qa.z & MH, qb.z & MH, qa.w & MH, qb.w & MH, xhi.z, xhi.w);
+            // columns 2t, 2t+1 of this lane: coefficient 2^(E-22) 256^plane and digit sum
+            const float4 xm = xmeta[(gi0 + u) * 4 + t];
+            const int zpa = (int)((za >> (4 * u)) & 0xFu), zpb = (int)((zb >> (4 * u)) & 0xFu);
+            // integer sum (n - zp) X = lo + hi/16 - zp * digit-sum, converted exactly through
+            // 1.5 * 2^23 + i (|i| < 2^22); hi is a multiple of 16 and 12582912 * 17/16 = 13369344
+            float v[2][2];                               // [row half][column]
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                const int ds = __float_as_int(j ? xm.w : xm.y);
+                v[0][j] = fmaf(__int_as_float(hi[j]), 0.0625f, __int_as_float(lo[j] - zpa * ds)) - 13369344.0f;
+                v[1][j] = fmaf(__int_as_float(hi[2 + j]), 0.0625f, __int_as_float(lo[2 + j] - zpb * ds)) - 13369344.0f;
+            }
+            if (MM == 1) {
+                // both columns are planes of batch row 0: combine them before the scale
+                res[0][0] = fmaf(fsa[u], fmaf(xm.z, v[0][1], xm.x * v[0][0]), res[0][0]);
+                res[1][0] = fmaf(fsb[u], fmaf(xm.z, v[1][1], xm.x * v[1][0]), res[1][0]);
+            } else {
+                res[0][0] = fmaf(fsa[u] * xm.x, v[0][0], res[0][0]);
+                res[0][1] = fmaf(fsa[u] * xm.z, v[0][1], res[0][1]);
+                res[1][0] = fmaf(fsb[u] * xm.x, v[1][0], res[1][0]);
+                res[1][1] = fmaf(fsb[u] * xm.z, v[1][1], res[1][1]);
+            }
+        }
+        // end of a unit: add the planes (lanes t) and drop the partial sums into the unit's slot
+        if (ccur.ci == NC - 1) {
+            const int ul = warp + ccur.ui * UW;
+#pragma unroll
+            for (int h = 0; h < 2; h++)
+#pragma unroll
+                for (int m = 0; m < MM; m++) {
+                    res[h][m] += __shfl_xor_sync(0xffffffffu, res[h][m], 1);
+                    res[h][m] += __shfl_xor_sync(0xffffffffu, res[h][m], 2);
+                }
+            if (t == 0) {
+#pragma unroll
+                for (int m = 0; m < MM; m++) {
+                    part[((size_t)ul * 16 + rg) * MM + m] = res[0][m];
+                    part[((size_t)ul * 16 + rg + 8) * MM + m] = res[1][m];
+                }
+            }
+            res[0][0] = res[0][1] = res[1][0] = res[1][1] = 0.0f;
+        }
+        advance(ccur);
+        TRACE(5);
+    }
+
+    TRACE(7);
+    __syncthreads();
+    if (*abort_flag) {
+        // A bounded wait gave up: report it and give copies still in flight time to land in
+        // this CTA's shared memory before it is released.
+        if (tid == 0 && p.status) atomicOr(p.status, 0x7C050003u);
+        for (int i = 0; i < 64; i++) __nanosleep(1000);
+        __syncthreads();
+        return;
+    }
+    const int nout = ntiles * 16 * MM;
+    for (int o = tid; o < nout; o += UW * 32) {
+        const int m = o % MM, r = (o / MM) & 15, tl = o / (16 * MM);
+        float sum[NACC];
+#pragma unroll
+        for (int a = 0; a < NACC; a++) {
+            const float* v0 = part + ((size_t)((tl * NACC + a) * p.U) * 16 + r) * MM + m;
+            float acc1 = 0.0f;
+            for (int k = 0; k < p.U; k++) acc1 += v0[(size_t)k * 16 * MM];        // fixed order: deterministic
+            sum[a] = acc1;
+        }
+        const float out = SWIGLU ? silu_f32(sum[0]) * sum[NACC - 1] : sum[0];
+        p.y[(size_t)m * p.Nout + (tile_lo + tl) * 16 + r] = __float2half_rn(out);
+    }
+    TRACE(9);
+}
+
+template <int MT, bool SW, bool M1, int CG>
+cudaError_t launch_units_inst(const UnitsParams& p, int grid, size_t smem, cudaStream_t st) {
+    auto kfn = lux_qgemv_i4_g128_units<MT, SW, M1, CG>;
+    static std::atomic<size_t> configured[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (smem > 48 * 1024 && smem > configured[dev & 63].load(std::memory_order_relaxed)) {
+        cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        configured[dev & 63].store(smem, std::memory_order_relaxed);
+    }
+    kfn<<<grid, UW * 32, smem, st>>>(p);
+    return cudaGetLastError();
+}
+
+template <int MM, bool SW, int CG>
+cudaError_t launch_units_fx_inst(const CUtensorMap& map, const UnitsParams& p, int grid, size_t smem, cudaStream_t st) {
+    auto kfn = lux_qgemv_i4_g128_units_fx<MM, SW, CG>;
+    static std::atomic<size_t> configured[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (smem > 48 * 1024 && smem > configured[dev & 63].load(std::memory_order_relaxed)) {
+        cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        configured[dev & 63].store(smem, std::memory_order_relaxed);
+    }
+    kfn<<<grid, UW * 32, smem, st>>>(map, p);
+    return cudaGetLastError();
+}
+
+template <int MM, bool SW>
+cudaError_t launch_units_fx_cg(int cg, const CUtensorMap& map, const UnitsParams& p, int grid, size_t smem, cudaStream_t st) {
+    return cg == 4 ? launch_units_fx_inst<MM, SW, 4>(map, p, grid, smem, st)
+                   : launch_units_fx_inst<MM, SW, 2>(map, p, grid, smem, st);
+}
+
+template <int MT, bool SW, bool M1>
+cudaError_t launch_units_cg(int cg, const UnitsParams& p, int grid, size_t smem, cudaStream_t st) {
+    return cg == 4 ? launch_units_inst<MT, SW, M1, 4>(p, grid, smem, st)
+                   : launch_units_inst<MT, SW, M1, 2>(p, grid, smem, st);
+}
+
+}  // namespace
+
+// Returns NOT_SUPPORTED when the shape does not suit this kernel (the caller then uses one of
+// the other int4 kernels): batch above 16, an odd number of groups, an output size that is
+// not a multiple of the 16-row tile, a zero-point row that is not a whole number of 16-byte
+// pieces per tile, or activations / scale tables too large to stage in shared memory next
+// to at least two chunks of FIFO per warp.
+LuxBackendError launch_qgemv_i4_units(Context* ctx, const QArgs& a) {
+    const int nout = a.swiglu ? a.N / 2 : a.N;
+    if (a.M < 1 || a.M > 16 || a.G < 2 || (a.G & 1) || nout % 16) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+    const int MT = a.M <= 8 ? 1 : 2;
+    const int nacc = a.swiglu ? 2 : 1;
+    const int tiles = nout / 16;
+    const int grid = std::min(ctx->sm_count, tiles);
+    const int tiles_per_cta = (tiles + grid - 1) / grid;
+
+    // Chunk size: 4 groups when the group count allows, else 2.  Unit size KS (a multiple of
+    // the chunk, dividing G): the one that spreads the busiest CTA's groups most evenly over
+    // its 16 warps, each unit costing about a quarter of a group of overhead.
+    int cg = g_tune.gemv_units_cg == 2 || g_tune.gemv_units_cg == 4 ? g_tune.gemv_units_cg : ((a.G & 3) ? 2 : 4);
+    if (a.G % cg) cg = 2;
+    int KS = 0;
+    if (g_tune.gemv_units_ks > 0 && a.G % g_tune.gemv_units_ks == 0 && g_tune.gemv_units_ks % cg == 0) {
+        KS = g_tune.gemv_units_ks;
+    } else {
+        double best = 1e30;
+        for (int ks = cg; ks <= std::min(a.G, 32); ks += cg) {
+            if (a.G % ks) continue;
+            const int units = tiles_per_cta * nacc * (a.G / ks);
+            const double cost = (double)((units + UW - 1) / UW) * (ks + 0.25);
+            if (cost < best - 1e-9) { best = cost; KS = ks; }
+        }
+    }
+    if (KS == 0) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+    const int U = a.G / KS;
+
+    UnitsParams p{};
+    p.x = (const __half*)a.x;
+    p.w = a.w;
+    p.scales = (const __half*)a.scales;
+    p.zeros = a.zeros;
+    p.y = (__half*)a.y;
+    p.M = a.M;
+    p.K = a.K;
+    p.G = a.G;
+    p.ZS = (a.G + 1) / 2;
+    p.Nout = nout;
+    p.up_row_offset = a.swiglu ? nout : 0;
+    p.U = U;
+    p.KS = KS;
+    p.xstride = a.G * 256 + 64;
+    p.tmax = (std::min(a.M, 8) + 1) / 2;
+    p.tiles_base = tiles / grid;
+    p.tiles_rem = tiles % grid;
+    p.units_cap = tiles_per_cta * nacc * U;
+    p.rows_cap = tiles_per_cta * 16 * nacc;
+    // the staged tables are copied in 16-byte pieces per (CTA, gate/up half): 16 rows of scales
+    // are 32*G bytes (always whole pieces); 16 rows of zero-points are 16*ZS bytes (always whole);
+    // the sources must be 16-byte aligned
+    if ((reinterpret_cast<uintptr_t>(a.scales) & 15) || (a.zeros && (reinterpret_cast<uintptr_t>(a.zeros) & 15)) ||
+        (reinterpret_cast<uintptr_t>(a.w) & 15) || (reinterpret_cast<uintptr_t>(a.x) & 15))
+        return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+    if (a.swiglu && (((size_t)nout * a.G * 2) & 15)) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+
+    // batch 1 and 2 use the block-fixed-point variant unless the tunable says otherwise
+    const bool fx = a.M <= 2 && g_tune.gemv_units_fx != 2;
+    const size_t x_bytes = fx ? (size_t)a.G * 3 * a.M * 128 + (size_t)a.G * 4 * sizeof(float4)
+                              : (size_t)a.M * p.xstride + (size_t)a.G * 8 * MT * sizeof(float2);
+    const size_t meta_bytes = (size_t)p.rows_cap * a.G * 2 + (((size_t)p.rows_cap * p.ZS + 15) & ~(size_t)15);
+    const size_t part_bytes = fx ? (size_t)p.units_cap * 16 * a.M * sizeof(float)
+                                 : (size_t)p.units_cap * MT * 8 * p.tmax * sizeof(float4);
+    // the fixed-point variant also holds its barriers and flag, and 1024 bytes of alignment slack
+    const size_t fixed = x_bytes + meta_bytes + part_bytes + (size_t)p.units_cap * sizeof(int4) +
+                         (fx ? (size_t)UW * MAX_STAGES * 8 + 16 + 1024 : 0);
+    const size_t budget = 227 * 1024;
+    const size_t chunk = (size_t)cg * 1024;
+    if (fixed + 2 * UW * chunk > budget) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+    const int max_chunks = (p.units_cap + UW - 1) / UW * (KS / cg);       // per warp
+    int S = (int)std::min<size_t>((budget - fixed) / (UW * chunk), MAX_STAGES);
+    S = std::min(S, std::max(max_chunks, 1));
+    if (g_tune.gemv_units_stages > 0) S = std::min(S, g_tune.gemv_units_stages);
+    p.S = std::max(S, 1);
+    p.S0 = std::min(p.S, g_tune.gemv_units_pre > 0 ? g_tune.gemv_units_pre : 1);
+    p.status = ctx->d_status;
+    const size_t smem = fixed + (size_t)p.S * UW * chunk;
+
+    cudaError_t e;
+    if (fx) {
+        // packed weights as a 3-D tensor {128 bytes, N rows, K/256 lines}; a chunk is one box
+        // {128, 16, cg/2}, 128-byte swizzle keyed by the row
+        alignas(64) CUtensorMap map;
+        const uint64_t dims[3] = {128, (uint64_t)a.N, (uint64_t)a.K / 256};
+        const uint64_t strides[2] = {(uint64_t)a.K / 2, 128};
+        const uint32_t box[3] = {128, 16, (uint32_t)cg / 2};
+        if (!encode_tensor_map_u8(&map, 3, a.w, dims, strides, box, true)) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+        if (a.M == 1)
+            e = a.swiglu ? launch_units_fx_cg<1, true>(cg, map, p, grid, smem, ctx->stream)
+                         : launch_units_fx_cg<1, false>(cg, map, p, grid, smem, ctx->stream);
+        else
+            e = a.swiglu ? launch_units_fx_cg<2, true>(cg, map, p, grid, smem, ctx->stream)
+                         : launch_units_fx_cg<2, false>(cg, map, p, grid, smem, ctx->stream);
+    } else if (a.M == 1) {
+        e = a.swiglu ? launch_units_cg<1, true, true>(cg, p, grid, smem, ctx->stream)
+                     : launch_units_cg<1, false, true>(cg, p, grid, smem, ctx->stream);
+    } else if (a.swiglu) {
+        e = MT == 1 ? launch_units_cg<1, true, false>(cg, p, grid, smem, ctx->stream)
+                    : launch_units_cg<2, true, false>(cg, p, grid, smem, ctx->stream);
+    } else {
+        e = MT == 1 ? launch_units_cg<1, false, false>(cg, p, grid, smem, ctx->stream)
+                    : launch_units_cg<2, false, false>(cg, p, grid, smem, ctx->stream);
+    }
+    count_launch();
+    return map_cuda(e, "lux_qgemv_i4_g128_units");
+}
+
+#ifdef LUX_STREAM_TRACE
+extern "C" __attribute__((visibility("default"))) int lux_cuda_debug_units_trace(unsigned long long* out, int n) {
+    return (int)cudaMemcpyFromSymbol(out, g_units_trace, sizeof(unsigned long long) * (size_t)n);
+}
+#endif
+
+const void* kernel_addr_qgemv_i4_units() { return (const void*)lux_qgemv_i4_g128_units<1, false, false, 4>; }
+const void* kernel_addr_qgemv_i4_units_fx() { return (const void*)lux_qgemv_i4_g128_units_fx<1, false, 4>; }
+
+}  // namespace luxcuda

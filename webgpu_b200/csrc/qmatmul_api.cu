@@ -83,6 +83,12 @@ LuxBackendError dispatch(Context* ctx, const Checked& c) {
             // the register-staged kernel wins for batch 1..3 on small layers and covers every
             // shape the ring kernel does not take.
             const QArgs& a = c.a;
+            // Batch 1 and 2: the warp-autonomous kernel in its fixed-point variant is the fastest
+            // wherever its shared-memory plan fits.
+            if (g_tune.gemv_i4_kernel == 3 || (g_tune.gemv_i4_kernel == 0 && a.M <= 2)) {
+                LuxBackendError e = launch_qgemv_i4_units(ctx, a);
+                if (e != LUX_BACKEND_ERROR_NOT_SUPPORTED || g_tune.gemv_i4_kernel == 3) return e;
+            }
             const size_t wbytes = (size_t)a.N * a.K / 2;
             const bool prefer_ring = a.M >= 4 || a.K >= 8192 || wbytes >= ((size_t)40 << 20);
             if (g_tune.gemv_i4_kernel == 2 || (g_tune.gemv_i4_kernel == 0 && prefer_ring)) {
@@ -257,6 +263,7 @@ LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_tune_set(const char* key, int val
         {"gemv_i8_warps", &g_tune.gemv_i8_warps},   {"gemm_tc_bn", &g_tune.gemm_tc_bn},
         {"gemv_i4_kernel", &g_tune.gemv_i4_kernel}, {"gemv_stream_cg", &g_tune.gemv_stream_cg},
         {"gemv_stream_stages", &g_tune.gemv_stream_stages}, {"gemv_stream_warps", &g_tune.gemv_stream_warps},
+        {"gemv_units_ks", &g_tune.gemv_units_ks}, {"gemv_units_stages", &g_tune.gemv_units_stages}, {"gemv_units_cg", &g_tune.gemv_units_cg}, {"gemv_units_pre", &g_tune.gemv_units_pre}, {"gemv_units_fx", &g_tune.gemv_units_fx},
         {"gemm_tc_stages", &g_tune.gemm_tc_stages}, {"gemm_tc_splitk", &g_tune.gemm_tc_splitk},
     };
     for (auto& t : table)
