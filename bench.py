@@ -38,9 +38,13 @@ if ROOT not in sys.path:
 import numpy as np  # noqa: E402
 
 L2_BYTES = 126 * 1024 * 1024
-# dram__bytes_read.sum + dram__bytes_write.sum of one config-2 GEMV launch, from the ncu
-# captures summarised in profiles/qskinny_i4_g128_config2.md (30.546 MB read, 0 written)
-NCU_TRAFFIC_CONFIG2 = 30546432
+# dram__bytes_read.sum + dram__bytes_write.sum of one config-2 GEMV launch per kernel, from the
+# ncu captures summarised under profiles/ (None: not captured for that kernel)
+NCU_TRAFFIC_CONFIG2 = {
+    "lux_qskinny_i4_g128": 30546432,
+    "lux_qgemv_i4_g128_stream": 30546432,
+    "lux_qgemv_i4_g128_units_fx": 30551808,
+}
 NOMINAL_HBM_GBS = 8000.0          # the benchmark specification's "~8 TB/s"
 NOMINAL_BF16_TFLOPS = 2250.0
 FALLBACK_HBM_GBS = 6650.0         # earlier measurement on this pool, used only without MEASURED_PEAKS.json
@@ -203,6 +207,7 @@ def bench_single(args, peaks):
     sampler.start()
     l0 = rig.backend.launch_count()
     sec, graph = rig.time_graph(launch, len(pool), args.steps, args.warmup)
+    kernel = rig.backend.last_kernel_name()          # the library picks a kernel per shape
     captured = rig.backend.launch_count() - l0
     # keep the same load running a little longer so that the clock sampler sees it
     t_end = time.time() + 0.4
@@ -291,9 +296,9 @@ def bench_single(args, peaks):
                    "l2": f"inputs larger than L2: {len(pool)} weight copies x {wbytes / 1e6:.1f} MB rotated per step",
                    "timing": "CUDA graph replays of the launch sequence, CUDA events on the launching stream"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s",
-                     "frac": achieved / peaks["hbm"], "traffic": NCU_TRAFFIC_CONFIG2, "peak_source": peaks["source"],
+                     "frac": achieved / peaks["hbm"], "traffic": NCU_TRAFFIC_CONFIG2.get(kernel), "peak_source": peaks["source"],
                      "frac_of_nominal_8tbs": achieved / NOMINAL_HBM_GBS, "algorithmic_bytes": abytes,
-                     "kernel": "lux_qskinny_i4_g128"},
+                     "kernel": kernel},
         "cpu_baseline": {"value": wbytes / cpu_sec / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
                          "sample": f"{reps} full config-2 GEMVs, oracle f32 path, OpenMP over rows"},
         "e2e": {"value": wbytes / e2e_sec / 1e9, "unit": "GB/s", "h2d_bytes_per_step": int(x.nbytes),

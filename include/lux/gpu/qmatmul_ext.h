@@ -175,6 +175,11 @@ LUX_GPU_PLUGIN_EXPORT size_t lux_cuda_buffer_size(LuxBackendBuffer* buf);
 /* Number of kernel launches this library has issued since load (all contexts). */
 LUX_GPU_PLUGIN_EXPORT uint64_t lux_cuda_launch_count(void);
 
+/* Name of the quantized-matmul kernel launched most recently by this library (all contexts;
+ * "" before the first one).  The library picks a kernel per shape; benchmarks and profiles
+ * use this to say which one they measured.  The string is static. */
+LUX_GPU_PLUGIN_EXPORT const char* lux_cuda_last_kernel_name(void);
+
 /* Benchmark / tuning hook: overrides one launch heuristic (value 0 restores the
  * default).  Keys: gemv_i4_kernel (1 register-staged, 2 bulk-copy ring, 3 warp-autonomous
  * units), gemv_i4_warps, gemv_i4_row_tiles, gemv_stream_warps, gemv_stream_cg, gemv_stream_stages,

@@ -28,7 +28,7 @@ def _units_supported(M, K, n_out=16, swiglu=False, sms=148, f16_variant=False):
     """Mirror of the units kernel's shape rule: batch <= 16, an even group count, output rows a
     multiple of the 16-row tile, and room in 227 KB of shared memory for the staged
     activations, their group sums, the CTA's scale / zero-point tables, the partial-sum slots,
-    the unit table and two chunks of FIFO per warp."""
+    the unit table and one (fixed-point variant) or two chunks of FIFO per warp."""
     G = K // 128
     if M > 16 or G < 2 or G % 2 or n_out % 16:
         return False
@@ -54,7 +54,8 @@ def _units_supported(M, K, n_out=16, swiglu=False, sms=148, f16_variant=False):
         fixed = G * 3 * M * 128 + G * 64 + meta + cap * 16 * M * 4 + 16 * 8 * 8 + 16 + 1024   # + barriers, slack
     else:
         fixed = M * (2 * K + 64) + G * 8 * mt * 8 + meta + cap * mt * 8 * tmax * 16
-    return fixed + 2 * 16 * cg * 1024 <= 227 * 1024
+    min_stages = 1 if (M <= 2 and not f16_variant) else 2
+    return fixed + min_stages * 16 * cg * 1024 <= 227 * 1024
 
 
 def _kernel_supported(kernel, M, K, n_out, swiglu=False):

@@ -105,7 +105,7 @@ EXPORTED_SYMBOLS = [
     "lux_cuda_qmatmul", "lux_cuda_qmatmul_host", "lux_cuda_qmatmul_route", "lux_cuda_qdequant",
     "lux_cuda_qunpack", "lux_cuda_qmlp", "lux_cuda_qmlp_noalloc", "lux_cuda_context_set_stream", "lux_cuda_context_get_stream",
     "lux_cuda_buffer_wrap", "lux_cuda_buffer_device_ptr", "lux_cuda_buffer_size",
-    "lux_cuda_launch_count", "lux_cuda_tune_set", "lux_cuda_last_device_status",
+    "lux_cuda_launch_count", "lux_cuda_last_kernel_name", "lux_cuda_tune_set", "lux_cuda_last_device_status",
     "lux_cuda_kernel_get", "lux_cuda_kernel_destroy", "lux_cuda_kernel_entry_point",
     "lux_cuda_kernel_function", "lux_cuda_kernel_attributes", "lux_cuda_kernel_workgroup_size",
     "lux_cuda_kernel_count", "lux_cuda_kernel_name",
@@ -197,6 +197,7 @@ class Backend:
         L.lux_cuda_buffer_size.argtypes = [_vp]
         L.lux_cuda_buffer_size.restype = _sz
         L.lux_cuda_launch_count.restype = C.c_uint64
+        L.lux_cuda_last_kernel_name.restype = C.c_char_p
         L.lux_cuda_tune_set.argtypes = [C.c_char_p, _int]
         L.lux_cuda_last_device_status.argtypes = [_vp]
         L.lux_cuda_last_device_status.restype = C.c_uint32
@@ -231,6 +232,10 @@ class Backend:
 
     def launch_count(self) -> int:
         return int(self.lib.lux_cuda_launch_count())
+
+    def last_kernel_name(self) -> str:
+        """Which quantized-matmul kernel the library launched most recently."""
+        return self.lib.lux_cuda_last_kernel_name().decode()
 
     def tune(self, key: str, value: int) -> None:
         _check(self.lib.lux_cuda_tune_set(key.encode(), int(value)), f"tune_set({key})")

@@ -50,7 +50,13 @@ inline Context* as_ctx(LuxBackendContext* c) { return reinterpret_cast<Context*>
 inline Buffer*  as_buf(LuxBackendBuffer* b) { return reinterpret_cast<Buffer*>(b); }
 
 extern std::atomic<uint64_t> g_launches;
+extern std::atomic<const char*> g_last_kernel;
 inline void count_launch(unsigned n = 1) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+// counts one launch and remembers which kernel it was (a string literal)
+inline void count_launch(const char* kernel) {
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    g_last_kernel.store(kernel, std::memory_order_relaxed);
+}
 
 // Maps a CUDA error to the plugin's error vocabulary, logging in the reference's
 // stderr style ("[lux-webgpu] ...", src/webgpu_plugin.cpp:695).

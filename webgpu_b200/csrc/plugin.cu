@@ -14,6 +14,7 @@
 namespace luxcuda {
 
 std::atomic<uint64_t> g_launches{0};
+std::atomic<const char*> g_last_kernel{""};
 Tunables g_tune;
 
 LuxBackendError finish_op(Context* ctx, bool no_sync, const char* what) {
@@ -445,6 +446,7 @@ void* lux_cuda_buffer_device_ptr(LuxBackendBuffer* buf) { return buf ? as_buf(bu
 size_t lux_cuda_buffer_size(LuxBackendBuffer* buf) { return buf ? as_buf(buf)->size : 0; }
 
 uint64_t lux_cuda_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+const char* lux_cuda_last_kernel_name(void) { return g_last_kernel.load(std::memory_order_relaxed); }
 
 uint32_t lux_cuda_last_device_status(LuxBackendContext* context) {
     auto* ctx = as_ctx(context);

@@ -595,7 +595,7 @@ LuxBackendError launch_qgemm_i4_tc(Context* ctx, const QArgs& a) {
         else           e = bf16 ? launch_inst<64, false, true>(mx, mw, p, grid, smem, ctx->stream)
                                 : launch_inst<64, false, false>(mx, mw, p, grid, smem, ctx->stream);
     }
-    count_launch();
+    count_launch(bf16 ? "lux_qgemm_i4_tc_bf16" : "lux_qgemm_i4_tc_f16");
     return map_cuda(e, "lux_qgemm_i4_tc");
 }
 

@@ -511,7 +511,7 @@ LuxBackendError launch_qskinny_i4(Context* ctx, const QArgs& a) {
           : MT == 2 ? launch_skinny_rt<2, false>(rt, p, grid, threads, smem, ctx->stream)
                     : launch_skinny_rt<4, false>(rt, p, grid, threads, smem, ctx->stream);
     }
-    count_launch();
+    count_launch(a.swiglu ? "lux_qskinny_i4_g128_swiglu" : "lux_qskinny_i4_g128");
     return map_cuda(e, "lux_qskinny_i4_g128");
 }
 
@@ -543,7 +543,7 @@ LuxBackendError launch_qgemv_i8(Context* ctx, const QArgs& a) {
     }
     dim3 grid((a.N + 15) / 16, a.M);
     lux_qgemv_i8_g32_f32<<<grid, wpc * 32, smem, ctx->stream>>>(p);
-    count_launch();
+    count_launch("lux_qgemv_i8_g32_f32");
     return map_cuda(cudaGetLastError(), "lux_qgemv_i8_g32_f32");
 }
 

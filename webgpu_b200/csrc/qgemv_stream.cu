@@ -586,7 +586,7 @@ LuxBackendError launch_stream_cw(Context* ctx, const QArgs& a) {
         case 4: if constexpr (CW == 8) e = go(std::integral_constant<int, 4>{}); break;
         default: break;
     }
-    count_launch();
+    count_launch("lux_qgemv_i4_g128_stream");
     return map_cuda(e, "lux_qgemv_i4_g128_stream");
 }
 

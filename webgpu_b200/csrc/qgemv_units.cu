@@ -31,16 +31,18 @@
 //       mma.m16n8k16.f16 with f32 accumulation: the arithmetic of lux_qskinny_i4_g128.
 //   lux_qgemv_i4_g128_units_fx  (batch 1..2)   the integer pipe of an SM sub-core issues one
 //       lop3 per TWO cycles, and at 5 integer ops per 8 nibbles the unpack above -- not HBM, not
-//       the tensor pipe -- bounds the f16 variant.  This one spends 2 ops per 8 nibbles: the
-//       bytes (w & 0x0f0f0f0f) and (w & 0xf0f0f0f0) ARE the low and 16 x the high nibbles as u8,
-//       fed to mma.m16n8k32.u8.s8 (half as many mma).  The activations are converted once per
-//       CTA to block fixed point: per group of 128, X = rint(x * 2^(22-E)) with 2^E just above
-//       the group's largest |x| (every f16 within 2^-11 of that magnitude is represented
-//       exactly; the absolute error is at most 2^(E-23)), split into three signed bytes
-//       X = d0 + 256 d1 + 65536 d2 that ride in three of the eight B columns.  The int32
-//       accumulators are exact; sum (n - zp) X is formed in integers, scaled by
-//       2^(E-22) 256^plane and the group's f16 scale in f32, and the three planes are added
-//       at the end of a unit.
+//       the tensor pipe -- bounds the f16 variant.  This one spends ONE op per 8 nibbles: a
+//       weight word's bytes are R = lo + 16 hi, and w & 0xf0f0f0f0 gives H = 16 hi; both are
+//       valid u8 operands of mma.m16n8k32.u8.s8 (half as many mma as f16), and
+//       lo Xe + hi Xo = R Xe + H (Zo - Xe) when the odd-k activation is held as Xo = 16 Zo.
+//       The activations are converted once per CTA to block fixed point: per group of 128,
+//       X = rint(x 2^(22-E)) for even k and 16 rint(x 2^(18-E)) for odd k, with 2^E just above
+//       the group's largest |x| (an f16 within 2^-11, resp. 2^-7, of that magnitude is
+//       represented exactly; the absolute error is at most 2^(E-23), resp. 2^(E-19)).  Xe and
+//       W = Zo - Xe are split into three signed bytes I = d0 + 256 d1 + 65536 d2 that ride in
+//       three of the eight B columns.  The int32 accumulators are exact; sum (n - zp) X is
+//       completed exactly in f32, scaled by 2^(E-22) 256^plane and the group's f16 scale, and
+//       the three planes are added at the end of a unit.
 //
 // Both compute matmul_nax_grouped (luxcpp/webgpu kernels/wgsl/gpu/quantized_nax.wgsl:568-626)
 // in a different summation order.
@@ -637,13 +639,25 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
         const float up = (amax > 0.0f && !bad) ? __uint_as_float((275u - eb) << 23) : 0.0f;   // 2^(22-E)
         float down = amax > 0.0f ? __uint_as_float((eb - 21u) << 23) : 0.0f;                 // 2^(E-22)
         if (bad) down = __uint_as_float(0x7FC00000u);    // inf / NaN in the group: the outputs are NaN
-        // X + 0x808080 has bytes d0+128, d1+128, d2+128 (X = d0 + 256 d1 + 65536 d2, digits in
-        // [-128, 127]); flipping the top bit of each turns them into the digits as signed bytes
-        uint32_t e[8];
+        // Even k: X = rint(x 2^(22-E)).  Odd k: Z = rint(x 2^(18-E)) and X = 16 Z, so that the
+        // high nibble's product n X equals (16 n) Z: the weights' bytes then need one mask, not two.
+        // With R = lo + 16 hi the raw byte and H = 16 hi the masked one,
+        //   lo Xe + hi Xo = R Xe + H (Zo - Xe),
+        // so the B operand holds the digits of Xe against R and of W = Zo - Xe against H.
+        // I + 0x808080 has bytes d0+128, d1+128, d2+128 (I = d0 + 256 d1 + 65536 d2, digits in
+        // [-128, 127]); flipping the top bit of each turns them into the digits as signed bytes.
+        uint32_t e[8], xo[4];
 #pragma unroll
-        for (int i = 0; i < 8; i++) e[i] = (uint32_t)(__float2int_rn(v[i] * up) + 0x808080) ^ 0x808080u;
-        // byte transpose: word h of plane pl holds the digits of k = 2i + h, i = 0..3
-        uint32_t pw[3][2];
+        for (int i = 0; i < 4; i++) {
+            const int xe = __float2int_rn(v[2 * i] * up);
+            const int zo = __float2int_rn(v[2 * i + 1] * (up * 0.0625f));
+            e[2 * i] = (uint32_t)(xe + 0x808080) ^ 0x808080u;
+            e[2 * i + 1] = (uint32_t)(zo - xe + 0x808080) ^ 0x808080u;
+            xo[i] = (uint32_t)(16 * zo + 0x808080) ^ 0x808080u;    // digits of the odd k's true X, for the sums
+        }
+        // byte transpose: word h of plane pl holds, for i = 0..3, the digit of Xe (h = 0) or W (h = 1)
+        // of the byte with nibbles k = 2i, 2i+1
+        uint32_t pw[3][2], po[3];
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             const uint32_t a01 = prmt(e[h], e[2 + h], 0x5140), a23 = prmt(e[4 + h], e[6 + h], 0x5140);
@@ -652,11 +666,19 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
             pw[1][h] = prmt(a01, a23, 0x7632);
             pw[2][h] = prmt(c01, c23, 0x5410);
         }
+        {
+            const uint32_t a01 = prmt(xo[0], xo[1], 0x5140), a23 = prmt(xo[2], xo[3], 0x5140);
+            const uint32_t c01 = prmt(xo[0], xo[1], 0x0062), c23 = prmt(xo[2], xo[3], 0x0062);
+            po[0] = prmt(a01, a23, 0x5410);
+            po[1] = prmt(a01, a23, 0x7632);
+            po[2] = prmt(c01, c23, 0x5410);
+        }
         // this thread's 8 k are 32t' + 16jp + 8b + (2i + h)
         const int tq = l16 >> 2, jp = (l16 >> 1) & 1, bb = l16 & 1;
 #pragma unroll
         for (int pl = 0; pl < 3; pl++) {
-            int dsum = __dp4a((int)pw[pl][0], 0x01010101, __dp4a((int)pw[pl][1], 0x01010101, 0));
+            // sum over the group of the true X's digit in this plane (for the zero-point term)
+            int dsum = __dp4a((int)pw[pl][0], 0x01010101, __dp4a((int)po[pl], 0x01010101, 0));
 #pragma unroll
             for (int o = 8; o > 0; o >>= 1) dsum += __shfl_xor_sync(0xffffffffu, dsum, o);
             unsigned char* dst = xq + (size_t)grp * XG + (pl * MM + m) * 128 + tq * 32;
@@ -666,7 +688,7 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
                 // lane t reads one float4 = {coef, digit sum} of its columns 2t and 2t+1
                 float* xm = reinterpret_cast<float*>(xmeta + grp * 4) + (MM == 1 ? 2 * pl : 4 * pl + 2 * m);
                 xm[0] = down * (pl == 0 ? 1.0f : pl == 1 ? 256.0f : 65536.0f);
-                xm[1] = __int_as_float(dsum);
+                xm[1] = (float)dsum;
             }
         }
     }
@@ -744,24 +766,26 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
             const unsigned char* xg = xq + (size_t)(gi0 + u) * XG + xcol_off;
             const uint4 xlo = *reinterpret_cast<const uint4*>(xg);          // even k: word pairs 0, 1
             const uint4 xhi = *reinterpret_cast<const uint4*>(xg + 16);     // odd k
-            // the accumulators start at MAGIC, so that they can be read as floats afterwards
-            int lo[4] = {MAGIC, MAGIC, MAGIC, MAGIC}, hi[4] = {MAGIC, MAGIC, MAGIC, MAGIC};
-            constexpr uint32_t ML = 0x0f0f0f0fu, MH = 0xf0f0f0f0u;
-            mma16832_u8s8(lo, qa.x & ML, qb.x & ML, qa.y & ML, qb.y & ML, xlo.x, xlo.y);
-            mma16832_u8s8(hi, qa.x & MH, qb.x & MH, qa.y & MH, qb.y & MH, xhi.x, xhi.y);
-            mma16832_u8s8(lo, qa.z & ML, qb.z & ML, qa.w & ML, qb.w & ML, xlo.z, xlo.w);
-            mma16832_u8s8(hi, qa.z & MH, qb.z & MH, qa.w & MH, qb.w & MH, xhi.z, xhi.w);
+            // the accumulator starts at MAGIC, so that it can be read as a float afterwards
+            int acc[4] = {MAGIC, MAGIC, MAGIC, MAGIC};
+            constexpr uint32_t MH = 0xf0f0f0f0u;
+            mma16832_u8s8(acc, qa.x, qb.x, qa.y, qb.y, xlo.x, xlo.y);                          // R  x Xe
+            mma16832_u8s8(acc, qa.x & MH, qb.x & MH, qa.y & MH, qb.y & MH, xhi.x, xhi.y);      // H  x (Zo - Xe)
+            mma16832_u8s8(acc, qa.z, qb.z, qa.w, qb.w, xlo.z, xlo.w);
+            mma16832_u8s8(acc, qa.z & MH, qb.z & MH, qa.w & MH, qb.w & MH, xhi.z, xhi.w);
             // columns 2t, 2t+1 of this lane: coefficient 2^(E-22) 256^plane and digit sum
             const float4 xm = xmeta[(gi0 + u) * 4 + t];
-            const int zpa = (int)((za >> (4 * u)) & 0xFu), zpb = (int)((zb >> (4 * u)) & 0xFu);
-            // integer sum (n - zp) X = lo + hi/16 - zp * digit-sum, converted exactly through
-            // 1.5 * 2^23 + i (|i| < 2^22); hi is a multiple of 16 and 12582912 * 17/16 = 13369344
+            // -zp as a float: 12582912 - (12582912 + zp)
+            const float nza = 12582912.0f - __uint_as_float(0x4B400000u | ((za >> (4 * u)) & 0xFu));
+            const float nzb = 12582912.0f - __uint_as_float(0x4B400000u | ((zb >> (4 * u)) & 0xFu));
+            // integer sum (n - zp) X of the column = acc - zp * digit-sum, all exact in f32:
+            // |acc| < 2^22 (64 bytes x 255 x 128 + 64 x 240 x 128), |zp * sum| < 2^18
             float v[2][2];                               // [row half][column]
 #pragma unroll
             for (int j = 0; j < 2; j++) {
-                const int ds = __float_as_int(j ? xm.w : xm.y);
-                v[0][j] = fmaf(__int_as_float(hi[j]), 0.0625f, __int_as_float(lo[j] - zpa * ds)) - 13369344.0f;
-                v[1][j] = fmaf(__int_as_float(hi[2 + j]), 0.0625f, __int_as_float(lo[2 + j] - zpb * ds)) - 13369344.0f;
+                const float ds = j ? xm.w : xm.y;
+                v[0][j] = fmaf(nza, ds, __int_as_float(acc[j]) - 12582912.0f);
+                v[1][j] = fmaf(nzb, ds, __int_as_float(acc[2 + j]) - 12582912.0f);
             }
             if (MM == 1) {
                 // both columns are planes of batch row 0: combine them before the scale
@@ -872,7 +896,7 @@ cudaError_t launch_units_cg(int cg, const UnitsParams& p, int grid, size_t smem,
 // the other int4 kernels): batch above 16, an odd number of groups, an output size that is
 // not a multiple of the 16-row tile, a zero-point row that is not a whole number of 16-byte
 // pieces per tile, or activations / scale tables too large to stage in shared memory next
-// to at least two chunks of FIFO per warp.
+// to at least one chunk (fixed-point variant) or two chunks (f16 variant) of FIFO per warp.
 LuxBackendError launch_qgemv_i4_units(Context* ctx, const QArgs& a) {
     const int nout = a.swiglu ? a.N / 2 : a.N;
     if (a.M < 1 || a.M > 16 || a.G < 2 || (a.G & 1) || nout % 16) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
@@ -942,7 +966,8 @@ LuxBackendError launch_qgemv_i4_units(Context* ctx, const QArgs& a) {
                          (fx ? (size_t)UW * MAX_STAGES * 8 + 16 + 1024 : 0);
     const size_t budget = 227 * 1024;
     const size_t chunk = (size_t)cg * 1024;
-    if (fixed + 2 * UW * chunk > budget) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+    // room for at least one chunk of FIFO per warp (two for the cp.async variant)
+    if (fixed + (fx ? 1 : 2) * UW * chunk > budget) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
     const int max_chunks = (p.units_cap + UW - 1) / UW * (KS / cg);       // per warp
     int S = (int)std::min<size_t>((budget - fixed) / (UW * chunk), MAX_STAGES);
     S = std::min(S, std::max(max_chunks, 1));
@@ -977,7 +1002,7 @@ LuxBackendError launch_qgemv_i4_units(Context* ctx, const QArgs& a) {
         e = MT == 1 ? launch_units_cg<1, false, false>(cg, p, grid, smem, ctx->stream)
                     : launch_units_cg<2, false, false>(cg, p, grid, smem, ctx->stream);
     }
-    count_launch();
+    count_launch(fx ? "lux_qgemv_i4_g128_units_fx" : "lux_qgemv_i4_g128_units");
     return map_cuda(e, "lux_qgemv_i4_g128_units");
 }
 
