@@ -135,6 +135,7 @@ struct UnitsParams {
     int units_cap;          // partial-sum slots available per CTA
     int rows_cap;           // weight rows (gate + up) whose scales / zero-points are staged per CTA
     uint32_t* status;       // device status word for a wait that gave up (may be null)
+    uint32_t inv_upt, inv_U; // ceil(2^32 / (units per tile)), ceil(2^32 / U): division-free unit table
 };
 
 // Shared memory: [x staged: M * xstride][xsum: G * 8*MT * 8][scales: rows_cap * G f16]
@@ -542,25 +543,7 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
     uint4 x_first = make_uint4(0u, 0u, 0u, 0u);
     if (tid < npieces) x_first = __ldg(reinterpret_cast<const uint4*>(p.x) + tid);
 
-    // ---- this CTA's scales and zero-points (one cp.async group), requested before the weights:
-    // small copies queued behind the weight stream would arrive microseconds later ------------
-    {
-        const int sc16 = rows_half * p.G / 8;
-        const int zp16 = rows_half * p.ZS / 16;
-        for (int a = 0; a < NACC; a++) {
-            const size_t row0 = (size_t)tile_lo * 16 + (size_t)a * p.up_row_offset;
-            const unsigned char* ssrc = reinterpret_cast<const unsigned char*>(p.scales + row0 * p.G);
-            const uint32_t sdst = smem_u32(ssm + (size_t)a * rows_half * p.G);
-            for (int i = tid; i < sc16; i += UW * 32) cp_async16(sdst + i * 16, ssrc + (size_t)i * 16);
-            if (p.zeros) {
-                const unsigned char* zsrc = p.zeros + row0 * p.ZS;
-                const uint32_t zdst = smem_u32(zsm + (size_t)a * rows_half * p.ZS);
-                for (int i = tid; i < zp16; i += UW * 32) cp_async16(zdst + i * 16, zsrc + (size_t)i * 16);
-            }
-        }
-        cp_async_commit();
-    }
-
+    // ---- barriers, unit table, first weight request: as early as possible ---------------------
     if (lane == 0) {
         if (warp == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
@@ -569,9 +552,11 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
         for (int s0 = 0; s0 < p.S; s0++) mbar_init(bar0 + 8u * (uint32_t)s0, 1u);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    // exact division of a small number by a small constant: multiply by ceil(2^32 / d)
+    auto div_small = [](uint32_t n, uint32_t d, uint32_t inv) { return d == 1u ? n : __umulhi(n, inv); };
     for (int ul = warp + lane * UW; ul < nunits; ul += 32 * UW) {
-        const int tl = ul / upt, rem = ul - tl * upt;
-        const int a = rem / p.U, k = rem - a * p.U;
+        const int tl = (int)div_small((uint32_t)ul, (uint32_t)upt, p.inv_upt), rem = ul - tl * upt;
+        const int a = (int)div_small((uint32_t)rem, (uint32_t)p.U, p.inv_U), k = rem - a * p.U;
         utab[ul] = make_int4((tile_lo + tl) * 16 + a * p.up_row_offset, k * p.KS, a * rows_half + tl * 16, 0);
     }
     __syncwarp();
@@ -596,19 +581,33 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
     if (lane == 0 && my_chunks > 0) issue_chunk(0);
     TRACE(10);
 
+    // ---- this CTA's scales and zero-points (one cp.async group), requested before the bulk of
+    // the weights: small copies queued behind the weight stream would arrive microseconds later -
+    {
+        const int sc16 = rows_half * p.G / 8;
+        const int zp16 = rows_half * p.ZS / 16;
+        for (int a = 0; a < NACC; a++) {
+            const size_t row0 = (size_t)tile_lo * 16 + (size_t)a * p.up_row_offset;
+            const unsigned char* ssrc = reinterpret_cast<const unsigned char*>(p.scales + row0 * p.G);
+            const uint32_t sdst = smem_u32(ssm + (size_t)a * rows_half * p.G);
+            for (int i = tid; i < sc16; i += UW * 32) cp_async16(sdst + i * 16, ssrc + (size_t)i * 16);
+            if (p.zeros) {
+                const unsigned char* zsrc = p.zeros + row0 * p.ZS;
+                const uint32_t zdst = smem_u32(zsm + (size_t)a * rows_half * p.ZS);
+                for (int i = tid; i < zp16; i += UW * 32) cp_async16(zdst + i * 16, zsrc + (size_t)i * 16);
+            }
+        }
+        cp_async_commit();
+    }
     if (!p.zeros)                                         // symmetric: every zero-point is 8
         for (int i = tid; i < (NACC * rows_half * p.ZS + 3) / 4; i += UW * 32)
             reinterpret_cast<uint32_t*>(zsm)[i] = 0x88888888u;
-    // D columns without a plane behind them get coefficient 0 (their accumulators hold garbage);
-    // columns with one are written below by other threads, hence the barrier
-    for (int i = tid; i < p.G * 4; i += UW * 32) xmeta[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-    __syncthreads();
     TRACE(11);
 
     // ---- x -> block fixed point, three signed byte planes in B-fragment order -----------------
     for (int c = tid; c < npieces; c += UW * 32) {
         const uint4 s4 = c == tid ? x_first : __ldg(reinterpret_cast<const uint4*>(p.x) + c);
-        const int m = c / (p.G * 16), cg16 = c - m * p.G * 16;
+        const int m = (MM == 2 && c >= p.G * 16) ? 1 : 0, cg16 = c - m * p.G * 16;
         const int grp = cg16 >> 4, l16 = cg16 & 15;
         float v[8];
         {
@@ -618,26 +617,19 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
             const float2 f3 = __half22float2(*reinterpret_cast<const __half2*>(&s4.w));
             v[0] = f0.x; v[1] = f0.y; v[2] = f1.x; v[3] = f1.y; v[4] = f2.x; v[5] = f2.y; v[6] = f3.x; v[7] = f3.y;
         }
-        float amax = 0.0f;
+        // largest |x| of the group as an f16 bit pattern (monotonic for non-negative values;
+        // inf and NaN, exponent field all ones, compare above every finite value)
+        uint32_t mb = __vmaxu2(__vmaxu2(s4.x & 0x7fff7fffu, s4.y & 0x7fff7fffu),
+                               __vmaxu2(s4.z & 0x7fff7fffu, s4.w & 0x7fff7fffu));
+        mb = max(mb & 0xffffu, mb >> 16);
 #pragma unroll
-        for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
-        // an f16 is inf / NaN exactly when its exponent field is all ones (NaN does not survive fmaxf)
-        unsigned bad = 0;
-        {
-            const uint32_t w4[4] = {s4.x, s4.y, s4.z, s4.w};
-#pragma unroll
-            for (int i = 0; i < 4; i++)
-                bad |= (unsigned)((w4[i] & 0x7C00u) == 0x7C00u) | (unsigned)((w4[i] & 0x7C000000u) == 0x7C000000u);
-        }
-#pragma unroll
-        for (int o = 8; o > 0; o >>= 1) {
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-            bad |= __shfl_xor_sync(0xffffffffu, bad, o);
-        }
+        for (int o = 8; o > 0; o >>= 1) mb = max(mb, __shfl_xor_sync(0xffffffffu, mb, o));
+        const bool bad = mb >= 0x7C00u;
+        const float amax = __half2float(__ushort_as_half((unsigned short)mb));
         // amax = f * 2^E with f in [0.5, 1): biased exponent eb = E + 126.  x * 2^(22-E) is exact.
         const unsigned eb = __float_as_uint(amax) >> 23;
-        const float up = (amax > 0.0f && !bad) ? __uint_as_float((275u - eb) << 23) : 0.0f;   // 2^(22-E)
-        float down = amax > 0.0f ? __uint_as_float((eb - 21u) << 23) : 0.0f;                 // 2^(E-22)
+        const float up = (mb != 0u && !bad) ? __uint_as_float((275u - eb) << 23) : 0.0f;    // 2^(22-E)
+        float down = mb != 0u ? __uint_as_float((eb - 21u) << 23) : 0.0f;                  // 2^(E-22)
         if (bad) down = __uint_as_float(0x7FC00000u);    // inf / NaN in the group: the outputs are NaN
         // Even k: X = rint(x 2^(22-E)).  Odd k: Z = rint(x 2^(18-E)) and X = 16 Z, so that the
         // high nibble's product n X equals (16 n) Z: the weights' bytes then need one mask, not two.
@@ -677,23 +669,45 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
         const int tq = l16 >> 2, jp = (l16 >> 1) & 1, bb = l16 & 1;
 #pragma unroll
         for (int pl = 0; pl < 3; pl++) {
-            // sum over the group of the true X's digit in this plane (for the zero-point term)
-            int dsum = __dp4a((int)pw[pl][0], 0x01010101, __dp4a((int)po[pl], 0x01010101, 0));
-#pragma unroll
-            for (int o = 8; o > 0; o >>= 1) dsum += __shfl_xor_sync(0xffffffffu, dsum, o);
             unsigned char* dst = xq + (size_t)grp * XG + (pl * MM + m) * 128 + tq * 32;
             *reinterpret_cast<uint32_t*>(dst + ((0 * 2 + jp) * 2 + bb) * 4) = pw[pl][0];
             *reinterpret_cast<uint32_t*>(dst + ((1 * 2 + jp) * 2 + bb) * 4) = pw[pl][1];
-            if (l16 == 0) {
-                // lane t reads one float4 = {coef, digit sum} of its columns 2t and 2t+1
-                float* xm = reinterpret_cast<float*>(xmeta + grp * 4) + (MM == 1 ? 2 * pl : 4 * pl + 2 * m);
-                xm[0] = down * (pl == 0 ? 1.0f : pl == 1 ? 256.0f : 65536.0f);
-                xm[1] = (float)dsum;
+        }
+        // sums over the group of the true X's digits per plane (for the zero-point term); planes
+        // 0 and 1 share one register through the reduction (|sum| <= 128 * 128 fits 16 bits)
+        int ds[3];
+#pragma unroll
+        for (int pl = 0; pl < 3; pl++)
+            ds[pl] = __dp4a((int)pw[pl][0], 0x01010101, __dp4a((int)po[pl], 0x01010101, 0));
+        int d01 = ds[0] + ds[1] * 65536, d2 = ds[2];
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) {
+            d01 += __shfl_xor_sync(0xffffffffu, d01, o);
+            d2 += __shfl_xor_sync(0xffffffffu, d2, o);
+        }
+        if (l16 == 0) {
+            const int s0 = (int)(short)(d01 & 0xffff), s1 = (d01 - s0) >> 16;
+            // Lane t of a consumer reads one float4 = {coef, digit sum} of its columns 2t and 2t+1.
+            // Every float of the group's four entries is written here exactly once; columns
+            // without a plane behind them get coefficient 0 (their accumulators hold garbage).
+            float4* xm = xmeta + grp * 4;
+            if (MM == 1) {
+                xm[0] = make_float4(down, (float)s0, down * 256.0f, (float)s1);
+                xm[1] = make_float4(down * 65536.0f, (float)d2, 0.f, 0.f);
+                xm[2] = make_float4(0.f, 0.f, 0.f, 0.f);
+                xm[3] = make_float4(0.f, 0.f, 0.f, 0.f);
+            } else {
+                float2* x2 = reinterpret_cast<float2*>(xm) + m;          // .xy for m = 0, .zw for m = 1
+                x2[0] = make_float2(down, (float)s0);
+                x2[2] = make_float2(down * 256.0f, (float)s1);
+                x2[4] = make_float2(down * 65536.0f, (float)d2);
+                x2[6] = make_float2(0.f, 0.f);
             }
         }
     }
     TRACE(12);
-    // fill the rest of the FIFO (the async engine queues the requests: nothing stalls here)
+    // fill the rest of the FIFO (the async engine queues the requests: nothing stalls here; asked
+    // for before the conversion they only delay the first chunk and the tables: measured slower)
     if (lane == 0)
         for (int s0 = 1; s0 < p.S && issued < my_chunks; s0++) issue_chunk(s0);
     cp_async_wait(0);                                    // the scales and zero-points have landed
@@ -971,10 +985,18 @@ LuxBackendError launch_qgemv_i4_units(Context* ctx, const QArgs& a) {
     const int max_chunks = (p.units_cap + UW - 1) / UW * (KS / cg);       // per warp
     int S = (int)std::min<size_t>((budget - fixed) / (UW * chunk), MAX_STAGES);
     S = std::min(S, std::max(max_chunks, 1));
+    // measured on B200: the fixed-point variant is fastest two chunks deep (deeper FIFOs only delay
+    // the first chunk and the tables at start-up; large layers do not care)
     if (g_tune.gemv_units_stages > 0) S = std::min(S, g_tune.gemv_units_stages);
+    else if (fx) S = std::min(S, 2);
     p.S = std::max(S, 1);
     p.S0 = std::min(p.S, g_tune.gemv_units_pre > 0 ? g_tune.gemv_units_pre : 1);
     p.status = ctx->d_status;
+    {
+        const uint32_t upt = (uint32_t)(nacc * U);
+        p.inv_upt = upt > 1 ? (uint32_t)((((uint64_t)1 << 32) + upt - 1) / upt) : 0u;
+        p.inv_U = U > 1 ? (uint32_t)((((uint64_t)1 << 32) + (uint32_t)U - 1) / (uint32_t)U) : 0u;
+    }
     const size_t smem = fixed + (size_t)p.S * UW * chunk;
 
     cudaError_t e;
