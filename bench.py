@@ -260,6 +260,7 @@ def bench_single(args, peaks):
         ab1 = algorithmic_bytes(l1, 1, 4, 4)
         err1 = orc.rel_l2(yb1.to_host(np.float32, (1, l1.N)), orc.qmatmul(x1, *l1.triple, bits=8, group=32))
         extra["gemv_int8_cfg1"] = {
+            "kernel": rig.backend.last_kernel_name(),
             "weight_gbs": l1.weight_bytes / sec1 / 1e9, "total_gbs": ab1 / sec1 / 1e9, "us": sec1 * 1e6,
             "frac_of_measured_hbm": ab1 / sec1 / 1e9 / peaks["hbm"], "frac_of_nominal_8tbs": ab1 / sec1 / 1e9 / NOMINAL_HBM_GBS,
             "rel_l2_vs_oracle": err1}
@@ -280,6 +281,7 @@ def bench_single(args, peaks):
         err3 = orc.rel_l2(y3[rows], orc.qmatmul(x3[rows], *l3.triple, bits=4, group=128, w_round=orc.BF16))
         tf = flops / sec3 / 1e12
         extra["gemm_m512_cfg3"] = {
+            "kernel": rig.backend.last_kernel_name(),
             "tflops": tf, "us": sec3 * 1e6, "frac_of_measured_bf16_burst": tf / peaks["bf16"],
             "frac_of_measured_bf16_sustained": tf / peaks["bf16_sustained"],
             "frac_of_nominal_2250": tf / NOMINAL_BF16_TFLOPS, "rel_l2_vs_oracle": err3,

@@ -181,8 +181,8 @@ LUX_GPU_PLUGIN_EXPORT uint64_t lux_cuda_launch_count(void);
 LUX_GPU_PLUGIN_EXPORT const char* lux_cuda_last_kernel_name(void);
 
 /* Benchmark / tuning hook: overrides one launch heuristic (value 0 restores the
- * default).  Keys: gemv_i4_kernel (1 register-staged, 2 bulk-copy ring, 3 warp-autonomous
- * units), gemv_i4_warps, gemv_i4_row_tiles, gemv_stream_warps, gemv_stream_cg, gemv_stream_stages,
+ * default).  Keys: gemv_i8_kernel (1 row-per-warp-group, 2 warp-autonomous units), gemv_i4_kernel
+ * (1 register-staged, 2 bulk-copy ring, 3 warp-autonomous units), gemv_i4_warps, gemv_i4_row_tiles, gemv_stream_warps, gemv_stream_cg, gemv_stream_stages,
  * gemv_units_ks, gemv_units_stages, gemv_units_cg, gemv_units_pre, gemv_units_fx, gemv_i8_warps, gemm_tc_bn,
  * gemm_tc_stages, gemm_tc_splitk.  Unknown keys return INVALID_ARGUMENT.  Process-wide;
  * not part of the drop-in surface. */

@@ -137,24 +137,105 @@ def test_int8_unpack_and_dequant_bit_exact(ctx, shape):
 
 # -- config 1: int8 g32 GEMV, f32 ---------------------------------------------------------
 
-def test_config1_int8_gemv(ctx):
+class _kernel8:
+    """Forces one int8 GEMV kernel: 1 = lux_qgemv_i8_g32_f32 (any shape), 2 = warp-autonomous
+    lux_qgemv_i8_g32_units_fx (batch <= 2, K % 256 == 0, N % 16 == 0), 0 = the library's choice."""
+
+    def __init__(self, backend, which):
+        self.backend, self.which = backend, which
+
+    def __enter__(self):
+        self.backend.tune("gemv_i8_kernel", self.which)
+
+    def __exit__(self, *exc):
+        self.backend.tune("gemv_i8_kernel", 0)
+
+
+@pytest.mark.parametrize("kernel", [0, 1, 2])
+def test_config1_int8_gemv(ctx, backend, kernel):
     x, layer = synth.config1()
-    y = _run(ctx, x, layer)
+    with _kernel8(backend, kernel):
+        y = _run(ctx, x, layer)
     ref = orc.qmatmul(x, *layer.triple, bits=8, group=32)
     exact = orc.qmatmul(x, *layer.triple, bits=8, group=32, acc_mode=2)
     err = orc.rel_l2(y, ref)
     assert err < TOL_F32, err
     # the tensor-core order is at least as close to the exact sum as f32-sequential is
     assert orc.rel_l2(y, exact) <= max(2 * orc.rel_l2(ref, exact), 2e-6)
+    assert ctx.last_device_status() == 0
 
 
 @pytest.mark.parametrize("N,K,M", [(16, 64, 1), (40, 192, 1), (100, 1024, 3), (16, 16384, 1)])
-def test_int8_gemv_shapes(ctx, N, K, M):
+def test_int8_gemv_shapes(ctx, backend, N, K, M):
     x = synth.activations(M, K, "f32", 23, f"i8.{N}.{K}")
     layer = synth.int8_layer(N, K, 23, f"i8.{N}.{K}")
-    y = _run(ctx, x, layer)
+    with _kernel8(backend, 1):
+        y = _run(ctx, x, layer)
     ref = orc.qmatmul(x, *layer.triple, bits=8, group=32)
     assert orc.rel_l2(y, ref) < TOL_F32
+
+
+@pytest.mark.parametrize("N,K,M", [(16, 256, 1), (48, 512, 2), (16, 16384, 1), (4800, 256, 1), (4096, 4096, 2),
+                                   (1008, 3072, 1)])
+def test_int8_units_shapes(ctx, backend, N, K, M):
+    """The warp-autonomous int8 kernel: one tile, several tiles per CTA (4800 rows = 300 tiles),
+    long rows, batch 2."""
+    x = synth.activations(M, K, "f32", 24, f"i8u.{N}.{K}")
+    layer = synth.int8_layer(N, K, 24, f"i8u.{N}.{K}")
+    with _kernel8(backend, 2):
+        y = _run(ctx, x, layer)
+    ref = orc.qmatmul(x, *layer.triple, bits=8, group=32)
+    assert orc.rel_l2(y, ref) < TOL_F32
+    assert ctx.last_device_status() == 0
+
+
+@pytest.mark.parametrize("ks,stages", [(8, 1), (8, 3), (16, 2), (32, 2), (96, 4)])
+@pytest.mark.parametrize("M", [1, 2])
+def test_int8_units_geometries(ctx, backend, ks, stages, M):
+    """Every K-slice width and FIFO depth of the int8 units kernel gives the same answer
+    (96 groups per row; 63 tiles)."""
+    x = synth.activations(M, 3072, "f32", 26, "i8g.x")
+    layer = synth.int8_layer(1008, 3072, 26, "i8g")
+    ref = orc.qmatmul(x, *layer.triple, bits=8, group=32)
+    backend.tune("gemv_units_ks", ks)
+    backend.tune("gemv_units_stages", stages)
+    try:
+        with _kernel8(backend, 2):
+            y = _run(ctx, x, layer)
+    finally:
+        backend.tune("gemv_units_ks", 0)
+        backend.tune("gemv_units_stages", 0)
+    assert orc.rel_l2(y, ref) < TOL_F32
+    assert ctx.last_device_status() == 0
+
+
+def test_int8_units_fixed_point_ranges(ctx, backend):
+    """Block fixed point per group of 32 activations: groups of zeros, of tiny values (flushed
+    below 2^-96), of huge values and of magnitudes 2^20 apart must all agree with the oracle;
+    an infinity makes every output non-finite."""
+    K, N = 1024, 64
+    rng = np.random.default_rng(91)
+    x = rng.standard_normal((1, K)).astype(np.float32)
+    x[:, 0:32] = 0.0
+    x[:, 32:64] *= np.float32(1e-35)                              # below 2^-96: counts as zero
+    x[:, 64:96] *= np.float32(1e20)
+    x[:, 96:128] *= np.where(np.arange(32) % 5 == 0, np.float32(2.0 ** 20), np.float32(1.0))
+    x[:, 128:160] *= np.float32(1e-20)
+    layer = synth.int8_layer(N, K, 92, "i8r")
+    ref = orc.qmatmul(x, *layer.triple, bits=8, group=32)
+    with _kernel8(backend, 2):
+        y = _run(ctx, x, layer)
+    assert orc.rel_l2(y, ref) < TOL_F32
+    x2 = x.copy()
+    x2[:, 64:96] = 0                                              # without the huge group
+    ref2 = orc.qmatmul(x2, *layer.triple, bits=8, group=32)
+    with _kernel8(backend, 2):
+        y2 = _run(ctx, x2, layer)
+    assert orc.rel_l2(y2, ref2) < TOL_F32
+    x2[0, 700] = np.inf
+    with _kernel8(backend, 2):
+        y3 = _run(ctx, x2, layer)
+    assert not np.isfinite(y3).any()
 
 
 # -- config 2: int4 g128 GEMV, f16 ---------------------------------------------------------

@@ -83,6 +83,7 @@ struct Tunables {
     int gemv_i4_warps = 0;       // warps per CTA of the int4 skinny kernel
     int gemv_i4_row_tiles = 0;   // 16-row tiles per CTA
     int gemv_i8_warps = 0;
+    int gemv_i8_kernel = 0;      // 0 auto, 1 lux_qgemv_i8_g32_f32, 2 lux_qgemv_i8_g32_units_fx
     int gemv_i4_kernel = 0;      // 0 auto, 1 lux_qskinny_i4_g128, 2 lux_qgemv_i4_g128_stream, 3 lux_qgemv_i4_g128_units
     int gemv_stream_cg = 0;      // stream kernel: groups per stage / 8 (1, 2 or 4)
     int gemv_stream_stages = 0;  // stream kernel: ring depth cap
@@ -112,6 +113,7 @@ struct QArgs {
 };
 
 LuxBackendError launch_qgemv_i8(Context* ctx, const QArgs& a);
+LuxBackendError launch_qgemv_i8_units(Context* ctx, const QArgs& a);    // NOT_SUPPORTED if the shape does not fit
 LuxBackendError launch_qskinny_i4(Context* ctx, const QArgs& a);
 LuxBackendError launch_qgemv_i4_stream(Context* ctx, const QArgs& a);   // NOT_SUPPORTED if the shape does not fit
 LuxBackendError launch_qgemv_i4_units(Context* ctx, const QArgs& a);    // NOT_SUPPORTED if the shape does not fit

@@ -14,6 +14,7 @@ namespace luxcuda {
 const void* kernel_addr_qskinny_i4();
 const void* kernel_addr_qskinny_i4_swiglu();
 const void* kernel_addr_qgemv_i8();
+const void* kernel_addr_qgemv_i8_units_fx();
 const void* kernel_addr_qgemv_i4_stream();
 const void* kernel_addr_qgemv_i4_units();
 const void* kernel_addr_qgemv_i4_units_fx();
@@ -33,6 +34,7 @@ struct Entry {
 
 const Entry kTable[] = {
     {"lux_qgemv_i8_g32_f32",       luxcuda::kernel_addr_qgemv_i8,           256, 1, 1},
+    {"lux_qgemv_i8_g32_units_fx",  luxcuda::kernel_addr_qgemv_i8_units_fx,  512, 1, 1},
     {"lux_qgemv_i4_g128_stream",   luxcuda::kernel_addr_qgemv_i4_stream,    544, 1, 1},
     {"lux_qgemv_i4_g128_units",    luxcuda::kernel_addr_qgemv_i4_units,     512, 1, 1},
     {"lux_qgemv_i4_g128_units_fx", luxcuda::kernel_addr_qgemv_i4_units_fx,  512, 1, 1},

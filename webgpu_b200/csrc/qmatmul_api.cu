@@ -76,7 +76,14 @@ LuxBackendError bind_weights(Checked& c, Buffer* w, Buffer* scales, Buffer* zero
 
 LuxBackendError dispatch(Context* ctx, const Checked& c) {
     switch (c.route) {
-        case LUX_QROUTE_GEMV_I8:    return launch_qgemv_i8(ctx, c.a);
+        case LUX_QROUTE_GEMV_I8: {
+            // batch 1 and 2: the warp-autonomous fixed-point kernel wherever its plan fits
+            if (g_tune.gemv_i8_kernel == 2 || (g_tune.gemv_i8_kernel == 0 && c.a.M <= 2)) {
+                LuxBackendError e = launch_qgemv_i8_units(ctx, c.a);
+                if (e != LUX_BACKEND_ERROR_NOT_SUPPORTED || g_tune.gemv_i8_kernel == 2) return e;
+            }
+            return launch_qgemv_i8(ctx, c.a);
+        }
         case LUX_QROUTE_SKINNY_I4: {
             // Both kernels compute the same thing.  Measured on B200: the TMA ring kernel wins
             // for batches of 4..16 and for big layers (long rows or many megabytes of weights);
@@ -260,7 +267,7 @@ LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_tune_set(const char* key, int val
     if (!key) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
     struct { const char* k; int* v; } table[] = {
         {"gemv_i4_warps", &g_tune.gemv_i4_warps},   {"gemv_i4_row_tiles", &g_tune.gemv_i4_row_tiles},
-        {"gemv_i8_warps", &g_tune.gemv_i8_warps},   {"gemm_tc_bn", &g_tune.gemm_tc_bn},
+        {"gemv_i8_warps", &g_tune.gemv_i8_warps},   {"gemv_i8_kernel", &g_tune.gemv_i8_kernel},   {"gemm_tc_bn", &g_tune.gemm_tc_bn},
         {"gemv_i4_kernel", &g_tune.gemv_i4_kernel}, {"gemv_stream_cg", &g_tune.gemv_stream_cg},
         {"gemv_stream_stages", &g_tune.gemv_stream_stages}, {"gemv_stream_warps", &g_tune.gemv_stream_warps},
         {"gemv_units_ks", &g_tune.gemv_units_ks}, {"gemv_units_stages", &g_tune.gemv_units_stages}, {"gemv_units_cg", &g_tune.gemv_units_cg}, {"gemv_units_pre", &g_tune.gemv_units_pre}, {"gemv_units_fx", &g_tune.gemv_units_fx},
