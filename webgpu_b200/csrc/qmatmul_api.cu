@@ -118,7 +118,7 @@ LuxBackendError ensure_stage(Context* ctx, size_t bytes) {
     cudaStreamSynchronize(ctx->stream);
     if (ctx->h_stage) { cudaFreeHost(ctx->h_stage); ctx->h_stage = nullptr; ctx->h_stage_bytes = 0; }
     if (ctx->d_stage) { cudaFree(ctx->d_stage); ctx->d_stage = nullptr; ctx->d_stage_bytes = 0; }
-    LUX_CUDA_TRY(cudaHostAlloc(&ctx->h_stage, want, cudaHostAllocDefault));
+    LUX_CUDA_TRY(cudaHostAlloc(&ctx->h_stage, want, cudaHostAllocMapped));   // device-visible: small results are written into it directly
     ctx->h_stage_bytes = want;
     LUX_CUDA_TRY(cudaMalloc(&ctx->d_stage, want));
     ctx->d_stage_bytes = want;
@@ -181,14 +181,22 @@ LuxBackendError lux_cuda_qmatmul_host(LuxBackendContext* context, const LuxQMatm
     std::lock_guard<std::mutex> lock(ctx->mu);
     e = ensure_stage(ctx, y_off + yb);
     if (e != LUX_BACKEND_OK) return e;
-    // host -> pinned -> device, kernel, device -> pinned -> host: one stream wait in all.
+    // host -> pinned -> device, kernel, result -> pinned -> host: one stream wait in all.  A small
+    // result is written by the kernel straight into the pinned buffer (posted writes over PCIe),
+    // which takes the device-to-host copy and its DMA latency off the critical path; a large one
+    // (prefill) goes through device memory and one copy.
     std::memcpy(ctx->h_stage, x_host, xb);
     LUX_CUDA_TRY(cudaMemcpyAsync(ctx->d_stage, ctx->h_stage, xb, cudaMemcpyHostToDevice, ctx->stream));
     a.x = ctx->d_stage;
-    a.y = (char*)ctx->d_stage + y_off;
+    void* y_mapped = nullptr;
+    const bool direct = yb <= ((size_t)256 << 10) &&
+                        cudaHostGetDevicePointer(&y_mapped, (char*)ctx->h_stage + y_off, 0) == cudaSuccess && y_mapped;
+    if (!direct) (void)cudaGetLastError();
+    a.y = direct ? y_mapped : (void*)((char*)ctx->d_stage + y_off);
     e = dispatch(ctx, c);
     if (e != LUX_BACKEND_OK) return e;
-    LUX_CUDA_TRY(cudaMemcpyAsync((char*)ctx->h_stage + y_off, a.y, yb, cudaMemcpyDeviceToHost, ctx->stream));
+    if (!direct)
+        LUX_CUDA_TRY(cudaMemcpyAsync((char*)ctx->h_stage + y_off, a.y, yb, cudaMemcpyDeviceToHost, ctx->stream));
     e = finish_op(ctx, false, "lux_cuda_qmatmul_host");
     if (e != LUX_BACKEND_OK) return e;
     std::memcpy(y_host, (char*)ctx->h_stage + y_off, yb);
