@@ -346,32 +346,42 @@ def bench_tp(args, peaks):
     def step(i):
         return mlps[i % copies].forward(M)
 
-    with torch.cuda.stream(rig.stream):
-        for i in range(max(args.warmup, 3)):
-            step(i)
-        torch.cuda.synchronize()
+    # Timed as CUDA-graph replays of the step sequence (FFN kernels + NCCL all-reduce captured
+    # together): with 40 us of GPU work per step, eager Python + NCCL launches would be the
+    # thing measured.  Falls back to eager launches if the capture is refused.
+    timing = "CUDA graph replays of the step sequence (kernels + all-reduce), CUDA events on the launching stream"
+    if world > 1:
+        dist.barrier()
+    sampler.start()
+    try:
+        sec, _ = rig.time_graph(step, copies, args.steps, args.warmup)
         if world > 1:
             dist.barrier()
-        sampler.start()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(rig.stream)
-        for i in range(args.steps):
-            step(i)
-        e1.record(rig.stream)
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        sec = e0.elapsed_time(e1) * 1e-3 / args.steps
         # compute-only time (no collective) to separate kernel bandwidth from all-reduce cost
-        torch.cuda.synchronize()
-        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        c0.record(rig.stream)
-        for i in range(args.steps):
-            mlps[i % copies].forward(M, all_reduce=False)
-        c1.record(rig.stream)
-        torch.cuda.synchronize()
-        sec_compute = c0.elapsed_time(c1) * 1e-3 / args.steps
+        sec_compute, _ = rig.time_graph(lambda i: mlps[i % copies].forward(M, all_reduce=False), copies,
+                                        args.steps, args.warmup)
+    except Exception as exc:   # noqa: BLE001 - any capture failure: measure eagerly instead
+        timing = f"eager launches (graph capture failed: {type(exc).__name__})"
+        with torch.cuda.stream(rig.stream):
+            for i in range(max(args.warmup, 3)):
+                step(i)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(rig.stream)
+            for i in range(args.steps):
+                step(i)
+            e1.record(rig.stream)
+            torch.cuda.synchronize()
+            sec = e0.elapsed_time(e1) * 1e-3 / args.steps
+            c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            c0.record(rig.stream)
+            for i in range(args.steps):
+                mlps[i % copies].forward(M, all_reduce=False)
+            c1.record(rig.stream)
+            torch.cuda.synchronize()
+            sec_compute = c0.elapsed_time(c1) * 1e-3 / args.steps
+    if world > 1:
+        dist.barrier()
     clocks = sampler.stop()
     y = mlps[(args.steps - 1) % copies].y[:M].float().cpu().numpy()   # after the compute-only loop: partial
     t = torch.tensor([sec, sec_compute], device="cuda", dtype=torch.float64)
@@ -415,7 +425,8 @@ def bench_tp(args, peaks):
             "dtype": "int4 weights, f16 activations, f32 accumulate", "data": "synthetic",
             "config": {"workload": f"llama70b_mlp_tp (config 5): gate_up 8192->57344 + SwiGLU, down 28672->8192, batch {M}",
                        "parallelism": f"tp{world}", "collective": "NCCL all-reduce of f16 partials" if world > 1 else "none",
-                       "l2": f"inputs larger than L2: {copies} shard copies x {shard_bytes / 1e6:.1f} MB rotated per step"},
+                       "l2": f"inputs larger than L2: {copies} shard copies x {shard_bytes / 1e6:.1f} MB rotated per step",
+                       "timing": timing},
             "roofline": {"bound": "hbm", "achieved": per_gpu_alg / sec_compute / 1e9, "peak": peaks["hbm"],
                          "unit": "GB/s", "frac": per_gpu_alg / sec_compute / 1e9 / peaks["hbm"], "traffic": None,
                          "peak_source": peaks["source"], "note": "per GPU, both FFN kernels, without the all-reduce",
