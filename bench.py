@@ -336,7 +336,23 @@ def bench_tp(args, peaks):
     shard_bytes = total_wbytes // world
     copies = max(2, -(-int(2.9 * L2_BYTES) // shard_bytes))
     g_sh, d_sh = tp.shard_mlp(gate_up, down, rank, world)
-    mlps = [tp.TPMlp(ctx, g_sh, d_sh, rank, world, M, "f16", presharded=True) for _ in range(copies)]
+    peer, collective = None, "none"
+    if world > 1:
+        collective = "NCCL all-reduce of f16 partials"
+        if args.collective == "push" and (M * d["H"]) % 8 == 0:
+            ok = 1
+            try:
+                peer = tp.PeerAllReduce(ctx, rank, world, M * d["H"] * 2)
+            except Exception as exc:   # noqa: BLE001 - e.g. CUDA IPC refused in this environment
+                ok = 0
+                print(f"[bench] rank {rank}: push all-reduce unavailable ({exc}); using NCCL", file=sys.stderr)
+            flag = torch.tensor([ok], device="cuda")
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            if int(flag.item()) == 1:
+                collective = "push all-reduce over peer memory (lux_cuda_peer_allreduce), f16 partials, f32 sum"
+            else:
+                peer = None
+    mlps = [tp.TPMlp(ctx, g_sh, d_sh, rank, world, M, "f16", presharded=True, peer=peer) for _ in range(copies)]
     xt = torch.from_numpy(x).cuda()
     for m in mlps:
         m.x[:M].copy_(xt)
@@ -424,7 +440,7 @@ def bench_tp(args, peaks):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "int4 weights, f16 activations, f32 accumulate", "data": "synthetic",
             "config": {"workload": f"llama70b_mlp_tp (config 5): gate_up 8192->57344 + SwiGLU, down 28672->8192, batch {M}",
-                       "parallelism": f"tp{world}", "collective": "NCCL all-reduce of f16 partials" if world > 1 else "none",
+                       "parallelism": f"tp{world}", "collective": collective,
                        "l2": f"inputs larger than L2: {copies} shard copies x {shard_bytes / 1e6:.1f} MB rotated per step",
                        "timing": timing},
             "roofline": {"bound": "hbm", "achieved": per_gpu_alg / sec_compute / 1e9, "peak": peaks["hbm"],
@@ -433,8 +449,11 @@ def bench_tp(args, peaks):
                          "us_compute_only": sec_compute * 1e6, "us_with_allreduce": sec * 1e6},
             "e2e": {"value": total_wbytes / e2e_sec / 1e9, "unit": "GB/s", "h2d_bytes_per_step": int(x.nbytes),
                     "d2h_bytes_per_step": int(M * d["H"] * 2), "us_per_step": e2e_sec * 1e6},
-            "gpu_launches": 2 * args.steps, "clocks": clocks, "parity_rel_l2": parity,
+            "gpu_launches": (3 if peer is not None else 2) * args.steps, "clocks": clocks, "parity_rel_l2": parity,
         }
+    ctx.sync()                       # raises if a bounded device-side wait gave up during the run
+    if peer is not None:
+        peer.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -497,6 +516,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=1, help="batch M of the tensor-parallel FFN workload")
     ap.add_argument("--workload", default="auto", choices=["auto", "gemv", "tp_mlp"])
+    ap.add_argument("--collective", default="push", choices=["push", "nccl"],
+                    help="all-reduce of the tensor-parallel FFN: the plugin's push all-reduce over peer memory "
+                         "(falls back to NCCL if the peer mapping is refused) or NCCL")
     ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE",
                     help="override a launch heuristic (lux_cuda_tune_set), e.g. gemv_i4_kernel=2")
     args = ap.parse_args()

@@ -160,7 +160,8 @@ LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_qmlp_noalloc(
 /* -- interop needed by a host that already owns CUDA state (one process per GPU) ---- */
 
 /* Run this context's work on an existing stream (a cudaStream_t passed as void*;
- * NULL restores the context's own stream).  The reference has one implicit queue per
+ * NULL restores the context's own non-blocking stream; to name the default stream pass
+ * cudaStreamLegacy or cudaStreamPerThread, not 0).  The reference has one implicit queue per
  * context (src/webgpu_plugin.cpp:584-622); this is its CUDA counterpart. */
 LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_context_set_stream(LuxBackendContext* ctx, void* stream);
 LUX_GPU_PLUGIN_EXPORT void* lux_cuda_context_get_stream(LuxBackendContext* ctx);
@@ -171,6 +172,38 @@ LUX_GPU_PLUGIN_EXPORT void* lux_cuda_context_get_stream(LuxBackendContext* ctx);
 LUX_GPU_PLUGIN_EXPORT LuxBackendBuffer* lux_cuda_buffer_wrap(LuxBackendContext* ctx, void* device_ptr, size_t bytes);
 LUX_GPU_PLUGIN_EXPORT void*  lux_cuda_buffer_device_ptr(LuxBackendBuffer* buf);
 LUX_GPU_PLUGIN_EXPORT size_t lux_cuda_buffer_size(LuxBackendBuffer* buf);
+
+/* ---- one-node push all-reduce over peer memory (tensor-parallel FFN) --------------------
+ * No reference counterpart: luxcpp/webgpu has no multi-device path.  One process per GPU.
+ * Every rank creates a communicator (a window in its own memory that peers write into),
+ * exchanges the 64-byte handles by any means (the Python host uses torch.distributed),
+ * connects, and then calls lux_cuda_peer_allreduce on every rank for every reduction, in the
+ * same order.  The kernel pushes self-validating 8-byte words {payload, epoch} with plain
+ * stores, waits a bounded time for the peers' words and sums in rank order (bit-identical results on all ranks); a peer that never
+ * arrives leaves the tensor unchanged and is reported as LUX_BACKEND_ERROR_DEVICE_LOST by the
+ * next synchronising call (status 0x7C050005).  Works under CUDA-graph capture and replay. */
+typedef struct LuxPeerComm LuxPeerComm;
+#define LUX_PEER_HANDLE_BYTES 64
+/* max_bytes: largest tensor (in bytes) that will be reduced.  handle_out: 64 bytes to send to the
+ * other ranks (may be NULL when connecting with pointers). */
+LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_peer_comm_create(LuxBackendContext* ctx, int rank, int world,
+                                                                size_t max_bytes, LuxPeerComm** out, void* handle_out);
+/* handles: world * 64 bytes, rank order (the own entry is ignored); opens the peers' windows
+ * through CUDA IPC.  NOT_SUPPORTED if the system refuses the mapping. */
+LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_peer_comm_connect(LuxPeerComm* comm, const void* handles);
+/* For hosts that drive several GPUs from one process with peer access enabled: windows[r] is
+ * lux_cuda_peer_comm_window() of rank r's communicator (the own entry is ignored). */
+LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_peer_comm_connect_ptrs(LuxPeerComm* comm, void* const* windows);
+LUX_GPU_PLUGIN_EXPORT void*  lux_cuda_peer_comm_window(LuxPeerComm* comm);
+LUX_GPU_PLUGIN_EXPORT size_t lux_cuda_peer_comm_window_bytes(LuxPeerComm* comm);
+/* In-place sum of `count` f16 / bf16 elements (count % 8 == 0, 16-byte aligned buffer,
+ * count * 2 <= max_bytes) across the ranks, on the context's stream.  flags:
+ * LUX_QMATMUL_FLAG_NO_SYNC to return without waiting. */
+LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_peer_allreduce(LuxBackendContext* ctx, LuxPeerComm* comm,
+                                                              LuxBackendBuffer* buf, size_t count, LuxQDType dtype,
+                                                              uint32_t flags);
+/* Every rank must have finished its last reduction (e.g. a host barrier) before any rank destroys. */
+LUX_GPU_PLUGIN_EXPORT void lux_cuda_peer_comm_destroy(LuxPeerComm* comm);
 
 /* Number of kernel launches this library has issued since load (all contexts). */
 LUX_GPU_PLUGIN_EXPORT uint64_t lux_cuda_launch_count(void);
@@ -184,7 +217,7 @@ LUX_GPU_PLUGIN_EXPORT const char* lux_cuda_last_kernel_name(void);
  * default).  Keys: gemv_i8_kernel (1 row-per-warp-group, 2 warp-autonomous units), gemv_i4_kernel
  * (1 register-staged, 2 bulk-copy ring, 3 warp-autonomous units), gemv_i4_warps, gemv_i4_row_tiles, gemv_stream_warps, gemv_stream_cg, gemv_stream_stages,
  * gemv_units_ks, gemv_units_stages, gemv_units_cg, gemv_units_pre, gemv_units_fx, gemv_i8_warps, gemm_tc_bn,
- * gemm_tc_stages, gemm_tc_splitk.  Unknown keys return INVALID_ARGUMENT.  Process-wide;
+ * gemm_tc_stages, gemm_tc_splitk, peer_wait_limit.  Unknown keys return INVALID_ARGUMENT.  Process-wide;
  * not part of the drop-in surface. */
 LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_tune_set(const char* key, int value);
 

@@ -1,5 +1,7 @@
-"""Tensor-parallel FFN on two GPUs: one process per GPU, plugin kernels + NCCL all-reduce,
-rank 0 checks the result against the oracle's sharded computation (tolerance 5e-3, f16)."""
+"""Tensor-parallel FFN on two GPUs: one process per GPU, plugin kernels + NCCL all-reduce and,
+second, the plugin's own push all-reduce over peer memory (repeatability, identical bits on
+all ranks, CUDA-graph replay); rank 0 checks the results against the oracle's sharded
+computation (tolerance 5e-3, f16)."""
 import os
 import socket
 import subprocess
@@ -36,6 +38,44 @@ for M in (1, 8, 64):
         err = orc.rel_l2(y.astype(np.float16), ref)
         assert err < 5e-3, (M, err)
         print("TP_OK", M, err)
+# ---- the plugin's own push all-reduce over peer memory instead of NCCL ----------------------
+peer = tp.PeerAllReduce(ctx, rank, world, 64 * H * 2)
+for M in (1, 8, 64):
+    x = synth.activations(M, K, "f16", 51, f"tp2.x{M}")
+    mlp = tp.TPMlp(ctx, gate_up, down, rank, world, M, "f16", peer=peer)
+    mlp.x[:M].copy_(torch.from_numpy(x).cuda())
+    outs = []
+    for rep in range(5):                                   # several epochs: both parities, slot reuse
+        outs.append(mlp.forward(M).float().cpu().numpy().copy())
+        ctx.sync()                                         # raises DEVICE_LOST if a peer wait gave up
+    assert all(np.array_equal(outs[0], o) for o in outs[1:]), "push all-reduce is not repeatable"
+    assert ctx.last_device_status() == 0
+    # every rank holds the same bits
+    gathered = [None] * world
+    dist.all_gather_object(gathered, outs[0].tobytes())
+    assert all(g == gathered[0] for g in gathered), "ranks disagree"
+    # captured in a CUDA graph and replayed (the epoch lives in device memory)
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        mlp.forward(M)
+        st.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=st, capture_error_mode="relaxed"):
+            mlp.forward(M)
+            mlp.forward(M)
+        for _ in range(3):
+            g.replay()
+        st.synchronize()
+        ctx.sync()
+    assert np.array_equal(mlp.y[:M].float().cpu().numpy(), outs[0]), "graph replay differs"
+    if rank == 0:
+        from oracle import oracle as orc
+        shards = [tuple(l.triple for l in tp.shard_mlp(gate_up, down, r, world)) for r in range(world)]
+        ref = orc.tp_mlp(x, shards, fused=True, w_round=orc.F16 if M > 32 else orc.F32)
+        err = orc.rel_l2(outs[0].astype(np.float16), ref)
+        assert err < 5e-3, (M, err)
+        print("PUSH_OK", M, err)
+peer.close()
 dist.barrier()
 dist.destroy_process_group()
 """
@@ -58,3 +98,4 @@ def test_tp_two_gpus(tmp_path, backend):
     outs = [p.communicate(timeout=300)[0] for p in procs]
     assert all(p.returncode == 0 for p in procs), "\n".join(outs)
     assert outs[0].count("TP_OK") == 3, outs[0]
+    assert outs[0].count("PUSH_OK") == 3, outs[0]

@@ -109,7 +109,11 @@ EXPORTED_SYMBOLS = [
     "lux_cuda_kernel_get", "lux_cuda_kernel_destroy", "lux_cuda_kernel_entry_point",
     "lux_cuda_kernel_function", "lux_cuda_kernel_attributes", "lux_cuda_kernel_workgroup_size",
     "lux_cuda_kernel_count", "lux_cuda_kernel_name",
+    "lux_cuda_peer_comm_create", "lux_cuda_peer_comm_connect", "lux_cuda_peer_comm_connect_ptrs",
+    "lux_cuda_peer_comm_window", "lux_cuda_peer_comm_window_bytes", "lux_cuda_peer_allreduce",
+    "lux_cuda_peer_comm_destroy",
 ]
+PEER_HANDLE_BYTES = 64
 
 
 class BackendError(RuntimeError):
@@ -187,6 +191,20 @@ class Backend:
         L.lux_cuda_qunpack.argtypes = [_vp, C.POINTER(QMatmulDesc), _vp, _vp, _vp]
         L.lux_cuda_qmlp.argtypes = [_vp, C.POINTER(QMlpDesc)] + [_vp] * 9
         L.lux_cuda_qmlp_noalloc.argtypes = [_vp, C.POINTER(QMlpDesc)] + [_vp] * 8
+        L.lux_cuda_peer_comm_create.restype = C.c_int
+        L.lux_cuda_peer_comm_create.argtypes = [_vp, C.c_int, C.c_int, C.c_size_t, C.POINTER(_vp), _vp]
+        L.lux_cuda_peer_comm_connect.restype = C.c_int
+        L.lux_cuda_peer_comm_connect.argtypes = [_vp, _vp]
+        L.lux_cuda_peer_comm_connect_ptrs.restype = C.c_int
+        L.lux_cuda_peer_comm_connect_ptrs.argtypes = [_vp, C.POINTER(_vp)]
+        L.lux_cuda_peer_comm_window.restype = _vp
+        L.lux_cuda_peer_comm_window.argtypes = [_vp]
+        L.lux_cuda_peer_comm_window_bytes.restype = C.c_size_t
+        L.lux_cuda_peer_comm_window_bytes.argtypes = [_vp]
+        L.lux_cuda_peer_allreduce.restype = C.c_int
+        L.lux_cuda_peer_allreduce.argtypes = [_vp, _vp, _vp, C.c_size_t, C.c_uint32, C.c_uint32]
+        L.lux_cuda_peer_comm_destroy.restype = None
+        L.lux_cuda_peer_comm_destroy.argtypes = [_vp]
         L.lux_cuda_context_set_stream.argtypes = [_vp, _vp]
         L.lux_cuda_context_get_stream.argtypes = [_vp]
         L.lux_cuda_context_get_stream.restype = _vp
@@ -364,8 +382,15 @@ class Context:
             raise BackendError(INVALID_ARGUMENT, "lux_cuda_buffer_wrap")
         return Buffer(self, h, nbytes)
 
+    CUDA_STREAM_LEGACY = 1      # cudaStreamLegacy: the handle that names the default stream explicitly
+
     def set_stream(self, stream_ptr: int | None) -> None:
-        _check(self.backend.lib.lux_cuda_context_set_stream(self.handle, stream_ptr or None), "set_stream")
+        """None restores the context's own (non-blocking) stream.  0 is what frameworks report for
+        the default stream; it is passed on as cudaStreamLegacy, because a NULL handle means
+        "own stream" at the C boundary and work there would not be ordered with the caller's."""
+        if stream_ptr is not None and stream_ptr == 0:
+            stream_ptr = self.CUDA_STREAM_LEGACY
+        _check(self.backend.lib.lux_cuda_context_set_stream(self.handle, stream_ptr), "set_stream")
 
     def binary_f32(self, op: str, a: Buffer, b: Buffer, out: Buffer, n: int) -> None:
         _check(self.backend.vt[f"op_{op}_f32"](self.handle, a.handle, b.handle, out.handle, n), f"op_{op}_f32")
@@ -442,6 +467,33 @@ class Context:
 
     def last_device_status(self) -> int:
         return int(self.backend.lib.lux_cuda_last_device_status(self.handle))
+
+    # -- one-node push all-reduce over peer memory ------------------------------------------
+    def peer_comm_create(self, rank: int, world: int, max_bytes: int):
+        """Returns (communicator handle, 64-byte IPC handle to send to the other ranks)."""
+        comm = _vp()
+        handle = C.create_string_buffer(PEER_HANDLE_BYTES)
+        _check(self.backend.lib.lux_cuda_peer_comm_create(self.handle, rank, world, max_bytes, C.byref(comm), handle),
+               "lux_cuda_peer_comm_create")
+        return comm, handle.raw
+
+    def peer_comm_connect(self, comm, handles: bytes) -> None:
+        """`handles`: every rank's 64-byte handle concatenated in rank order."""
+        _check(self.backend.lib.lux_cuda_peer_comm_connect(comm, handles), "lux_cuda_peer_comm_connect")
+
+    def peer_comm_connect_ptrs(self, comm, windows) -> None:
+        arr = (_vp * len(windows))(*[_vp(w) for w in windows])
+        _check(self.backend.lib.lux_cuda_peer_comm_connect_ptrs(comm, arr), "lux_cuda_peer_comm_connect_ptrs")
+
+    def peer_comm_window(self, comm) -> int:
+        return int(self.backend.lib.lux_cuda_peer_comm_window(comm) or 0)
+
+    def peer_allreduce(self, comm, buf: "Buffer", count: int, dtype: int, flags: int = 0) -> None:
+        _check(self.backend.lib.lux_cuda_peer_allreduce(self.handle, comm, buf.handle, count, dtype, flags),
+               "lux_cuda_peer_allreduce")
+
+    def peer_comm_destroy(self, comm) -> None:
+        self.backend.lib.lux_cuda_peer_comm_destroy(comm)
 
     def __del__(self):
         # Contexts are destroyed explicitly; buffers hold a reference to their context,

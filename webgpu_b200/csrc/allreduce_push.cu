@@ -1,0 +1,321 @@
+// lux_peer_allreduce_push -- one-node, one-shot all-reduce (sum) of a small 16-bit tensor over
+// peer memory, for the tensor-parallel FFN's partial outputs (16 KB at batch 1): the payload is
+// far below the size where a ring or tree pays, and latency is everything.
+//
+// Every rank owns a WINDOW in its own HBM that its peers can write (CUDA IPC mapping, or plain
+// peer pointers inside one process):
+//
+//     [2 parities][world source ranks][slot: one 8-byte word {2 elements, epoch} per 2 elements]
+//
+// One kernel per call, one CTA:
+//   1. push   every thread packs its share of the local tensor into 8-byte words
+//             {two 16-bit elements, epoch} and stores them (two words per 16-byte store) into
+//             slot [parity][my rank] of EVERY rank's window, its own included.  An aligned 8-byte
+//             store arrives whole, so a word whose epoch field matches carries valid data: no
+//             fence and no separate "done" flag are needed (the scheme of NCCL's LL protocol).
+//             Plain stores only -- no loads from peer memory, no TMA, no multicast;
+//   2. reduce every thread polls the words it needs in its OWN window (L1 bypassed) until their
+//             epoch field matches, sums the source ranks in rank order in f32 and writes the local
+//             tensor, so all ranks hold bit-identical results.  Every poll is bounded; if one
+//             gives up the kernel leaves the tensor untouched and sets the context's status word
+//             (the host then reports DEVICE_LOST), nothing else happens.
+// The epoch counter lives in device memory and is advanced by the kernel itself, so the call
+// can be captured in a CUDA graph and replayed.  Two parities suffice: a rank can be at most
+// one epoch ahead of a peer, because finishing epoch n needs every peer's epoch-n words, which
+// a peer stores only after it has finished reading epoch n-1.
+//
+// The reference has no multi-device path (no NCCL / MPI call site in luxcpp/webgpu); this is
+// the push all-reduce its tensor-parallel replacement needs.
+#include "common.cuh"
+
+#include <cstring>
+
+namespace luxcuda {
+
+namespace {
+
+constexpr int MAX_WORLD = 8;
+constexpr int AR_THREADS = 1024;
+
+struct PeerComm {
+    int device = 0;
+    int rank = 0, world = 0;
+    size_t max_bytes = 0;
+    unsigned char* window = nullptr;          // this rank's window (owned)
+    unsigned char* peer[MAX_WORLD] = {};      // every rank's window as seen from here (peer[rank] == window)
+    bool opened[MAX_WORLD] = {};              // mapped with cudaIpcOpenMemHandle (to be closed)
+    uint32_t* epoch = nullptr;                // device counter (owned)
+    bool connected = false;
+};
+
+struct PushParams {
+    unsigned char* peer[MAX_WORLD];
+    void* buf;
+    uint32_t* epoch;
+    uint32_t* status;
+    unsigned long long max_bytes;
+    unsigned long long count;                 // 16-bit elements
+    int rank, world;
+    unsigned int wait_limit;
+};
+
+// a slot holds max_bytes of payload as 8-byte words {4 bytes of payload, 4 bytes of epoch}
+__host__ __device__ inline size_t slot_bytes(size_t max_bytes) { return 2 * max_bytes; }
+// the slots, then 256 bytes that hold an identification tag; the ALLOCATION is rounded up to a
+// multiple of 2 MiB so that it owns its driver block: cudaIpcOpenMemHandle maps whole blocks and
+// returns the block's base, which is the window only if nothing else shares the block
+__host__ __device__ inline size_t window_bytes(int world, size_t max_bytes) {
+    return (size_t)2 * world * slot_bytes(max_bytes) + 256;
+}
+inline size_t window_alloc_bytes(int world, size_t max_bytes) {
+    const size_t two_mib = (size_t)2 << 20;
+    return (window_bytes(world, max_bytes) + two_mib - 1) / two_mib * two_mib;
+}
+struct WindowTag { uint32_t magic, rank, world, max_bytes_lo; };
+constexpr uint32_t TAG_MAGIC = 0x4C555850u;   // "LUXP"
+inline size_t tag_offset(int world, size_t max_bytes) { return (size_t)2 * world * slot_bytes(max_bytes); }
+__device__ __forceinline__ unsigned char* slot_ptr(unsigned char* win, int world, size_t max_bytes, int parity, int src) {
+    return win + ((size_t)parity * world + src) * slot_bytes(max_bytes);
+}
+
+template <bool BF16> __device__ __forceinline__ float2 widen2(uint32_t v);
+template <> __device__ __forceinline__ float2 widen2<false>(uint32_t v) { return __half22float2(*reinterpret_cast<const __half2*>(&v)); }
+template <> __device__ __forceinline__ float2 widen2<true>(uint32_t v) { return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v)); }
+template <bool BF16> __device__ __forceinline__ uint32_t narrow2(float a, float b);
+template <> __device__ __forceinline__ uint32_t narrow2<false>(float a, float b) {
+    __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t narrow2<true>(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+// 16 bytes = two self-validating 8-byte words; volatile: straight to / from L2
+__device__ __forceinline__ void store_words(uint4* dst, uint4 v) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ uint4 load_words(const uint4* src) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src) : "memory");
+    return v;
+}
+
+// count is a multiple of 8 (16-byte pieces of the tensor); buf is 16-byte aligned
+template <bool BF16>
+__global__ void __launch_bounds__(AR_THREADS, 1) lux_peer_allreduce_push(const PushParams p) {
+    __shared__ int s_failed;
+    const int tid = threadIdx.x;
+    if (tid == 0) s_failed = 0;
+    const uint32_t epoch = *p.epoch + 1u;                         // the same value for every thread
+    const int parity = (int)(epoch & 1u);
+    const size_t pieces = (size_t)p.count / 8;                    // 16-byte pieces of the tensor
+    const uint4* src = reinterpret_cast<const uint4*>(p.buf);
+
+    // 1. push: piece i becomes four words = two 16-byte stores, into my slot of every window
+    for (size_t i = tid; i < pieces; i += AR_THREADS) {
+        const uint4 v = src[i];
+        const uint4 lo = make_uint4(v.x, epoch, v.y, epoch), hi = make_uint4(v.z, epoch, v.w, epoch);
+#pragma unroll 1
+        for (int r = 0; r < p.world; r++) {
+            uint4* dst = reinterpret_cast<uint4*>(slot_ptr(p.peer[r], p.world, p.max_bytes, parity, p.rank)) + 2 * i;
+            store_words(dst, lo);
+            store_words(dst + 1, hi);
+        }
+    }
+    __syncthreads();                                              // s_failed is initialised
+    // 2a. wait (bounded) until every word this thread will read carries this epoch
+    unsigned char* mine = p.peer[p.rank];
+    for (size_t i = tid; i < pieces; i += AR_THREADS) {
+#pragma unroll 1
+        for (int r = 0; r < p.world; r++) {
+            const uint4* w = reinterpret_cast<const uint4*>(slot_ptr(mine, p.world, p.max_bytes, parity, r)) + 2 * i;
+            bool ok = false;
+            for (unsigned int it = 0; it < p.wait_limit; ++it) {
+                const uint4 lo = load_words(w), hi = load_words(w + 1);
+                if (lo.y == epoch && lo.w == epoch && hi.y == epoch && hi.w == epoch) { ok = true; break; }
+                if (*(volatile int*)&s_failed) break;
+                __nanosleep(20);
+            }
+            if (!ok) { atomicExch(&s_failed, 1); break; }
+        }
+        if (*(volatile int*)&s_failed) break;
+    }
+    __syncthreads();
+    if (s_failed) {
+        // a peer never arrived: report it and leave the tensor as it is (the epoch is not
+        // advanced, so the next call starts from the same state)
+        if (tid == 0 && p.status) atomicOr(p.status, 0x7C050005u);
+        return;
+    }
+    // 2b. everything is here: sum the source ranks in rank order
+    for (size_t i = tid; i < pieces; i += AR_THREADS) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+        for (int r = 0; r < p.world; r++) {
+            const uint4* w = reinterpret_cast<const uint4*>(slot_ptr(mine, p.world, p.max_bytes, parity, r)) + 2 * i;
+            const uint4 lo = load_words(w), hi = load_words(w + 1);
+            const uint32_t d[4] = {lo.x, lo.z, hi.x, hi.z};
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float2 f = widen2<BF16>(d[j]);
+                acc[2 * j] += f.x;
+                acc[2 * j + 1] += f.y;
+            }
+        }
+        uint4 o;
+        o.x = narrow2<BF16>(acc[0], acc[1]);
+        o.y = narrow2<BF16>(acc[2], acc[3]);
+        o.z = narrow2<BF16>(acc[4], acc[5]);
+        o.w = narrow2<BF16>(acc[6], acc[7]);
+        reinterpret_cast<uint4*>(p.buf)[i] = o;
+    }
+    if (tid == 0) *p.epoch = epoch;
+}
+
+PeerComm* as_comm(LuxPeerComm* c) { return reinterpret_cast<PeerComm*>(c); }
+
+}  // namespace
+
+const void* kernel_addr_peer_allreduce_push() { return (const void*)lux_peer_allreduce_push<false>; }
+
+}  // namespace luxcuda
+
+using namespace luxcuda;
+
+extern "C" {
+
+LuxBackendError lux_cuda_peer_comm_create(LuxBackendContext* context, int rank, int world, size_t max_bytes,
+                                          LuxPeerComm** out, void* handle_out) {
+    Context* ctx = reinterpret_cast<Context*>(context);
+    if (!ctx || !out || world < 1 || world > MAX_WORLD || rank < 0 || rank >= world || max_bytes == 0)
+        return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    *out = nullptr;
+    max_bytes = (max_bytes + 255) & ~(size_t)255;
+    cudaSetDevice(ctx->device);
+    PeerComm* c = new (std::nothrow) PeerComm();
+    if (!c) return LUX_BACKEND_ERROR_OUT_OF_MEMORY;
+    c->device = ctx->device;
+    c->rank = rank;
+    c->world = world;
+    c->max_bytes = max_bytes;
+    const size_t bytes = window_alloc_bytes(world, max_bytes);
+    if (cudaMalloc(&c->window, bytes) != cudaSuccess || cudaMalloc(&c->epoch, sizeof(uint32_t)) != cudaSuccess) {
+        if (c->window) cudaFree(c->window);
+        delete c;
+        (void)cudaGetLastError();
+        return LUX_BACKEND_ERROR_OUT_OF_MEMORY;
+    }
+    cudaMemset(c->window, 0, bytes);
+    cudaMemset(c->epoch, 0, sizeof(uint32_t));
+    const WindowTag tag{TAG_MAGIC, (uint32_t)rank, (uint32_t)world, (uint32_t)max_bytes};
+    cudaMemcpy(c->window + tag_offset(world, max_bytes), &tag, sizeof tag, cudaMemcpyHostToDevice);
+    cudaDeviceSynchronize();
+    c->peer[rank] = c->window;
+    if (handle_out) {
+        static_assert(sizeof(cudaIpcMemHandle_t) == LUX_PEER_HANDLE_BYTES, "handle size");
+        cudaIpcMemHandle_t h;
+        std::memset(&h, 0, sizeof h);
+        if (world > 1 && cudaIpcGetMemHandle(&h, c->window) != cudaSuccess) {
+            // no IPC on this system: the caller can still connect with raw peer pointers
+            (void)cudaGetLastError();
+            std::memset(&h, 0, sizeof h);
+        }
+        std::memcpy(handle_out, &h, sizeof h);
+    }
+    *out = reinterpret_cast<LuxPeerComm*>(c);
+    return LUX_BACKEND_OK;
+}
+
+LuxBackendError lux_cuda_peer_comm_connect(LuxPeerComm* comm, const void* handles) {
+    PeerComm* c = as_comm(comm);
+    if (!c || !handles) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    cudaSetDevice(c->device);
+    for (int r = 0; r < c->world; r++) {
+        if (r == c->rank) continue;
+        cudaIpcMemHandle_t h;
+        std::memcpy(&h, (const unsigned char*)handles + (size_t)r * LUX_PEER_HANDLE_BYTES, sizeof h);
+        void* ptr = nullptr;
+        cudaError_t e = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            (void)cudaGetLastError();
+            std::fprintf(stderr, "[lux-cuda] cudaIpcOpenMemHandle(rank %d): %s\n", r, cudaGetErrorString(e));
+            return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+        }
+        c->peer[r] = (unsigned char*)ptr;
+        c->opened[r] = true;
+        // the mapping must really be rank r's window (same geometry, its tag where ours is)
+        WindowTag tag{};
+        e = cudaMemcpy(&tag, c->peer[r] + tag_offset(c->world, c->max_bytes), sizeof tag, cudaMemcpyDeviceToHost);
+        if (e != cudaSuccess || tag.magic != TAG_MAGIC || tag.rank != (uint32_t)r || tag.world != (uint32_t)c->world ||
+            tag.max_bytes_lo != (uint32_t)c->max_bytes) {
+            (void)cudaGetLastError();
+            std::fprintf(stderr, "[lux-cuda] peer window of rank %d does not identify itself (mapping refused)\n", r);
+            return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+        }
+    }
+    c->connected = true;
+    return LUX_BACKEND_OK;
+}
+
+LuxBackendError lux_cuda_peer_comm_connect_ptrs(LuxPeerComm* comm, void* const* windows) {
+    PeerComm* c = as_comm(comm);
+    if (!c || !windows) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    for (int r = 0; r < c->world; r++) {
+        if (r == c->rank) continue;
+        if (!windows[r]) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+        c->peer[r] = (unsigned char*)windows[r];
+    }
+    c->connected = true;
+    return LUX_BACKEND_OK;
+}
+
+void* lux_cuda_peer_comm_window(LuxPeerComm* comm) { return comm ? as_comm(comm)->window : nullptr; }
+size_t lux_cuda_peer_comm_window_bytes(LuxPeerComm* comm) {
+    return comm ? window_bytes(as_comm(comm)->world, as_comm(comm)->max_bytes) : 0;
+}
+
+LuxBackendError lux_cuda_peer_allreduce(LuxBackendContext* context, LuxPeerComm* comm, LuxBackendBuffer* buffer,
+                                        size_t count, LuxQDType dtype, uint32_t flags) {
+    Context* ctx = reinterpret_cast<Context*>(context);
+    PeerComm* c = as_comm(comm);
+    Buffer* b = reinterpret_cast<Buffer*>(buffer);
+    if (!ctx || !c || !b || !b->ptr || count == 0) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    if (dtype != LUX_QDTYPE_F16 && dtype != LUX_QDTYPE_BF16) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+    if (!c->connected && c->world > 1) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    if (count % 8 || (reinterpret_cast<uintptr_t>(b->ptr) & 15)) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+    if (count * 2 > c->max_bytes || count * 2 > b->size) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    if (ctx->device != c->device) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    cudaSetDevice(ctx->device);
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    PushParams p{};
+    for (int r = 0; r < c->world; r++) p.peer[r] = c->peer[r];
+    p.buf = b->ptr;
+    p.epoch = c->epoch;
+    p.status = ctx->d_status;
+    p.max_bytes = c->max_bytes;
+    p.count = count;
+    p.rank = c->rank;
+    p.world = c->world;
+    p.wait_limit = g_tune.peer_wait_limit > 0 ? (unsigned)g_tune.peer_wait_limit : (1u << 22);   // ~0.2 s per word
+    if (dtype == LUX_QDTYPE_BF16) lux_peer_allreduce_push<true><<<1, AR_THREADS, 0, ctx->stream>>>(p);
+    else lux_peer_allreduce_push<false><<<1, AR_THREADS, 0, ctx->stream>>>(p);
+    count_launch("lux_peer_allreduce_push");
+    LuxBackendError e = map_cuda(cudaGetLastError(), "lux_peer_allreduce_push");
+    if (e != LUX_BACKEND_OK) return e;
+    return finish_op(ctx, (flags & LUX_QMATMUL_FLAG_NO_SYNC) != 0, "lux_cuda_peer_allreduce");
+}
+
+void lux_cuda_peer_comm_destroy(LuxPeerComm* comm) {
+    PeerComm* c = as_comm(comm);
+    if (!c) return;
+    cudaSetDevice(c->device);
+    cudaDeviceSynchronize();
+    for (int r = 0; r < c->world; r++)
+        if (c->opened[r] && c->peer[r]) cudaIpcCloseMemHandle(c->peer[r]);
+    if (c->window) cudaFree(c->window);
+    if (c->epoch) cudaFree(c->epoch);
+    (void)cudaGetLastError();
+    delete c;
+}
+
+}  // extern "C"

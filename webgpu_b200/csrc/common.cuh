@@ -83,6 +83,7 @@ struct Tunables {
     int gemv_i4_warps = 0;       // warps per CTA of the int4 skinny kernel
     int gemv_i4_row_tiles = 0;   // 16-row tiles per CTA
     int gemv_i8_warps = 0;
+    int peer_wait_limit = 0;     // push all-reduce: polls (40 ns apart) before a wait gives up (default 2^22)
     int gemv_i8_kernel = 0;      // 0 auto, 1 lux_qgemv_i8_g32_f32, 2 lux_qgemv_i8_g32_units_fx
     int gemv_i4_kernel = 0;      // 0 auto, 1 lux_qskinny_i4_g128, 2 lux_qgemv_i4_g128_stream, 3 lux_qgemv_i4_g128_units
     int gemv_stream_cg = 0;      // stream kernel: groups per stage / 8 (1, 2 or 4)

@@ -18,6 +18,7 @@ const void* kernel_addr_qgemv_i8_units_fx();
 const void* kernel_addr_qgemv_i4_stream();
 const void* kernel_addr_qgemv_i4_units();
 const void* kernel_addr_qgemv_i4_units_fx();
+const void* kernel_addr_peer_allreduce_push();
 const void* kernel_addr_qdequant_i4();
 const void* kernel_addr_qdequant_i8();
 const void* kernel_addr_qgemm_i4_tc_bf16();
@@ -40,6 +41,7 @@ const Entry kTable[] = {
     {"lux_qgemv_i4_g128_units_fx", luxcuda::kernel_addr_qgemv_i4_units_fx,  512, 1, 1},
     {"lux_qskinny_i4_g128",        luxcuda::kernel_addr_qskinny_i4,         128, 1, 1},
     {"lux_qskinny_i4_g128_swiglu", luxcuda::kernel_addr_qskinny_i4_swiglu,  128, 1, 1},
+    {"lux_peer_allreduce_push",    luxcuda::kernel_addr_peer_allreduce_push, 1024, 1, 1},
     {"lux_qdequant_i4_g128",       luxcuda::kernel_addr_qdequant_i4,        256, 1, 1},
     {"lux_qdequant_i8_g32",        luxcuda::kernel_addr_qdequant_i8,        256, 1, 1},
     {"lux_qgemm_i4_tc_bf16",       luxcuda::kernel_addr_qgemm_i4_tc_bf16,   320, 1, 1},

@@ -7,7 +7,10 @@ Sharding (Megatron-style, one exchange step):
   down    [H, I]   row-parallel: rank r holds input columns [r*I/t, (r+1)*I/t) of every
                    row, i.e. whole groups (I/t must be a multiple of the group size);
                    its output is a PARTIAL [M, H] sum.
-  all-reduce(sum)  of the 16-bit partials over NCCL (NVLink/NVSwitch) finishes the layer.
+  all-reduce(sum)  of the 16-bit partials finishes the layer: NCCL (NVLink/NVSwitch) through
+                   torch.distributed, or the plugin's own one-shot push all-reduce over peer
+                   memory (`collective="push"`, lux_cuda_peer_allreduce), which costs a few
+                   microseconds instead of NCCL's ~11 for a 16 KB tensor.
 
 The reference has no multi-device path at all (no NCCL/MPI call site anywhere in
 luxcpp/webgpu); the `[gate ; up]` stacking is its own convention
@@ -58,6 +61,37 @@ def shard_mlp(gate_up: QLayer, down: QLayer, rank: int, world: int):
     return shard_gate_up(gate_up, rank, world), shard_down(down, rank, world)
 
 
+class PeerAllReduce:
+    """The plugin's push all-reduce for one process per GPU on one node: creates this rank's
+    window, exchanges the IPC handles through torch.distributed and connects.  ``__call__``
+    sums a wrapped 16-bit buffer in place across the ranks on the plugin's current stream."""
+
+    def __init__(self, ctx, rank: int, world: int, max_bytes: int, group=None):
+        import torch.distributed as dist
+
+        self.ctx, self.rank, self.world, self.group = ctx, rank, world, group
+        self.comm, handle = ctx.peer_comm_create(rank, world, max_bytes)
+        if world > 1:
+            handles = [None] * world
+            dist.all_gather_object(handles, handle, group=group)
+            ctx.peer_comm_connect(self.comm, b"".join(handles))
+            dist.barrier(group=group)          # every window is mapped everywhere before the first push
+
+    def __call__(self, buf, count: int, dtype: int, flags: int = 0) -> None:
+        self.ctx.peer_allreduce(self.comm, buf, count, dtype, flags)
+
+    def close(self) -> None:
+        import torch
+        import torch.distributed as dist
+
+        if self.comm is not None:
+            torch.cuda.synchronize()
+            if self.world > 1:
+                dist.barrier(group=self.group)  # nobody is still pushing into a window that goes away
+            self.ctx.peer_comm_destroy(self.comm)
+            self.comm = None
+
+
 class TPMlp:
     """One rank's shard of the FFN, resident on this process's GPU.
 
@@ -67,13 +101,14 @@ class TPMlp:
     """
 
     def __init__(self, ctx, gate_up: QLayer, down: QLayer, rank: int, world: int, m_max: int,
-                 act: str = "f16", group=None, presharded: bool = False):
+                 act: str = "f16", group=None, presharded: bool = False, peer: "PeerAllReduce | None" = None):
         import torch
         from . import backend as B
 
         self.torch = torch
         self.B = B
         self.ctx, self.rank, self.world, self.group = ctx, rank, world, group
+        self.peer = peer                     # None: torch.distributed (NCCL); else the push all-reduce
         self.act_code = {"f16": B.F16, "bf16": B.BF16}[act]
         tdt = {"f16": torch.float16, "bf16": torch.bfloat16}[act]
         g_sh, d_sh = (gate_up, down) if presharded else shard_mlp(gate_up, down, rank, world)
@@ -98,7 +133,10 @@ class TPMlp:
                       flags=self.B.FLAG_NO_SYNC)
         out = self.y[:M]
         if all_reduce and self.world > 1:
-            torch.distributed.all_reduce(out, group=self.group)
+            if self.peer is not None and (M * self.H) % 8 == 0:
+                self.peer(self._by, M * self.H, self.act_code, flags=self.B.FLAG_NO_SYNC)
+            else:
+                torch.distributed.all_reduce(out, group=self.group)
         return out
 
 
