@@ -202,6 +202,17 @@ LUX_GPU_PLUGIN_EXPORT size_t lux_cuda_peer_comm_window_bytes(LuxPeerComm* comm);
 LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_peer_allreduce(LuxBackendContext* ctx, LuxPeerComm* comm,
                                                               LuxBackendBuffer* buf, size_t count, LuxQDType dtype,
                                                               uint32_t flags);
+/* The tensor-parallel FFN of one rank in one call: lux_cuda_qmlp on this rank's shards followed by
+ * the all-reduce of y through `comm` (same argument meaning as lux_cuda_qmlp; y holds the reduced
+ * result on every rank).  At batch <= 2 with f16 activations the down projection's kernel stores
+ * its outputs straight into every rank's window (fused compute + collective) and a second small
+ * kernel waits for the peers and sums; otherwise it is lux_cuda_qmlp + lux_cuda_peer_allreduce.
+ * Call on every rank, in the same order as any other reduction on `comm`. */
+LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_qmlp_tp(
+    LuxBackendContext* ctx, const LuxQMlpDesc* desc, LuxBackendBuffer* x,
+    LuxBackendBuffer* w_gate_up, LuxBackendBuffer* s_gate_up, LuxBackendBuffer* z_gate_up,
+    LuxBackendBuffer* w_down, LuxBackendBuffer* s_down, LuxBackendBuffer* z_down,
+    LuxBackendBuffer* h_scratch, LuxBackendBuffer* y, LuxPeerComm* comm);
 /* Every rank must have finished its last reduction (e.g. a host barrier) before any rank destroys. */
 LUX_GPU_PLUGIN_EXPORT void lux_cuda_peer_comm_destroy(LuxPeerComm* comm);
 
@@ -217,7 +228,7 @@ LUX_GPU_PLUGIN_EXPORT const char* lux_cuda_last_kernel_name(void);
  * default).  Keys: gemv_i8_kernel (1 row-per-warp-group, 2 warp-autonomous units), gemv_i4_kernel
  * (1 register-staged, 2 bulk-copy ring, 3 warp-autonomous units), gemv_i4_warps, gemv_i4_row_tiles, gemv_stream_warps, gemv_stream_cg, gemv_stream_stages,
  * gemv_units_ks, gemv_units_stages, gemv_units_cg, gemv_units_pre, gemv_units_fx, gemv_i8_warps, gemm_tc_bn,
- * gemm_tc_stages, gemm_tc_splitk, peer_wait_limit.  Unknown keys return INVALID_ARGUMENT.  Process-wide;
+ * gemm_tc_stages, gemm_tc_splitk, peer_wait_limit, tp_fused_push.  Unknown keys return INVALID_ARGUMENT.  Process-wide;
  * not part of the drop-in surface. */
 LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_tune_set(const char* key, int value);
 

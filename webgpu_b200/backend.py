@@ -111,7 +111,7 @@ EXPORTED_SYMBOLS = [
     "lux_cuda_kernel_count", "lux_cuda_kernel_name",
     "lux_cuda_peer_comm_create", "lux_cuda_peer_comm_connect", "lux_cuda_peer_comm_connect_ptrs",
     "lux_cuda_peer_comm_window", "lux_cuda_peer_comm_window_bytes", "lux_cuda_peer_allreduce",
-    "lux_cuda_peer_comm_destroy",
+    "lux_cuda_peer_comm_destroy", "lux_cuda_qmlp_tp",
 ]
 PEER_HANDLE_BYTES = 64
 
@@ -203,6 +203,8 @@ class Backend:
         L.lux_cuda_peer_comm_window_bytes.argtypes = [_vp]
         L.lux_cuda_peer_allreduce.restype = C.c_int
         L.lux_cuda_peer_allreduce.argtypes = [_vp, _vp, _vp, C.c_size_t, C.c_uint32, C.c_uint32]
+        L.lux_cuda_qmlp_tp.restype = C.c_int
+        L.lux_cuda_qmlp_tp.argtypes = [_vp, C.POINTER(QMlpDesc)] + [_vp] * 10
         L.lux_cuda_peer_comm_destroy.restype = None
         L.lux_cuda_peer_comm_destroy.argtypes = [_vp]
         L.lux_cuda_context_set_stream.argtypes = [_vp, _vp]
@@ -491,6 +493,16 @@ class Context:
     def peer_allreduce(self, comm, buf: "Buffer", count: int, dtype: int, flags: int = 0) -> None:
         _check(self.backend.lib.lux_cuda_peer_allreduce(self.handle, comm, buf.handle, count, dtype, flags),
                "lux_cuda_peer_allreduce")
+
+    def qmlp_tp(self, x: "Buffer", gate_up: "DeviceQLayer", down: "DeviceQLayer", h: "Buffer", y: "Buffer", M: int,
+                act_dtype: int, comm, flags: int = 0) -> None:
+        """One rank's tensor-parallel FFN: lux_cuda_qmlp on its shards + the all-reduce of y through
+        the push communicator (fused into the down kernel's epilogue at batch <= 2)."""
+        d = QMlpDesc(C.sizeof(QMlpDesc), M, gate_up.K, gate_up.N // 2, down.N, gate_up.group, act_dtype, flags)
+        z = lambda L: L.zeros.handle if L.zeros else None
+        _check(self.backend.lib.lux_cuda_qmlp_tp(self.handle, C.byref(d), x.handle, gate_up.w.handle,
+                                                 gate_up.scales.handle, z(gate_up), down.w.handle, down.scales.handle,
+                                                 z(down), h.handle, y.handle, comm), "lux_cuda_qmlp_tp")
 
     def peer_comm_destroy(self, comm) -> None:
         self.backend.lib.lux_cuda_peer_comm_destroy(comm)

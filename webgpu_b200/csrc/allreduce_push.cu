@@ -101,7 +101,8 @@ __device__ __forceinline__ uint4 load_words(const uint4* src) {
 }
 
 // count is a multiple of 8 (16-byte pieces of the tensor); buf is 16-byte aligned
-template <bool BF16>
+// PUSH = false: the producer kernel's epilogue has already stored this rank's words (same epoch)
+template <bool BF16, bool PUSH>
 __global__ void __launch_bounds__(AR_THREADS, 1) lux_peer_allreduce_push(const PushParams p) {
     __shared__ int s_failed;
     const int tid = threadIdx.x;
@@ -112,7 +113,7 @@ __global__ void __launch_bounds__(AR_THREADS, 1) lux_peer_allreduce_push(const P
     const uint4* src = reinterpret_cast<const uint4*>(p.buf);
 
     // 1. push: piece i becomes four words = two 16-byte stores, into my slot of every window
-    for (size_t i = tid; i < pieces; i += AR_THREADS) {
+    for (size_t i = tid; PUSH && i < pieces; i += AR_THREADS) {
         const uint4 v = src[i];
         const uint4 lo = make_uint4(v.x, epoch, v.y, epoch), hi = make_uint4(v.z, epoch, v.w, epoch);
 #pragma unroll 1
@@ -176,7 +177,50 @@ PeerComm* as_comm(LuxPeerComm* c) { return reinterpret_cast<PeerComm*>(c); }
 
 }  // namespace
 
-const void* kernel_addr_peer_allreduce_push() { return (const void*)lux_peer_allreduce_push<false>; }
+const void* kernel_addr_peer_allreduce_push() { return (const void*)lux_peer_allreduce_push<false, true>; }
+
+bool peer_comm_push_target(LuxPeerComm* comm, size_t count, int device, PushTarget* out) {
+    PeerComm* c = reinterpret_cast<PeerComm*>(comm);
+    if (!c || !out || c->world < 2 || !c->connected || c->device != device) return false;
+    if (count == 0 || count % 8 || count * 2 > c->max_bytes) return false;
+    for (int r = 0; r < MAX_WORLD; r++) out->peer[r] = r < c->world ? c->peer[r] : nullptr;
+    out->epoch = c->epoch;
+    out->max_bytes = c->max_bytes;
+    out->rank = c->rank;
+    out->world = c->world;
+    return true;
+}
+
+LuxBackendError peer_allreduce_launch(Context* ctx, LuxPeerComm* comm, void* buf, size_t buf_bytes, size_t count,
+                                      int dtype, bool push) {
+    PeerComm* c = reinterpret_cast<PeerComm*>(comm);
+    if (!ctx || !c || !buf || count == 0) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    if (dtype != LUX_QDTYPE_F16 && dtype != LUX_QDTYPE_BF16) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+    if (!c->connected && c->world > 1) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    if (count % 8 || (reinterpret_cast<uintptr_t>(buf) & 15)) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+    if (count * 2 > c->max_bytes || count * 2 > buf_bytes) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    if (ctx->device != c->device) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    PushParams p{};
+    for (int r = 0; r < c->world; r++) p.peer[r] = c->peer[r];
+    p.buf = buf;
+    p.epoch = c->epoch;
+    p.status = ctx->d_status;
+    p.max_bytes = c->max_bytes;
+    p.count = count;
+    p.rank = c->rank;
+    p.world = c->world;
+    p.wait_limit = g_tune.peer_wait_limit > 0 ? (unsigned)g_tune.peer_wait_limit : (1u << 22);   // ~0.2 s per word
+    const bool bf16 = dtype == LUX_QDTYPE_BF16;
+    if (push) {
+        if (bf16) lux_peer_allreduce_push<true, true><<<1, AR_THREADS, 0, ctx->stream>>>(p);
+        else lux_peer_allreduce_push<false, true><<<1, AR_THREADS, 0, ctx->stream>>>(p);
+    } else {
+        if (bf16) lux_peer_allreduce_push<true, false><<<1, AR_THREADS, 0, ctx->stream>>>(p);
+        else lux_peer_allreduce_push<false, false><<<1, AR_THREADS, 0, ctx->stream>>>(p);
+    }
+    count_launch("lux_peer_allreduce_push");
+    return map_cuda(cudaGetLastError(), "lux_peer_allreduce_push");
+}
 
 }  // namespace luxcuda
 
@@ -277,30 +321,11 @@ size_t lux_cuda_peer_comm_window_bytes(LuxPeerComm* comm) {
 LuxBackendError lux_cuda_peer_allreduce(LuxBackendContext* context, LuxPeerComm* comm, LuxBackendBuffer* buffer,
                                         size_t count, LuxQDType dtype, uint32_t flags) {
     Context* ctx = reinterpret_cast<Context*>(context);
-    PeerComm* c = as_comm(comm);
     Buffer* b = reinterpret_cast<Buffer*>(buffer);
-    if (!ctx || !c || !b || !b->ptr || count == 0) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
-    if (dtype != LUX_QDTYPE_F16 && dtype != LUX_QDTYPE_BF16) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
-    if (!c->connected && c->world > 1) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
-    if (count % 8 || (reinterpret_cast<uintptr_t>(b->ptr) & 15)) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
-    if (count * 2 > c->max_bytes || count * 2 > b->size) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
-    if (ctx->device != c->device) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    if (!ctx || !comm || !b || !b->ptr) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
     cudaSetDevice(ctx->device);
     std::lock_guard<std::mutex> lock(ctx->mu);
-    PushParams p{};
-    for (int r = 0; r < c->world; r++) p.peer[r] = c->peer[r];
-    p.buf = b->ptr;
-    p.epoch = c->epoch;
-    p.status = ctx->d_status;
-    p.max_bytes = c->max_bytes;
-    p.count = count;
-    p.rank = c->rank;
-    p.world = c->world;
-    p.wait_limit = g_tune.peer_wait_limit > 0 ? (unsigned)g_tune.peer_wait_limit : (1u << 22);   // ~0.2 s per word
-    if (dtype == LUX_QDTYPE_BF16) lux_peer_allreduce_push<true><<<1, AR_THREADS, 0, ctx->stream>>>(p);
-    else lux_peer_allreduce_push<false><<<1, AR_THREADS, 0, ctx->stream>>>(p);
-    count_launch("lux_peer_allreduce_push");
-    LuxBackendError e = map_cuda(cudaGetLastError(), "lux_peer_allreduce_push");
+    LuxBackendError e = peer_allreduce_launch(ctx, comm, b->ptr, b->size, count, (int)dtype, true);
     if (e != LUX_BACKEND_OK) return e;
     return finish_op(ctx, (flags & LUX_QMATMUL_FLAG_NO_SYNC) != 0, "lux_cuda_peer_allreduce");
 }

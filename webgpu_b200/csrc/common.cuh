@@ -83,6 +83,7 @@ struct Tunables {
     int gemv_i4_warps = 0;       // warps per CTA of the int4 skinny kernel
     int gemv_i4_row_tiles = 0;   // 16-row tiles per CTA
     int gemv_i8_warps = 0;
+    int tp_fused_push = 0;       // lux_cuda_qmlp_tp: 0/1 push from the down kernel's epilogue when possible, 2 never
     int peer_wait_limit = 0;     // push all-reduce: polls (40 ns apart) before a wait gives up (default 2^22)
     int gemv_i8_kernel = 0;      // 0 auto, 1 lux_qgemv_i8_g32_f32, 2 lux_qgemv_i8_g32_units_fx
     int gemv_i4_kernel = 0;      // 0 auto, 1 lux_qskinny_i4_g128, 2 lux_qgemv_i4_g128_stream, 3 lux_qgemv_i4_g128_units
@@ -102,6 +103,15 @@ extern Tunables g_tune;
 
 // ---- kernel launchers (defined in the .cu file named after each kernel family) ------
 
+// Where a kernel's epilogue pushes its 16-bit outputs for the push all-reduce (allreduce_push.cu):
+// every rank's window, this rank's number, the communicator's epoch counter.  world <= 1: no push.
+struct PushTarget {
+    unsigned char* peer[8];
+    uint32_t* epoch;
+    unsigned long long max_bytes;
+    int rank, world;
+};
+
 struct QArgs {
     int M, N, K, G;              // G = K / group
     const void* x;
@@ -111,7 +121,14 @@ struct QArgs {
     void* y;
     int x_dtype, scale_dtype, y_dtype;
     bool swiglu;
+    const PushTarget* push = nullptr;   // set: push the outputs into the peers' windows instead of writing y
 };
+
+// allreduce_push.cu: the push target of a connected communicator (false if it cannot take `count`
+// 16-bit elements), and the all-reduce launch with or without its own push phase
+bool peer_comm_push_target(LuxPeerComm* comm, size_t count, int device, PushTarget* out);
+LuxBackendError peer_allreduce_launch(Context* ctx, LuxPeerComm* comm, void* buf, size_t buf_bytes, size_t count,
+                                      int dtype, bool push);
 
 LuxBackendError launch_qgemv_i8(Context* ctx, const QArgs& a);
 LuxBackendError launch_qgemv_i8_units(Context* ctx, const QArgs& a);    // NOT_SUPPORTED if the shape does not fit

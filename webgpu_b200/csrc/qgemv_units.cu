@@ -136,6 +136,7 @@ struct UnitsParams {
     int rows_cap;           // weight rows (gate + up) whose scales / zero-points are staged per CTA
     uint32_t* status;       // device status word for a wait that gave up (may be null)
     uint32_t inv_upt, inv_U; // ceil(2^32 / (units per tile)), ceil(2^32 / U): division-free unit table
+    PushTarget push;        // world > 1: the outputs go to the peers' all-reduce windows instead of y
 };
 
 // Shared memory: [x staged: M * xstride][xsum: G * 8*MT * 8][scales: rows_cap * G f16]
@@ -845,6 +846,35 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
         __syncthreads();
         return;
     }
+    if (!SWIGLU && p.push.world > 1) {
+        // Fused collective: instead of writing y, every pair of outputs goes straight into slot
+        // [parity][my rank] of EVERY rank's all-reduce window as one self-validating 8-byte word
+        // {two f16, epoch} (plain stores to peer memory; allreduce_push.cu waits for them and sums).
+        // The epoch is the communicator's counter + 1: the all-reduce kernel that follows on this
+        // stream computes the same value and advances the counter.
+        const uint32_t epoch = *p.push.epoch + 1u;
+        const size_t slot = ((size_t)(epoch & 1u) * p.push.world + p.push.rank) * (2 * p.push.max_bytes);
+        const int npairs = ntiles * 8 * MM;
+        for (int o = tid; o < npairs; o += UW * 32) {
+            const int m = o % MM, r2 = (o / MM) & 7, tl = o / (8 * MM);
+            const float* v0 = part + ((size_t)(tl * p.U) * 16 + 2 * r2) * MM + m;
+            float s0 = 0.0f, s1 = 0.0f;
+            for (int k = 0; k < p.U; k++) {                       // fixed order: deterministic
+                s0 += v0[(size_t)k * 16 * MM];
+                s1 += v0[(size_t)k * 16 * MM + MM];
+            }
+            const __half2 h2 = __floats2half2_rn(s0, s1);
+            const uint32_t pk = *reinterpret_cast<const uint32_t*>(&h2);
+            const size_t word = ((size_t)m * p.Nout + (size_t)(tile_lo + tl) * 16 + 2 * r2) >> 1;
+#pragma unroll 1
+            for (int r = 0; r < p.push.world; r++) {
+                uint2* dst = reinterpret_cast<uint2*>(p.push.peer[r] + slot) + word;
+                asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(pk), "r"(epoch) : "memory");
+            }
+        }
+        TRACE(9);
+        return;
+    }
     const int nout = ntiles * 16 * MM;
     for (int o = tid; o < nout; o += UW * 32) {
         const int m = o % MM, r = (o / MM) & 15, tl = o / (16 * MM);
@@ -992,6 +1022,12 @@ LuxBackendError launch_qgemv_i4_units(Context* ctx, const QArgs& a) {
     p.S = std::max(S, 1);
     p.S0 = std::min(p.S, g_tune.gemv_units_pre > 0 ? g_tune.gemv_units_pre : 1);
     p.status = ctx->d_status;
+    p.push = PushTarget{};
+    if (a.push) {
+        // only the fixed-point variant pushes, and only plain (non-SwiGLU) outputs with an even row count
+        if (!fx || a.swiglu || (nout & 1)) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+        p.push = *a.push;
+    }
     {
         const uint32_t upt = (uint32_t)(nacc * U);
         p.inv_upt = upt > 1 ? (uint32_t)((((uint64_t)1 << 32) + upt - 1) / upt) : 0u;

@@ -247,6 +247,61 @@ LuxBackendError lux_cuda_qunpack(LuxBackendContext* context, const LuxQMatmulDes
     return finish_op(ctx, c.no_sync, "lux_cuda_qunpack");
 }
 
+// The tensor-parallel FFN of one rank: gate_up + SwiGLU, down, and the all-reduce of the partial
+// outputs through the push communicator.  When the down projection runs in the warp-autonomous
+// fixed-point kernel (batch <= 2), its final reduction stores the outputs straight into every
+// rank's window and the second kernel only waits and sums; otherwise down writes y and the
+// all-reduce kernel pushes it.
+LuxBackendError lux_cuda_qmlp_tp(LuxBackendContext* context, const LuxQMlpDesc* d, LuxBackendBuffer* x,
+                                 LuxBackendBuffer* w_gate_up, LuxBackendBuffer* s_gate_up, LuxBackendBuffer* z_gate_up,
+                                 LuxBackendBuffer* w_down, LuxBackendBuffer* s_down, LuxBackendBuffer* z_down,
+                                 LuxBackendBuffer* h_scratch, LuxBackendBuffer* y, LuxPeerComm* comm) {
+    Context* ctx = as_ctx(context);
+    if (!ctx || !d || d->struct_size < sizeof(LuxQMlpDesc) || !comm) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    if (!x || !w_gate_up || !s_gate_up || !w_down || !s_down || !h_scratch || !y) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    if (d->act_dtype != LUX_QDTYPE_F16 && d->act_dtype != LUX_QDTYPE_BF16) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+    LuxQMatmulDesc gu{};
+    gu.struct_size = sizeof(gu);
+    gu.M = d->M; gu.N = 2 * d->I; gu.K = d->K;
+    gu.bits = 4; gu.group_size = d->group_size;
+    gu.x_dtype = d->act_dtype; gu.scale_dtype = LUX_QDTYPE_F16; gu.y_dtype = d->act_dtype;
+    gu.flags = LUX_QMATMUL_FLAG_SWIGLU | LUX_QMATMUL_FLAG_NO_SYNC;
+    LuxBackendError e = lux_cuda_qmatmul(context, &gu, x, w_gate_up, s_gate_up, z_gate_up, h_scratch);
+    if (e != LUX_BACKEND_OK) return e;
+    LuxQMatmulDesc dn = gu;
+    dn.N = d->H; dn.K = d->I;
+    dn.flags = LUX_QMATMUL_FLAG_NO_SYNC;
+    const size_t count = (size_t)d->M * d->H;
+    Buffer* by = as_buf(y);
+    bool fused = false;
+    PushTarget target{};
+    if (d->M <= 2 && d->act_dtype == LUX_QDTYPE_F16 && g_tune.tp_fused_push != 2 &&
+        peer_comm_push_target(comm, count, ctx->device, &target)) {
+        Buffer *bh = as_buf(h_scratch), *bw = as_buf(w_down), *bs = as_buf(s_down), *bz = as_buf(z_down);
+        Checked c{};
+        e = check_desc(&dn, bz != nullptr, true, &c);
+        if (e == LUX_BACKEND_OK) e = bind_weights(c, bw, bs, bz);
+        if (e == LUX_BACKEND_OK && c.route == LUX_QROUTE_SKINNY_I4 && bh->ptr && by->ptr && aligned16(bh->ptr) &&
+            aligned16(by->ptr) && bh->size >= (size_t)d->M * d->I * 2 && by->size >= count * 2) {
+            c.a.x = bh->ptr;
+            c.a.y = by->ptr;
+            c.a.push = &target;
+            cudaSetDevice(ctx->device);
+            e = launch_qgemv_i4_units(ctx, c.a);
+            if (e == LUX_BACKEND_OK) fused = true;
+            else if (e != LUX_BACKEND_ERROR_NOT_SUPPORTED) return e;
+        }
+    }
+    if (!fused) {
+        e = lux_cuda_qmatmul(context, &dn, h_scratch, w_down, s_down, z_down, y);
+        if (e != LUX_BACKEND_OK) return e;
+    }
+    cudaSetDevice(ctx->device);
+    e = peer_allreduce_launch(ctx, comm, by->ptr, by->size, count, (int)d->act_dtype, !fused);
+    if (e != LUX_BACKEND_OK) return e;
+    return finish_op(ctx, (d->flags & LUX_QMATMUL_FLAG_NO_SYNC) != 0, "lux_cuda_qmlp_tp");
+}
+
 LuxBackendError lux_cuda_qmlp(LuxBackendContext* context, const LuxQMlpDesc* d, LuxBackendBuffer* x,
                               LuxBackendBuffer* w_gate_up, LuxBackendBuffer* s_gate_up, LuxBackendBuffer* z_gate_up,
                               LuxBackendBuffer* w_down, LuxBackendBuffer* s_down, LuxBackendBuffer* z_down,
@@ -275,7 +330,7 @@ LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_tune_set(const char* key, int val
     if (!key) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
     struct { const char* k; int* v; } table[] = {
         {"gemv_i4_warps", &g_tune.gemv_i4_warps},   {"gemv_i4_row_tiles", &g_tune.gemv_i4_row_tiles},
-        {"gemv_i8_warps", &g_tune.gemv_i8_warps},   {"gemv_i8_kernel", &g_tune.gemv_i8_kernel}, {"peer_wait_limit", &g_tune.peer_wait_limit},   {"gemm_tc_bn", &g_tune.gemm_tc_bn},
+        {"gemv_i8_warps", &g_tune.gemv_i8_warps},   {"gemv_i8_kernel", &g_tune.gemv_i8_kernel}, {"peer_wait_limit", &g_tune.peer_wait_limit}, {"tp_fused_push", &g_tune.tp_fused_push},   {"gemm_tc_bn", &g_tune.gemm_tc_bn},
         {"gemv_i4_kernel", &g_tune.gemv_i4_kernel}, {"gemv_stream_cg", &g_tune.gemv_stream_cg},
         {"gemv_stream_stages", &g_tune.gemv_stream_stages}, {"gemv_stream_warps", &g_tune.gemv_stream_warps},
         {"gemv_units_ks", &g_tune.gemv_units_ks}, {"gemv_units_stages", &g_tune.gemv_units_stages}, {"gemv_units_cg", &g_tune.gemv_units_cg}, {"gemv_units_pre", &g_tune.gemv_units_pre}, {"gemv_units_fx", &g_tune.gemv_units_fx},

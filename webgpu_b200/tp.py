@@ -129,14 +129,16 @@ class TPMlp:
         """x[:M] must already be in ``self.x``.  Returns the view ``self.y[:M]``."""
         torch = self.torch
         self.ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+        out = self.y[:M]
+        if all_reduce and self.world > 1 and self.peer is not None and (M * self.H) % 8 == 0:
+            # FFN + push all-reduce in one call (the down kernel pushes from its epilogue at batch <= 2)
+            self.ctx.qmlp_tp(self._bx, self.gate_up, self.down, self._bh, self._by, M, self.act_code,
+                             self.peer.comm, flags=self.B.FLAG_NO_SYNC)
+            return out
         self.ctx.qmlp(self._bx, self.gate_up, self.down, self._bh, self._by, M, self.act_code,
                       flags=self.B.FLAG_NO_SYNC)
-        out = self.y[:M]
         if all_reduce and self.world > 1:
-            if self.peer is not None and (M * self.H) % 8 == 0:
-                self.peer(self._by, M * self.H, self.act_code, flags=self.B.FLAG_NO_SYNC)
-            else:
-                torch.distributed.all_reduce(out, group=self.group)
+            torch.distributed.all_reduce(out, group=self.group)
         return out
 
 
