@@ -544,7 +544,11 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
     uint4 x_first = make_uint4(0u, 0u, 0u, 0u);
     if (tid < npieces) x_first = __ldg(reinterpret_cast<const uint4*>(p.x) + tid);
 
-    // ---- barriers, unit table, first weight request: as early as possible ---------------------
+    // ---- barriers and the first weight request: the very first thing every warp does ----------
+    // exact division of a small number by a small constant: multiply by ceil(2^32 / d)
+    auto div_small = [](uint32_t n, uint32_t d, uint32_t inv) { return d == 1u ? n : __umulhi(n, inv); };
+    uint64_t policy = 0;
+    int issued = 0;
     if (lane == 0) {
         if (warp == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
@@ -552,9 +556,17 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
         }
         for (int s0 = 0; s0 < p.S; s0++) mbar_init(bar0 + 8u * (uint32_t)s0, 1u);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+        if (my_chunks > 0) {
+            // this warp's first unit is unit `warp` of the CTA: its first chunk goes out before the
+            // unit table exists
+            const int tl = (int)div_small((uint32_t)warp, (uint32_t)upt, p.inv_upt), rem = warp - tl * upt;
+            const int a = (int)div_small((uint32_t)rem, (uint32_t)p.U, p.inv_U), k = rem - a * p.U;
+            mbar_expect_tx(bar0, (uint32_t)CHUNK);
+            tma_load_3d(smem_u32(fifo), &map_w, 0, (tile_lo + tl) * 16 + a * p.up_row_offset, (k * p.KS) >> 1, bar0, policy);
+            issued = 1;
+        }
     }
-    // exact division of a small number by a small constant: multiply by ceil(2^32 / d)
-    auto div_small = [](uint32_t n, uint32_t d, uint32_t inv) { return d == 1u ? n : __umulhi(n, inv); };
     for (int ul = warp + lane * UW; ul < nunits; ul += 32 * UW) {
         const int tl = (int)div_small((uint32_t)ul, (uint32_t)upt, p.inv_upt), rem = ul - tl * upt;
         const int a = (int)div_small((uint32_t)rem, (uint32_t)p.U, p.inv_U), k = rem - a * p.U;
@@ -566,9 +578,7 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
     struct Cursor { int ui, ci; };
     auto advance = [&](Cursor& c) { if (++c.ci == NC) { c.ci = 0; ++c.ui; } };
     Cursor cload{0, 0}, ccur{0, 0};
-    int issued = 0;
-    uint64_t policy = 0;
-    if (lane == 0) asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    if (issued) advance(cload);                           // lane 0: the first chunk is already on its way
     // lane 0 only: ask for the next chunk into FIFO slot `slot` (the slot's barrier is armed first)
     auto issue_chunk = [&](int slot) {
         const int4 u = utab[warp + cload.ui * UW];
@@ -578,8 +588,6 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
         advance(cload);
         issued++;
     };
-    // the first chunk now; the rest of the FIFO once x is converted (see below)
-    if (lane == 0 && my_chunks > 0) issue_chunk(0);
     TRACE(10);
 
     // ---- this CTA's scales and zero-points (one cp.async group), requested before the bulk of
