@@ -156,7 +156,9 @@ lux_qgemv_i8_g32_units_fx(const __grid_constant__ CUtensorMap map_w, const I8Uni
         xb = __ldg(reinterpret_cast<const uint4*>(p.x) + 2 * tid + 1);
     }
 
-    // ---- barriers, unit table, first weight request: as early as possible ---------------------
+    // ---- barriers and the first weight request: the very first thing every warp does ----------
+    uint64_t policy = 0;
+    int issued = 0;
     if (lane == 0) {
         if (warp == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
@@ -164,6 +166,15 @@ lux_qgemv_i8_g32_units_fx(const __grid_constant__ CUtensorMap map_w, const I8Uni
         }
         for (int s0 = 0; s0 < p.S; s0++) mbar_init(bar0 + 8u * (uint32_t)s0, 1u);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+        if (my_chunks > 0) {
+            // this warp's first unit is unit `warp` of the CTA: its first chunk goes out before the
+            // unit table exists (a line of the tensor map is 128 K = 4 groups)
+            const int tl = p.U == 1 ? warp : (int)__umulhi((uint32_t)warp, p.inv_U), k = warp - tl * p.U;
+            mbar_expect_tx(bar0, (uint32_t)CHUNK);
+            tma_load_3d(smem_u32(fifo), &map_w, 0, (tile_lo + tl) * 16, (k * p.KS) >> 2, bar0, policy);
+            issued = 1;
+        }
     }
     for (int ul = warp + lane * UW; ul < nunits; ul += 32 * UW) {
         const int tl = p.U == 1 ? ul : (int)__umulhi((uint32_t)ul, p.inv_U), k = ul - tl * p.U;
@@ -175,11 +186,8 @@ lux_qgemv_i8_g32_units_fx(const __grid_constant__ CUtensorMap map_w, const I8Uni
     struct Cursor { int ui, ci; };
     auto advance = [&](Cursor& c) { if (++c.ci == NC) { c.ci = 0; ++c.ui; } };
     Cursor cload{0, 0}, ccur{0, 0};
-    int issued = 0;
-    uint64_t policy = 0;
-    if (lane == 0) asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
-    // lane 0 only: ask for the next chunk into FIFO slot `slot` (the slot's barrier is armed first);
-    // a line of the tensor map is 128 K = 4 groups
+    if (issued) advance(cload);                           // lane 0: the first chunk is already on its way
+    // lane 0 only: ask for the next chunk into FIFO slot `slot` (the slot's barrier is armed first)
     auto issue_chunk = [&](int slot) {
         const int2 u = utab[warp + cload.ui * UW];
         const uint32_t bar = bar0 + 8u * (uint32_t)slot;
@@ -189,7 +197,6 @@ lux_qgemv_i8_g32_units_fx(const __grid_constant__ CUtensorMap map_w, const I8Uni
         advance(cload);
         issued++;
     };
-    if (lane == 0 && my_chunks > 0) issue_chunk(0);
 
     // ---- this CTA's scales (one cp.async group): rows are contiguous ---------------------------
     {
