@@ -412,13 +412,43 @@ def bench_tp(args, peaks):
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
+    # One CUDA graph per weight copy holding the whole step a caller makes: x from pinned host
+    # memory, the FFN with its collective, y back to pinned host memory; each timed step is one
+    # replay plus one stream wait (the host reads y after every step).  Eager launches if the
+    # capture is refused.
+    def e2e_step(m):
+        m.x[:M].copy_(xh, non_blocking=True)
+        out = m.forward(M)
+        yh.copy_(out, non_blocking=True)
+
+    e2e_path = "CUDA graph per step: pinned H2D copy of x, FFN + collective, D2H copy of y; one stream wait per step"
+    graphs = None
+    try:
+        with torch.cuda.stream(rig.stream):
+            for m in mlps:
+                e2e_step(m)
+            rig.stream.synchronize()
+            graphs = []
+            for m in mlps:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=rig.stream, capture_error_mode="relaxed"):
+                    e2e_step(m)
+                graphs.append(g)
+            for g in graphs:
+                g.replay()
+            rig.stream.synchronize()
+    except Exception as exc:   # noqa: BLE001
+        graphs = None
+        e2e_path = f"eager launches per step (graph capture failed: {type(exc).__name__})"
+    if world > 1:
+        dist.barrier()
     t0 = time.perf_counter()
     with torch.cuda.stream(rig.stream):
         for i in range(n_e2e):
-            m = mlps[i % copies]
-            m.x[:M].copy_(xh, non_blocking=True)
-            out = m.forward(M)
-            yh.copy_(out, non_blocking=True)
+            if graphs is not None:
+                graphs[i % copies].replay()
+            else:
+                e2e_step(mlps[i % copies])
             rig.stream.synchronize()
     e2e_sec = (time.perf_counter() - t0) / n_e2e
     t = torch.tensor([e2e_sec], device="cuda", dtype=torch.float64)
@@ -448,7 +478,7 @@ def bench_tp(args, peaks):
                          "peak_source": peaks["source"], "note": "per GPU, both FFN kernels, without the all-reduce",
                          "us_compute_only": sec_compute * 1e6, "us_with_allreduce": sec * 1e6},
             "e2e": {"value": total_wbytes / e2e_sec / 1e9, "unit": "GB/s", "h2d_bytes_per_step": int(x.nbytes),
-                    "d2h_bytes_per_step": int(M * d["H"] * 2), "us_per_step": e2e_sec * 1e6},
+                    "d2h_bytes_per_step": int(M * d["H"] * 2), "us_per_step": e2e_sec * 1e6, "path": e2e_path},
             "gpu_launches": (3 if peer is not None else 2) * args.steps, "clocks": clocks, "parity_rel_l2": parity,
         }
     ctx.sync()                       # raises if a bounded device-side wait gave up during the run
