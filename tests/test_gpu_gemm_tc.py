@@ -44,18 +44,36 @@ def test_gemm_small_shapes(ctx, backend, dtype, M, N, K):
 
 
 @pytest.mark.parametrize("bn,stages", [(64, 2), (64, 4), (128, 3), (128, 6)])
-def test_gemm_tile_and_stage_choices(ctx, backend, bn, stages):
+@pytest.mark.parametrize("ma", [1, 2])
+def test_gemm_tile_and_stage_choices(ctx, backend, bn, stages, ma):
+    """Every weight-tile width, pipeline depth and number of batch tiles per CTA gives the same
+    answer; 160 rows: the second batch tile of a CTA is partly (ma = 1) or mostly (ma = 2) empty."""
     x = synth.activations(160, 1024, "bf16", 32, "gt.x")
     layer = synth.int4_layer(256, 1024, 32, "gt")
     ref = _oracle(x, layer)
     backend.tune("gemm_tc_bn", bn)
     backend.tune("gemm_tc_stages", stages)
+    backend.tune("gemm_tc_ma", ma)
     try:
         y = _run(ctx, x, layer)
     finally:
         backend.tune("gemm_tc_bn", 0)
         backend.tune("gemm_tc_stages", 0)
+        backend.tune("gemm_tc_ma", 0)
     assert orc.rel_l2(y, ref) < TOL_16
+    assert ctx.last_device_status() == 0
+
+
+@pytest.mark.parametrize("M", [129, 256, 300, 512])
+def test_gemm_two_batch_tiles(ctx, backend, M):
+    """Batches above 128 rows use two batch tiles per CTA by default (one converted weight tile,
+    two accumulators); ragged last tiles included."""
+    x = synth.activations(M, 512, "f16", 33, f"g2.x{M}")
+    layer = synth.int4_layer(192, 512, 33, "g2")
+    ref = _oracle(x, layer)
+    y = _run(ctx, x, layer)
+    assert orc.rel_l2(y, ref) < TOL_16
+    assert ctx.last_device_status() == 0
 
 
 def test_config3_prefill_gemm(ctx):

@@ -1,0 +1,97 @@
+"""GPU parity of lux_qgemm_i4_tc_wa (converted weights as the tensor-memory A operand,
+128 weight rows x 256 batch rows per CTA, optional split-K over a CTA pair) against the
+CPU oracle, through the same C-ABI call as every other quantized matmul.
+
+Tolerance: relative L2 <= 5e-3 (16-bit outputs), oracle evaluated with weights rounded
+once to the activation type as the kernel does.
+"""
+import numpy as np
+import pytest
+
+from oracle import oracle as orc
+from webgpu_b200 import backend as B
+from webgpu_b200 import synth
+
+pytestmark = pytest.mark.gpu
+TOL_16 = 5e-3
+
+
+def _run(ctx, x, layer):
+    L = ctx.upload_layer(layer)
+    xb = ctx.upload(x)
+    M = x.shape[0]
+    yb = ctx.alloc(M * layer.N * 2)
+    ctx.qmatmul(xb, L, yb, M, B.np_dtype_code(x))
+    return yb.to_host(x.dtype, (M, layer.N))
+
+
+def _oracle(x, layer, rows=None):
+    xs = x if rows is None else x[rows]
+    return orc.qmatmul(xs, *layer.triple, bits=4, group=128, w_round=orc.dtype_code(x))
+
+
+class _Tuned:
+    def __init__(self, backend, **kv):
+        self.b, self.kv = backend, kv
+
+    def __enter__(self):
+        for k, v in self.kv.items():
+            self.b.tune(k, v)
+
+    def __exit__(self, *exc):
+        for k in self.kv:
+            self.b.tune(k, 0)
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+@pytest.mark.parametrize("splitk", [1, 2])
+@pytest.mark.parametrize("M,N,K", [(256, 128, 256), (129, 128, 512), (300, 256, 512), (512, 384, 1024), (40, 128, 256)])
+def test_wa_shapes(ctx, backend, dtype, splitk, M, N, K):
+    """Whole and ragged batch tiles, one and several weight tiles, both K splits; the kernel is
+    forced (gemm_tc_kernel = 2) so that batches of 128 rows and fewer run it too."""
+    x = synth.activations(M, K, dtype, 41, f"wa.{M}.{K}")
+    layer = synth.int4_layer(N, K, 41, f"wa.{N}.{K}")
+    with _Tuned(backend, gemm_tc_kernel=2, gemm_tc_splitk=splitk):
+        y = _run(ctx, x, layer)
+        assert backend.last_kernel_name().startswith("lux_qgemm_i4_tc_wa")
+    err = orc.rel_l2(y, _oracle(x, layer))
+    assert err < TOL_16, err
+    assert ctx.last_device_status() == 0
+
+
+@pytest.mark.parametrize("groups,stages", [(2, 2), (2, 6), (3, 4), (4, 3), (4, 7)])
+def test_wa_groups_and_stages(ctx, backend, groups, stages):
+    """Every number of converter groups and ring depth gives the same bits."""
+    x = synth.activations(384, 1024, "bf16", 42, "wag.x")
+    layer = synth.int4_layer(256, 1024, 42, "wag")
+    with _Tuned(backend, gemm_tc_kernel=2):
+        base = _run(ctx, x, layer)
+    with _Tuned(backend, gemm_tc_kernel=2, gemm_tc_groups=groups, gemm_tc_stages=stages):
+        y = _run(ctx, x, layer)
+    assert np.array_equal(y.view(np.uint16), base.view(np.uint16))
+    assert orc.rel_l2(y, _oracle(x, layer)) < TOL_16
+    assert ctx.last_device_status() == 0
+
+
+def test_wa_symmetric_weights(ctx, backend):
+    """No zero-point table: the symmetric special case (zero-point 8)."""
+    x = synth.activations(256, 512, "f16", 43, "was.x")
+    layer = synth.int4_layer(128, 512, 43, "was", symmetric=True)
+    with _Tuned(backend, gemm_tc_kernel=2):
+        y = _run(ctx, x, layer)
+    assert orc.rel_l2(y, _oracle(x, layer)) < TOL_16
+
+
+def test_wa_is_default_above_128_rows(ctx, backend):
+    """Config 3 (512 x 4096 x 4096, bf16) takes this kernel by default and agrees with the
+    other tcgen05 kernel to accumulation order."""
+    x, layer = synth.config3()
+    y = _run(ctx, x, layer)
+    assert backend.last_kernel_name() == "lux_qgemm_i4_tc_wa_bf16"
+    rows = np.arange(0, 512, 37)
+    assert orc.rel_l2(y[rows], _oracle(x, layer, rows)) < TOL_16
+    with _Tuned(backend, gemm_tc_kernel=1):
+        y_old = _run(ctx, x, layer)
+        assert backend.last_kernel_name() == "lux_qgemm_i4_tc_bf16"
+    assert orc.rel_l2(y, y_old) < 1e-3
+    assert ctx.last_device_status() == 0

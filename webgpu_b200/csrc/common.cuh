@@ -97,7 +97,10 @@ struct Tunables {
     int gemv_units_fx = 0;       // units kernel, batch <= 2: 0/1 block-fixed-point int8 variant, 2 f16 variant
     int gemm_tc_bn = 0;          // N tile of the tcgen05 GEMM
     int gemm_tc_stages = 0;
-    int gemm_tc_splitk = 0;
+    int gemm_tc_splitk = 0;      // weights-in-TMEM GEMM: K splits over a CTA pair, 1 or 2 (0 = choose)
+    int gemm_tc_groups = 0;      // weights-in-TMEM GEMM: converter groups of four warps, 2..4
+    int gemm_tc_kernel = 0;      // 0 auto, 1 lux_qgemm_i4_tc, 2 lux_qgemm_i4_tc_wa wherever it applies
+    int gemm_tc_ma = 0;          // GEMM: batch tiles (128 rows) per CTA, 1 or 2 (0 = choose)
 };
 extern Tunables g_tune;
 
@@ -136,6 +139,7 @@ LuxBackendError launch_qskinny_i4(Context* ctx, const QArgs& a);
 LuxBackendError launch_qgemv_i4_stream(Context* ctx, const QArgs& a);   // NOT_SUPPORTED if the shape does not fit
 LuxBackendError launch_qgemv_i4_units(Context* ctx, const QArgs& a);    // NOT_SUPPORTED if the shape does not fit
 LuxBackendError launch_qgemm_i4_tc(Context* ctx, const QArgs& a);
+LuxBackendError launch_qgemm_i4_tc_wa(Context* ctx, const QArgs& a);    // NOT_SUPPORTED if the shape does not fit
 LuxBackendError launch_qdequant(Context* ctx, const QArgs& a, int bits);
 LuxBackendError launch_qunpack(Context* ctx, const QArgs& a, int bits);
 

@@ -25,186 +25,20 @@
 // outstanding copies land, frees its TMEM and returns; the host reports DEVICE_LOST.
 // No cluster launch and no multicast anywhere: the same kernel serves multi-GPU runs.
 #include "common.cuh"
+#include "tc_ptx.cuh"
 
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
 #include <algorithm>
+#include <type_traits>
 
 namespace luxcuda {
 
 namespace {
 
-constexpr int BM = 128;              // batch rows per CTA (UMMA M)
-constexpr int BK = 64;               // K per pipeline stage: one 128-byte swizzle row
-constexpr int NUM_DQ_WARPS = 8;
-constexpr int NUM_THREADS = (2 + NUM_DQ_WARPS) * 32;
-// one try_wait may suspend for a few microseconds; 2^15 of them bound a wait to ~0.1 s
-constexpr uint32_t WAIT_LIMIT = 1u << 15;
+using namespace tcptx;
 
-// ---- PTX wrappers ----------------------------------------------------------------------
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-// Bounded wait.  Returns false if the phase did not complete within WAIT_LIMIT polls or
-// another thread of the CTA already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
-    for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return true;
-        if ((it & 31u) == 31u && *abort_flag) return false;
-    }
-    *abort_flag = 1u;
-    return false;
-}
-// Warp-level wait: lane 0 polls (32 lanes polling the same barrier word are served one by
-// one), the outcome is broadcast, and __syncwarp orders the other lanes' later reads after
-// lane 0's acquire.  Must be called by a converged warp.
-__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, int lane) {
-    bool ok = true;
-    if (lane == 0) ok = mbar_wait(bar, parity, abort_flag);
-    __syncwarp();
-    return __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
-}
-// Plain (untiled) bulk copy global -> shared: 16-byte aligned addresses, size a multiple of 16.
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-__device__ __forceinline__ uint32_t prmt_b32(uint32_t a, uint32_t b, uint32_t sel) {
-    uint32_t d;
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
-    return d;
-}
-__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t mask, uint32_t orv) {
-    uint32_t d;
-    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(mask), "r"(orv));
-    return d;
-}
-
-// Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows 128 bytes apart,
-// 8-row groups 1024 bytes apart (SBO); version 1 (sm_100); LBO unused for swizzled
-// K-major and set to 1.  Field positions: start[0,14) LBO[16,30) SBO[32,46)
-// version[46,48) layout[61,64), all addresses in 16-byte units.
-__device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
-    const uint32_t lo = ((smem_addr & 0x3FFFFu) >> 4) | (1u << 16);
-    const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
-    return ((uint64_t)hi << 32) | lo;
-}
-
-// Instruction descriptor for kind::f16: D=f32 (bits 4-5 = 1), A/B format at bits 7-9 /
-// 10-12 (0 = f16, 1 = bf16), both K-major (bits 15, 16 = 0), N>>3 at bits 17-22,
-// M>>4 at bits 24-28.
-__host__ __device__ constexpr uint32_t make_idesc(bool bf16, int n) {
-    return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((uint32_t)(n >> 3) << 17) |
-           ((uint32_t)(BM >> 4) << 24);
-}
-
-// ---- dequantization of one packed word (8 nibbles) to 8 elements in K order ---------------
-
-// bf16: pair (n_lo, n_hi) of byte i becomes bf16x2 (128 + n_lo, 16 + n_hi): the low nibble
-// sits in mantissa bits 0-3 under exponent 2^7, the high nibble (after >>1) in mantissa
-// bits 3-6 under exponent 2^4.  bz = (128 + zp, 16 + zp).  Then
-//   d = pair - bz (exact), c = d * s_lo (exact: 4 x 3 bits), r = fma(d, s_hi, c) (one rounding)
-// which is bf16_rne(f32(q - zp) * f32(scale)).
-__device__ __forceinline__ uint4 dequant_word_bf16(uint32_t w, uint32_t bz, uint32_t s_hi2, uint32_t s_lo2) {
-    const uint32_t u = w >> 1;
-    uint32_t out[4];
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        const uint32_t p = prmt_b32(w, u, (uint32_t)(i | ((4 + i) << 8)));      // byte0 = w.b[i], byte2 = u.b[i]
-        const uint32_t v = lop3_and_or(p, 0x0078000fu, 0x41804300u);
-        uint32_t d, c, r;
-        asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(v), "r"(bz));
-        asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(c) : "r"(d), "r"(s_lo2));
-        asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(d), "r"(s_hi2), "r"(c));
-        out[i] = r;
-    }
-    return make_uint4(out[0], out[1], out[2], out[3]);
-}
-
-// f16: byte i replicated, low nibble under 0x6400 (1024 + n), high nibble in place under
-// 0x5400 (64 + n); hz = (1024 + zp, 64 + zp); one correctly rounded multiply by the scale.
-__device__ __forceinline__ uint4 dequant_word_f16(uint32_t w, uint32_t hz, uint32_t s2) {
-    uint32_t out[4];
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        const uint32_t p = prmt_b32(w, w, (uint32_t)(i * 0x1111));
-        const uint32_t v = lop3_and_or(p, 0x00f0000fu, 0x54006400u);
-        uint32_t d, r;
-        asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(v), "r"(hz));
-        asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(d), "r"(s2));
-        out[i] = r;
-    }
-    return make_uint4(out[0], out[1], out[2], out[3]);
-}
-
-__device__ __forceinline__ float silu_f32(float x) { return x / (1.0f + __expf(-x)); }
-
-template <bool BF16> __device__ __forceinline__ uint32_t pack2(float a, float b);
-template <> __device__ __forceinline__ uint32_t pack2<true>(float a, float b) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
-template <> __device__ __forceinline__ uint32_t pack2<false>(float a, float b) {
-    __half2 v = __floats2half2_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
 
 struct GemmParams {
     const __half* scales;     // [Nw, G]
@@ -222,15 +56,19 @@ struct GemmParams {
 //   [A ring: stages x 16 KB][B ring: stages x NB*128 B][packed ring: stages x NB*32 B]
 //   [barriers + tmem slot: 256 B][scales NB x G f16, zero-points NB x ZS bytes (if meta_smem)]
 // NB = BN (or 2*BN with SwiGLU: gate rows then up rows).
-template <int BN, bool SWIGLU, bool BF16>
+// MA = batch tiles (128 rows each) per CTA: the converted weight tile of a stage feeds MA
+// accumulators, so a weight tile is converted once per MA*128 batch rows.
+template <int BN, bool SWIGLU, bool BF16, int MA>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 lux_qgemm_i4_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                 const GemmParams p) {
     constexpr int NB = SWIGLU ? 2 * BN : BN;                 // B-tile rows = UMMA N
-    constexpr int A_BYTES = BM * 128;
+    constexpr int A_BYTES = MA * BM * 128;                   // MA tiles of 128 rows x 64 K, one TMA box
     constexpr int B_BYTES = NB * 128;
     constexpr int Q_BYTES = NB * 32;
-    constexpr uint32_t TMEM_COLS = NB <= 32 ? 32 : (NB <= 64 ? 64 : (NB <= 128 ? 128 : 256));
+    constexpr int ACC_COLS = MA * NB;                        // accumulator a at columns [a*NB, +NB)
+    constexpr uint32_t TMEM_COLS = ACC_COLS <= 32 ? 32 : (ACC_COLS <= 64 ? 64 : (ACC_COLS <= 128 ? 128 : (ACC_COLS <= 256 ? 256 : 512)));
+    static_assert(ACC_COLS <= 512, "TMEM holds 512 columns");
     static_assert(NB % 16 == 0 && NB >= 16 && NB <= 256, "UMMA N for M=128");
     static_assert((NB * 2) % (NUM_DQ_WARPS * 32) == 0 || (NUM_DQ_WARPS * 32) % (NB * 2) == 0, "dequant mapping");
 
@@ -251,7 +89,7 @@ lux_qgemm_i4_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.x * BN;            // first output column (weight row) of this tile
-    const int m0 = blockIdx.y * BM;
+    const int m0 = blockIdx.y * (MA * BM);
     const int KB = p.K / BK;
 
     const uint32_t bar0 = smem_u32(bars);
@@ -326,9 +164,12 @@ lux_qgemm_i4_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 const uint64_t b_desc = make_kmajor_sw128_desc(smem_u32(b_ring + (size_t)s * B_BYTES));
 #pragma unroll
                 for (int k = 0; k < BK / 16; k++) {
-                    // +32 bytes per 16 K inside the swizzle row: +2 in the 16-byte address field
-                    umma_f16(tmem_base, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc,
-                             (kb | k) != 0 ? 1u : 0u);
+                    // +32 bytes per 16 K inside the swizzle row: +2 in the 16-byte address field;
+                    // batch tile a is 16 KB (1024 in the address field) further on
+#pragma unroll
+                    for (int a = 0; a < MA; a++)
+                        umma_f16(tmem_base + (uint32_t)(a * NB), a_desc + (uint64_t)(a * 1024 + 2 * k),
+                                 b_desc + (uint64_t)(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
                 }
                 umma_commit(empty(s));        // stage reusable once these MMAs have read it
                 if (++s == S) { s = 0; ph ^= 1u; }
@@ -416,17 +257,20 @@ lux_qgemm_i4_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             tc_fence_after();
             const int quad = warp & 3;                          // TMEM lanes this warp may read
             const int half = (warp - 2) >> 2;                   // which half of the columns
-            const int row = m0 + quad * 32 + lane;
+#pragma unroll 1
+            for (int at = 0; at < MA; at++) {
+            const int row = m0 + at * BM + quad * 32 + lane;
+            const uint32_t tacc = tmem_base + (uint32_t)(at * NB);
             constexpr int COLS_PER_WARP = BN / 2;
             constexpr int CHUNK = COLS_PER_WARP < 32 ? COLS_PER_WARP : 32;
             static_assert(CHUNK == 32, "BN >= 64 expected");
 #pragma unroll 1
             for (int c0 = half * COLS_PER_WARP; c0 < (half + 1) * COLS_PER_WARP; c0 += 32) {
                 uint32_t acc[32];
-                tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, acc);
+                tmem_ld32(tacc + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, acc);
                 if (SWIGLU) {
                     uint32_t up[32];
-                    tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(BN + c0), up);
+                    tmem_ld32(tacc + ((uint32_t)(quad * 32) << 16) + (uint32_t)(BN + c0), up);
                     tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 32; i++)
@@ -450,6 +294,7 @@ lux_qgemm_i4_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     }
                 }
             }
+            }   // batch tiles
             tc_fence_before();
         }
     }
@@ -516,9 +361,9 @@ bool encode_tensor_map_u8(void* map, int rank, const void* base, const uint64_t*
 
 namespace {
 
-template <int BN, bool SW, bool BF16>
+template <int BN, bool SW, bool BF16, int MA>
 cudaError_t launch_inst(const CUtensorMap& mx, const CUtensorMap& mw, GemmParams p, dim3 grid, size_t smem, cudaStream_t st) {
-    auto kfn = lux_qgemm_i4_tc<BN, SW, BF16>;
+    auto kfn = lux_qgemm_i4_tc<BN, SW, BF16, MA>;
     // Raise the dynamic shared-memory limit once per device (not on every launch, so that
     // launches stay legal inside a stream capture).
     static std::atomic<size_t> configured[64];
@@ -543,7 +388,12 @@ LuxBackendError launch_qgemm_i4_tc(Context* ctx, const QArgs& a) {
     int bn = g_tune.gemm_tc_bn > 0 ? g_tune.gemm_tc_bn : 128;
     bn = (bn >= 128 && !a.swiglu) ? 128 : (a.swiglu ? (bn >= 128 ? 128 : 64) : 64);
     const int nb = a.swiglu ? 2 * bn : bn;
-    const size_t stage_bytes = (size_t)BM * 128 + (size_t)nb * 128 + (size_t)nb * 32;
+    // Two batch tiles per CTA (256 rows share one converted weight tile) when the batch has them
+    // and two accumulators fit TMEM (2 * nb <= 512 columns): the conversion of a weight tile, the
+    // instruction-bound part of the kernel, is then paid once per 256 rows instead of per 128.
+    int ma = (a.M > BM && 2 * nb <= 512) ? 2 : 1;
+    if (g_tune.gemm_tc_ma == 1 || g_tune.gemm_tc_ma == 2) ma = (g_tune.gemm_tc_ma == 2 && 2 * nb <= 512) ? 2 : 1;
+    const size_t stage_bytes = (size_t)ma * BM * 128 + (size_t)nb * 128 + (size_t)nb * 32;
     // Scales and zero-points of the CTA's rows go to shared memory when every block is a
     // 16-byte aligned, 16-byte multiple copy and the table leaves room for >= 3 stages.
     const int zs = (a.G + 1) / 2;
@@ -561,7 +411,7 @@ LuxBackendError launch_qgemm_i4_tc(Context* ctx, const QArgs& a) {
 
     CUtensorMap mx, mw;
     if (!encode_2d(&mx, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.x,
-                   (uint64_t)a.K, (uint64_t)a.M, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B))
+                   (uint64_t)a.K, (uint64_t)a.M, BK, (uint32_t)(ma * BM), CU_TENSOR_MAP_SWIZZLE_128B))
         return LUX_BACKEND_ERROR_INTERNAL;
     if (!encode_2d(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.w, (uint64_t)a.K / 2, (uint64_t)a.N, BK / 2, (uint32_t)bn,
                    CU_TENSOR_MAP_SWIZZLE_NONE))
@@ -582,24 +432,34 @@ LuxBackendError launch_qgemm_i4_tc(Context* ctx, const QArgs& a) {
     p.meta_smem = meta_smem ? 1 : 0;
     p.meta_zeros_off = (int)meta_scale_bytes;
 
-    dim3 grid((nout + bn - 1) / bn, (a.M + BM - 1) / BM);
+    dim3 grid((nout + bn - 1) / bn, (a.M + ma * BM - 1) / (ma * BM));
     cudaError_t e;
+    auto go = [&](auto bn_tag, auto sw_tag, auto ma_tag) {
+        constexpr int BN_ = decltype(bn_tag)::value;
+        constexpr bool SW_ = decltype(sw_tag)::value;
+        constexpr int MA_ = decltype(ma_tag)::value;
+        if constexpr (MA_ * (SW_ ? 2 * BN_ : BN_) <= 512)
+            return bf16 ? launch_inst<BN_, SW_, true, MA_>(mx, mw, p, grid, smem, ctx->stream)
+                        : launch_inst<BN_, SW_, false, MA_>(mx, mw, p, grid, smem, ctx->stream);
+        else
+            return cudaErrorInvalidValue;
+    };
+    using I64 = std::integral_constant<int, 64>;
+    using I128 = std::integral_constant<int, 128>;
+    using I1 = std::integral_constant<int, 1>;
+    using I2 = std::integral_constant<int, 2>;
     if (a.swiglu) {
-        if (bn == 128) e = bf16 ? launch_inst<128, true, true>(mx, mw, p, grid, smem, ctx->stream)
-                                : launch_inst<128, true, false>(mx, mw, p, grid, smem, ctx->stream);
-        else           e = bf16 ? launch_inst<64, true, true>(mx, mw, p, grid, smem, ctx->stream)
-                                : launch_inst<64, true, false>(mx, mw, p, grid, smem, ctx->stream);
+        if (bn == 128) e = ma == 2 ? go(I128{}, std::true_type{}, I2{}) : go(I128{}, std::true_type{}, I1{});
+        else           e = ma == 2 ? go(I64{}, std::true_type{}, I2{}) : go(I64{}, std::true_type{}, I1{});
     } else {
-        if (bn == 128) e = bf16 ? launch_inst<128, false, true>(mx, mw, p, grid, smem, ctx->stream)
-                                : launch_inst<128, false, false>(mx, mw, p, grid, smem, ctx->stream);
-        else           e = bf16 ? launch_inst<64, false, true>(mx, mw, p, grid, smem, ctx->stream)
-                                : launch_inst<64, false, false>(mx, mw, p, grid, smem, ctx->stream);
+        if (bn == 128) e = ma == 2 ? go(I128{}, std::false_type{}, I2{}) : go(I128{}, std::false_type{}, I1{});
+        else           e = ma == 2 ? go(I64{}, std::false_type{}, I2{}) : go(I64{}, std::false_type{}, I1{});
     }
     count_launch(bf16 ? "lux_qgemm_i4_tc_bf16" : "lux_qgemm_i4_tc_f16");
     return map_cuda(e, "lux_qgemm_i4_tc");
 }
 
-const void* kernel_addr_qgemm_i4_tc_bf16() { return (const void*)lux_qgemm_i4_tc<128, false, true>; }
-const void* kernel_addr_qgemm_i4_tc_f16() { return (const void*)lux_qgemm_i4_tc<128, false, false>; }
+const void* kernel_addr_qgemm_i4_tc_bf16() { return (const void*)lux_qgemm_i4_tc<128, false, true, 1>; }
+const void* kernel_addr_qgemm_i4_tc_f16() { return (const void*)lux_qgemm_i4_tc<128, false, false, 1>; }
 
 }  // namespace luxcuda

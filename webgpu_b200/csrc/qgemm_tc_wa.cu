@@ -1,0 +1,371 @@
+// int4 g128 weight-only GEMM on tcgen05 with the converted WEIGHTS as the tensor-memory A
+// operand, for prefill batches above 128 rows.
+//
+//   y[M, N] = x[M, K] . dequant(W[N, K])^T      x, y bf16 or f16; f32 accumulate in TMEM
+//
+// Same contraction as matmul_nax_grouped (luxcpp/webgpu kernels/wgsl/gpu/quantized_nax.wgsl:
+// 568-626) and the same dequantized values as dequantize_nax_int4_asym (:312-330) narrowed once.
+// The accumulator is held transposed: D[weight row, batch row], 128 weight rows on the 128 TMEM
+// lanes and 256 batch rows on 256 columns, so that
+//
+//   * one tcgen05.mma is 128 x 256 x 16 (the shape that issues at the full tensor rate),
+//   * a weight tile is converted once per 256 batch rows,
+//   * the converted tile never touches shared memory: a converting thread owns one weight row
+//     (= its TMEM lane), reads that row's packed bytes straight from global memory into
+//     registers one quantization group ahead, and writes the converted 64-K block with one
+//     tcgen05.st; shared memory only carries the x tiles (TMA, 128B swizzle) the tensor core
+//     reads as the B operand.
+//
+//   warp 0        TMA producer of the x tiles (256 batch rows x 64 K per stage).
+//   warp 1        issues four tcgen05.mma (A in TMEM, B in shared memory) per stage and commits
+//                 the stage back to the producer and the converters.
+//   warps 2..     converters, in groups of four warps (one per TMEM lane quarter); group g takes
+//                 quantization groups g, g + NG, ... of the CTA's K range.
+//   warps 2..9    epilogue.
+//
+// Split-K: with KS = 2 the two CTAs of a cluster take the two halves of K for the same tile;
+// each then sends the accumulator columns the other one finishes through distributed shared
+// memory (st.shared::cluster into the peer's idle x ring), adds what it received to its own half
+// and writes it.  No multicast anywhere.  Every mbarrier wait is bounded; the cluster barriers are
+// hardware barriers that every thread reaches on every path.
+#include "common.cuh"
+#include "tc_ptx.cuh"
+
+#include <algorithm>
+
+namespace luxcuda {
+
+namespace {
+
+using namespace tcptx;
+
+constexpr int WA_BN = 256;                 // batch rows per CTA = UMMA N = accumulator columns
+constexpr int WA_X_BYTES = WA_BN * 128;    // x tile of a stage: 256 rows x 64 K x 2 bytes
+constexpr int WA_A_COLS = BK / 2;          // TMEM columns of a converted 64-K block (2 K per column)
+constexpr int WA_A_STAGES = 8;             // converted blocks resident in TMEM (a power of two)
+constexpr int WA_MAX_GROUPS = 4;           // 2 * groups - 1 <= WA_A_STAGES
+constexpr int WA_MAX_THREADS = (2 + 4 * WA_MAX_GROUPS) * 32;
+constexpr uint32_t WA_TMEM_COLS = 512;     // accumulator [0, 256) + up to 8 A stages [256, 512)
+
+struct WaParams {
+    const uint8_t* w;         // [N, K/2]
+    const __half* scales;     // [N, G]
+    const uint8_t* zeros;     // [N, ZS] or null
+    void* y;                  // [M, N]
+    uint32_t* status;
+    int M, N, K, G, ZS;
+    int stages;               // ring depth of the x tiles in shared memory
+    int groups;               // converter groups of four warps
+};
+
+// Group constants of one weight row: zero-point pair and the scale (bf16: split in two).
+template <bool BF16>
+__device__ __forceinline__ void group_consts(__half sh, uint32_t zp, uint32_t& zc, uint32_t& sa, uint32_t& sb) {
+    if (BF16) {
+        const uint32_t sbits = __float_as_uint(__half2float(sh));
+        const uint32_t hi = sbits & 0xFFFF0000u;                    // top 8 significand bits
+        const float lo = __half2float(sh) - __uint_as_float(hi);     // remaining 3 bits, exact
+        sa = (hi >> 16) * 0x00010001u;
+        sb = (__float_as_uint(lo) >> 16) * 0x00010001u;
+        zc = (0x4300u | zp) | ((0x4180u | (zp << 3)) << 16);        // (128 + zp, 16 + zp)
+    } else {
+        sa = (uint32_t)__half_as_ushort(sh) * 0x00010001u;
+        sb = 0u;
+        zc = (0x6400u | zp) | ((0x5400u | (zp << 4)) << 16);        // (1024 + zp, 64 + zp)
+    }
+}
+
+template <bool BF16, int KS>
+__global__ void __launch_bounds__(WA_MAX_THREADS, 1)
+lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    const int S = p.stages;
+    unsigned char* x_ring = smem;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(x_ring + (size_t)S * WA_X_BYTES);
+    // bars[0..S) full_x, [S..2S) empty_x, [2S..2S+8) full_a, [2S+8..2S+16) empty_a, [2S+16] acc_full
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 2 * WA_A_STAGES + 1);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * BM;                 // first weight row of the tile
+    const int m0 = blockIdx.y * WA_BN;              // first batch row of the tile
+    const int ksplit = KS == 1 ? 0 : (int)blockIdx.z;
+    const int k_len = p.K / KS;
+    const int k_base = ksplit * k_len;
+    const int KB = k_len / BK;
+
+    const uint32_t bar0 = smem_u32(bars);
+    auto full_x = [&](int s) { return bar0 + 8u * (uint32_t)s; };
+    auto empty_x = [&](int s) { return bar0 + 8u * (uint32_t)(S + s); };
+    auto full_a = [&](int s) { return bar0 + 8u * (uint32_t)(2 * S + s); };
+    auto empty_a = [&](int s) { return bar0 + 8u * (uint32_t)(2 * S + WA_A_STAGES + s); };
+    const uint32_t acc_full = bar0 + 8u * (uint32_t)(2 * S + 2 * WA_A_STAGES);
+
+    if (tid == 0) {
+        for (int s = 0; s < S; s++) {
+            mbar_init(full_x(s), 1);
+            mbar_init(empty_x(s), 1);
+        }
+        for (int s = 0; s < WA_A_STAGES; s++) {
+            mbar_init(full_a(s), 4);
+            mbar_init(empty_a(s), 1);
+        }
+        mbar_init(acc_full, 1);
+        *abort_flag = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), WA_TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_a0 = tmem_base + (uint32_t)WA_BN;      // first A stage
+
+    bool ok = true;
+    if (warp == 0) {
+        // =============================== TMA producer of x ==============================
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            for (int kb = 0; kb < KB; kb++) {
+                if (!mbar_wait(empty_x(s), ph ^ 1u, abort_flag)) break;
+                mbar_expect_tx(full_x(s), WA_X_BYTES);
+                // byte coordinates: the map describes x as [M][2K bytes]
+                tma_load_2d(smem_u32(x_ring + (size_t)s * WA_X_BYTES), &map_x, (k_base + kb * BK) * 2, m0, full_x(s));
+                if (++s == S) { s = 0; ph ^= 1u; }
+            }
+        }
+    } else if (warp == 1) {
+        // =============================== MMA issuer =====================================
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(BF16, WA_BN);
+            int s = 0, sa = 0;
+            uint32_t ph = 0, pha = 0;
+            for (int kb = 0; kb < KB && ok; kb++) {
+                ok = mbar_wait(full_x(s), ph, abort_flag) && mbar_wait(full_a(sa), pha, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                const uint64_t b_desc = make_kmajor_sw128_desc(smem_u32(x_ring + (size_t)s * WA_X_BYTES));
+                const uint32_t a_tmem = tmem_a0 + (uint32_t)(sa * WA_A_COLS);
+#pragma unroll
+                for (int k = 0; k < BK / 16; k++)
+                    umma_f16_ts(tmem_base, a_tmem + (uint32_t)(k * 8), b_desc + (uint64_t)(2 * k), idesc,
+                                (kb | k) != 0 ? 1u : 0u);
+                umma_commit(empty_x(s));      // x tile and A block reusable once these MMAs have read them
+                umma_commit(empty_a(sa));
+                if (++s == S) { s = 0; ph ^= 1u; }
+                if (++sa == WA_A_STAGES) { sa = 0; pha ^= 1u; }
+            }
+            if (ok) umma_commit(acc_full);
+        }
+    } else {
+        // =============================== converters =====================================
+        const int grp = (warp - 2) >> 2;
+        const int quad = warp & 3;                          // TMEM lane quarter of this warp
+        const int wrow = n0 + quad * 32 + lane;             // this thread's weight row
+        const int NG = p.groups;
+        const int QG = KB / 2;                              // quantization groups in this CTA's K range
+        const int g_base = k_base >> 7;
+        const uint8_t* wp = p.w + (size_t)wrow * (p.K / 2) + (k_base >> 1);
+        const __half* sp = p.scales + (size_t)wrow * p.G + g_base;
+        const uint8_t* zp_row = p.zeros ? p.zeros + (size_t)wrow * p.ZS : nullptr;
+
+        uint4 nq[4];                                        // next group's 64 packed bytes
+        __half nsh = __float2half(0.f);
+        uint32_t nzp = 8u;
+        auto fetch = [&](int qg) {
+            const uint4* src = reinterpret_cast<const uint4*>(wp + (size_t)qg * 64);
+#pragma unroll
+            for (int i = 0; i < 4; i++) nq[i] = __ldg(src + i);
+            nsh = __ldg(sp + qg);
+            if (zp_row) {
+                const int g = g_base + qg;
+                nzp = ((uint32_t)__ldg(zp_row + (g >> 1)) >> ((g & 1) * 4)) & 0xFu;
+            }
+        };
+        if (grp < QG) fetch(grp);
+        for (int qg = grp; qg < QG && ok; qg += NG) {
+            uint4 cq[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) cq[i] = nq[i];
+            uint32_t zc, sa, sb;
+            group_consts<BF16>(nsh, nzp, zc, sa, sb);
+            if (qg + NG < QG) fetch(qg + NG);
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const int kb = 2 * qg + h;
+                // A ring of 8 blocks: a group moves 2 * NG <= 8 blocks from one of its blocks to the
+                // next, so it is never more than one lap ahead of the commits it waits for
+                const int s = kb & (WA_A_STAGES - 1);
+                const uint32_t ph = (uint32_t)(kb / WA_A_STAGES) & 1u;
+                const uint32_t words[8] = {cq[2 * h].x, cq[2 * h].y, cq[2 * h].z, cq[2 * h].w,
+                                           cq[2 * h + 1].x, cq[2 * h + 1].y, cq[2 * h + 1].z, cq[2 * h + 1].w};
+                uint32_t out[32];
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const uint4 v = BF16 ? dequant_word_bf16(words[j], zc, sa, sb) : dequant_word_f16(words[j], zc, sa);
+                    out[4 * j + 0] = v.x; out[4 * j + 1] = v.y; out[4 * j + 2] = v.z; out[4 * j + 3] = v.w;
+                }
+                ok = warp_wait(empty_a(s), ph ^ 1u, abort_flag, lane);   // A block s free (warp-uniform outcome)
+                if (!ok) break;
+                tc_fence_after();
+                tmem_st32(tmem_a0 + ((uint32_t)(quad * 32) << 16) + (uint32_t)(s * WA_A_COLS), out);
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full_a(s));
+            }
+        }
+        if (ok && warp < 10) ok = warp_wait(acc_full, 0u, abort_flag, lane);
+        if (ok) tc_fence_after();
+    }
+    __syncwarp();
+
+    // =============================== epilogue ===========================================
+    // Warps 2..9: quarter `quad` of the lanes (weight rows), half `eh` of the columns handled.
+    const int quad = warp & 3;
+    const int eh = (warp - 2) >> 2;
+    const bool ep_warp = warp >= 2 && warp < 10;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+    float* recv = reinterpret_cast<float*>(x_ring);            // [128 columns][128 lanes] f32, KS == 2 only
+    const int keep0 = KS == 1 ? 0 : ksplit * (WA_BN / 2);       // first accumulator column this CTA writes
+    constexpr int KEEP = WA_BN / KS;                            // columns this CTA writes
+    constexpr int PER_WARP = KEEP / 2;                          // per epilogue warp
+
+    if (KS == 2) {
+        cluster_sync_all();          // both CTAs are done with their rings
+        if (ep_warp && ok) {
+            const int send0 = (1 - ksplit) * (WA_BN / 2);
+            const uint32_t peer = map_to_cta(smem_u32(recv), (uint32_t)(1 - ksplit));
+#pragma unroll 1
+            for (int c0 = eh * PER_WARP; c0 < (eh + 1) * PER_WARP; c0 += 32) {
+                uint32_t acc[32];
+                tmem_ld32(lane_addr + (uint32_t)(send0 + c0), acc);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; i++)
+                    st_cluster_f32(peer + (uint32_t)(((c0 + i) * BM + quad * 32 + lane) * 4), __uint_as_float(acc[i]));
+            }
+        }
+        cluster_sync_all();          // the peer's partial sums have arrived
+    }
+    if (ep_warp && ok) {
+        const bool odd = lane & 1;
+        // lanes pair up: the even lane writes (row, row + 1) of the even columns, the odd lane of the odd ones
+        const int wr = n0 + quad * 32 + (lane & ~1);
+#pragma unroll 1
+        for (int c0 = eh * PER_WARP; c0 < (eh + 1) * PER_WARP; c0 += 32) {
+            uint32_t acc[32];
+            tmem_ld32(lane_addr + (uint32_t)(keep0 + c0), acc);
+            tmem_ld_wait();
+            if (KS == 2) {
+#pragma unroll
+                for (int i = 0; i < 32; i++)
+                    acc[i] = __float_as_uint(__uint_as_float(acc[i]) + recv[(c0 + i) * BM + quad * 32 + lane]);
+            }
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                const float mine = __uint_as_float(odd ? acc[i + 1] : acc[i]);
+                const float give = __uint_as_float(odd ? acc[i] : acc[i + 1]);
+                const float got = __shfl_xor_sync(0xffffffffu, give, 1);
+                const int m = m0 + keep0 + c0 + i + (odd ? 1 : 0);
+                if (m < p.M) {
+                    const uint32_t v = odd ? pack2<BF16>(got, mine) : pack2<BF16>(mine, got);
+                    *reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned char*>(p.y) + ((size_t)m * p.N + wr) * 2) = v;
+                }
+            }
+        }
+        tc_fence_before();
+    }
+
+    __syncthreads();
+    if (*abort_flag) {
+        if (tid == 0 && p.status) atomicOr(p.status, 0x7C050002u);
+        for (int i = 0; i < 64; i++) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, WA_TMEM_COLS);
+    }
+}
+
+template <bool BF16, int KS>
+cudaError_t launch_wa(const CUtensorMap& mx, const WaParams& p, dim3 grid, int threads, size_t smem, cudaStream_t st) {
+    auto kfn = lux_qgemm_i4_tc_wa<BF16, KS>;
+    static std::atomic<size_t> configured[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && configured[dev].load(std::memory_order_relaxed) < smem) {
+        cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        configured[dev].store(smem, std::memory_order_relaxed);
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3((unsigned)threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = KS;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kfn, mx, p);
+}
+
+}  // namespace
+
+// Takes plain (no SwiGLU, no push) int4 GEMMs whose weight rows come in whole tiles of 128 and
+// whose batch is above 128 rows; everything else stays with lux_qgemm_i4_tc.
+LuxBackendError launch_qgemm_i4_tc_wa(Context* ctx, const QArgs& a) {
+    if (a.swiglu || a.push || a.N % BM || a.K % 128 || a.M < 1) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+    if (a.scale_dtype != LUX_QDTYPE_F16 || a.x_dtype != a.y_dtype) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+    if (a.x_dtype != LUX_QDTYPE_BF16 && a.x_dtype != LUX_QDTYPE_F16) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(a.w) & 15u) || (a.K / 2) % 16) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+    const bool bf16 = a.x_dtype == LUX_QDTYPE_BF16;
+
+    // Split K over a pair of CTAs when whole tiles alone would leave most SMs idle.
+    const int tiles = (a.N / BM) * ((a.M + WA_BN - 1) / WA_BN);
+    int ks = (tiles * 2 <= ctx->sm_count && a.K % 256 == 0) ? 2 : 1;
+    if (g_tune.gemm_tc_splitk == 1 || (g_tune.gemm_tc_splitk == 2 && a.K % 256 == 0)) ks = g_tune.gemm_tc_splitk;
+    int groups = g_tune.gemm_tc_groups >= 2 && g_tune.gemm_tc_groups <= WA_MAX_GROUPS ? g_tune.gemm_tc_groups : 4;
+    int stages = g_tune.gemm_tc_stages >= 2 && g_tune.gemm_tc_stages <= 7 ? g_tune.gemm_tc_stages : 6;
+    const size_t smem = 1024 + (size_t)stages * WA_X_BYTES + 512;
+
+    CUtensorMap mx;
+    const uint64_t dims[2] = {(uint64_t)a.K * 2, (uint64_t)a.M};
+    const uint64_t strides[1] = {(uint64_t)a.K * 2};
+    const uint32_t box[2] = {128, (uint32_t)WA_BN};
+    if (!encode_tensor_map_u8(&mx, 2, a.x, dims, strides, box, true)) return LUX_BACKEND_ERROR_INTERNAL;
+
+    WaParams p{};
+    p.w = a.w;
+    p.scales = (const __half*)a.scales;
+    p.zeros = a.zeros;
+    p.y = a.y;
+    p.status = ctx->d_status;
+    p.M = a.M; p.N = a.N; p.K = a.K; p.G = a.G; p.ZS = (a.G + 1) / 2;
+    p.stages = stages;
+    p.groups = groups;
+
+    dim3 grid(a.N / BM, (a.M + WA_BN - 1) / WA_BN, ks);
+    const int threads = (2 + 4 * groups) * 32;                  // groups >= 2: the epilogue needs warps 2..9
+    cudaError_t e;
+    if (ks == 2) e = bf16 ? launch_wa<true, 2>(mx, p, grid, threads, smem, ctx->stream)
+                          : launch_wa<false, 2>(mx, p, grid, threads, smem, ctx->stream);
+    else         e = bf16 ? launch_wa<true, 1>(mx, p, grid, threads, smem, ctx->stream)
+                          : launch_wa<false, 1>(mx, p, grid, threads, smem, ctx->stream);
+    count_launch(bf16 ? "lux_qgemm_i4_tc_wa_bf16" : "lux_qgemm_i4_tc_wa_f16");
+    return map_cuda(e, "lux_qgemm_i4_tc_wa");
+}
+
+const void* kernel_addr_qgemm_i4_tc_wa_bf16() { return (const void*)lux_qgemm_i4_tc_wa<true, 2>; }
+
+}  // namespace luxcuda
