@@ -59,9 +59,10 @@ def test_wa_shapes(ctx, backend, dtype, splitk, M, N, K):
     assert ctx.last_device_status() == 0
 
 
-@pytest.mark.parametrize("groups,stages", [(2, 2), (2, 6), (3, 4), (4, 3), (4, 7)])
+@pytest.mark.parametrize("groups,stages", [(2, 2), (2, 3), (3, 3), (3, 2)])
 def test_wa_groups_and_stages(ctx, backend, groups, stages):
-    """Every number of converter groups and ring depth gives the same bits."""
+    """Every number of converter groups and ring depth gives the same bits (more groups than
+    ring slots are clamped to the ring depth)."""
     x = synth.activations(384, 1024, "bf16", 42, "wag.x")
     layer = synth.int4_layer(256, 1024, 42, "wag")
     with _Tuned(backend, gemm_tc_kernel=2):

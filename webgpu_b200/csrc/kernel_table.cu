@@ -47,7 +47,7 @@ const Entry kTable[] = {
     {"lux_qdequant_i8_g32",        luxcuda::kernel_addr_qdequant_i8,        256, 1, 1},
     {"lux_qgemm_i4_tc_bf16",       luxcuda::kernel_addr_qgemm_i4_tc_bf16,   320, 1, 1},
     {"lux_qgemm_i4_tc_f16",        luxcuda::kernel_addr_qgemm_i4_tc_f16,    320, 1, 1},
-    {"lux_qgemm_i4_tc_wa_bf16",    luxcuda::kernel_addr_qgemm_i4_tc_wa_bf16, 576, 1, 1},
+    {"lux_qgemm_i4_tc_wa_bf16",    luxcuda::kernel_addr_qgemm_i4_tc_wa_bf16, 320, 1, 1},
 };
 constexpr size_t kCount = sizeof(kTable) / sizeof(kTable[0]);
 

@@ -16,11 +16,14 @@
 //     tcgen05.st; shared memory only carries the x tiles (TMA, 128B swizzle) the tensor core
 //     reads as the B operand.
 //
-//   warp 0        TMA producer of the x tiles (256 batch rows x 64 K per stage).
-//   warp 1        issues four tcgen05.mma (A in TMEM, B in shared memory) per stage and commits
-//                 the stage back to the producer and the converters.
+// The ring works in units of 128 K (one quantization group, two 64-K swizzle blocks): up to three
+// units of x in shared memory and of converted weights in TMEM.
+//
+//   warp 0        TMA producer of the x tiles (256 batch rows x 128 K per unit, two boxes).
+//   warp 1        one wait, eight tcgen05.mma (A in TMEM, B in shared memory) and one commit per
+//                 unit; the commit hands the unit back to the producer and the converters.
 //   warps 2..     converters, in groups of four warps (one per TMEM lane quarter); group g takes
-//                 quantization groups g, g + NG, ... of the CTA's K range.
+//                 units g, g + NG, ... of the CTA's K range.
 //   warps 2..9    epilogue.
 //
 // Split-K: with KS = 2 the two CTAs of a cluster take the two halves of K for the same tile;
@@ -42,10 +45,30 @@ using namespace tcptx;
 constexpr int WA_BN = 256;                 // batch rows per CTA = UMMA N = accumulator columns
 constexpr int WA_X_BYTES = WA_BN * 128;    // x tile of a stage: 256 rows x 64 K x 2 bytes
 constexpr int WA_A_COLS = BK / 2;          // TMEM columns of a converted 64-K block (2 K per column)
-constexpr int WA_A_STAGES = 8;             // converted blocks resident in TMEM (a power of two)
-constexpr int WA_MAX_GROUPS = 4;           // 2 * groups - 1 <= WA_A_STAGES
+constexpr int WA_UNIT_K = 128;             // K per ring slot: one quantization group = two 64-K blocks
+constexpr int WA_UNIT_X_BYTES = 2 * WA_X_BYTES;
+constexpr int WA_UNIT_A_COLS = 2 * WA_A_COLS;
+constexpr int WA_MAX_UNITS = 3;            // ring depth: 3 x 64 KB of x in shared memory, 3 x 64 columns of A in TMEM
+constexpr int WA_MAX_GROUPS = 3;           // converter groups <= ring depth
 constexpr int WA_MAX_THREADS = (2 + 4 * WA_MAX_GROUPS) * 32;
-constexpr uint32_t WA_TMEM_COLS = 512;     // accumulator [0, 256) + up to 8 A stages [256, 512)
+constexpr uint32_t WA_TMEM_COLS = 512;     // accumulator [0, 256) + A units [256, 448)
+constexpr int WA_STAGE_PITCH = 320;        // bytes per batch row of the staged output tile: 256 + 64, so that the
+                                           // even and the odd lanes of a staging store use different banks
+
+// Optional timeline for kernel development: built only with -DLUX_WA_TRACE (the product build
+// leaves it out).  CTA (0,0,0) records clock64() per warp at each step into g_wa_trace.
+#ifdef LUX_WA_TRACE
+__device__ unsigned long long g_wa_trace[32 * 128];
+#define TRACE_DECL int tr_i = 0
+#define TRACE(tag)                                                                   \
+    do {                                                                             \
+        if ((blockIdx.x | blockIdx.y | blockIdx.z) == 0 && (threadIdx.x & 31) == 0 && tr_i < 128)                  \
+            g_wa_trace[(threadIdx.x >> 5) * 128 + tr_i++] = ((unsigned long long)(tag) << 56) | (clock64() & 0xFFFFFFFFFFFFFFull); \
+    } while (0)
+#else
+#define TRACE_DECL
+#define TRACE(tag)
+#endif
 
 struct WaParams {
     const uint8_t* w;         // [N, K/2]
@@ -54,8 +77,8 @@ struct WaParams {
     void* y;                  // [M, N]
     uint32_t* status;
     int M, N, K, G, ZS;
-    int stages;               // ring depth of the x tiles in shared memory
-    int groups;               // converter groups of four warps
+    int stages;               // ring depth in units of 128 K (x in shared memory, A in TMEM)
+    int groups;               // converter groups of four warps, <= stages
 };
 
 // Group constants of one weight row: zero-point pair and the scale (bf16: split in two).
@@ -80,36 +103,62 @@ __global__ void __launch_bounds__(WA_MAX_THREADS, 1)
 lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    const int S = p.stages;
+    const int P = p.stages;                          // ring depth in units of 128 K
     unsigned char* x_ring = smem;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(x_ring + (size_t)S * WA_X_BYTES);
-    // bars[0..S) full_x, [S..2S) empty_x, [2S..2S+8) full_a, [2S+8..2S+16) empty_a, [2S+16] acc_full
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 2 * WA_A_STAGES + 1);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(x_ring + (size_t)P * WA_UNIT_X_BYTES);
+    // bars[0..P) full, [P..2P) empty, [2P] acc_full
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * P + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
+    TRACE_DECL;
+    TRACE(1);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.x * BM;                 // first weight row of the tile
     const int m0 = blockIdx.y * WA_BN;              // first batch row of the tile
     const int ksplit = KS == 1 ? 0 : (int)blockIdx.z;
     const int k_len = p.K / KS;
     const int k_base = ksplit * k_len;
-    const int KB = k_len / BK;
+    const int U = k_len / WA_UNIT_K;                // units (= quantization groups) of this CTA
+    const int g_base = k_base / WA_UNIT_K;
 
     const uint32_t bar0 = smem_u32(bars);
-    auto full_x = [&](int s) { return bar0 + 8u * (uint32_t)s; };
-    auto empty_x = [&](int s) { return bar0 + 8u * (uint32_t)(S + s); };
-    auto full_a = [&](int s) { return bar0 + 8u * (uint32_t)(2 * S + s); };
-    auto empty_a = [&](int s) { return bar0 + 8u * (uint32_t)(2 * S + WA_A_STAGES + s); };
-    const uint32_t acc_full = bar0 + 8u * (uint32_t)(2 * S + 2 * WA_A_STAGES);
+    auto full = [&](int s) { return bar0 + 8u * (uint32_t)s; };
+    auto empty = [&](int s) { return bar0 + 8u * (uint32_t)(P + s); };
+    const uint32_t acc_full = bar0 + 8u * (uint32_t)(2 * P);
 
-    if (tid == 0) {
-        for (int s = 0; s < S; s++) {
-            mbar_init(full_x(s), 1);
-            mbar_init(empty_x(s), 1);
+    // Converter state, set up before the CTA-wide barrier so that the first weight bytes are
+    // already on their way while the barriers and the tensor memory are being set up.
+    const int grp = (warp - 2) >> 2;
+    const int quad = warp & 3;                          // TMEM lane quarter of this warp
+    const int NG = p.groups;
+    uint4 nq[4];                                        // next unit's 64 packed bytes of this thread's row
+    __half nsh = __float2half(0.f);
+    uint32_t nzp = 8u;
+    const uint8_t* wp = nullptr;
+    const __half* sp = nullptr;
+    const uint8_t* zrow = nullptr;
+    auto fetch = [&](int u) {
+        const uint4* src = reinterpret_cast<const uint4*>(wp + (size_t)u * (WA_UNIT_K / 2));
+#pragma unroll
+        for (int i = 0; i < 4; i++) nq[i] = __ldg(src + i);
+        nsh = __ldg(sp + u);
+        if (zrow) {
+            const int g = g_base + u;
+            nzp = ((uint32_t)__ldg(zrow + (g >> 1)) >> ((g & 1) * 4)) & 0xFu;
         }
-        for (int s = 0; s < WA_A_STAGES; s++) {
-            mbar_init(full_a(s), 4);
-            mbar_init(empty_a(s), 1);
+    };
+    if (warp >= 2) {
+        const int wrow = n0 + quad * 32 + lane;         // this thread's weight row
+        wp = p.w + (size_t)wrow * (p.K / 2) + (k_base >> 1);
+        sp = p.scales + (size_t)wrow * p.G + g_base;
+        zrow = p.zeros ? p.zeros + (size_t)wrow * p.ZS : nullptr;
+        if (grp < U) fetch(grp);
+    } else if (tid == 1) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+    } else if (tid == 0) {
+        for (int s = 0; s < P; s++) {
+            mbar_init(full(s), 5);          // the producer's expect_tx arrival + four converter warps
+            mbar_init(empty(s), 1);
         }
         mbar_init(acc_full, 1);
         *abort_flag = 0u;
@@ -123,7 +172,8 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_a0 = tmem_base + (uint32_t)WA_BN;      // first A stage
+    TRACE(2);
+    const uint32_t tmem_a0 = tmem_base + (uint32_t)WA_BN;      // first A unit
 
     bool ok = true;
     if (warp == 0) {
@@ -131,77 +181,64 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
         if (lane == 0) {
             int s = 0;
             uint32_t ph = 0;
-            for (int kb = 0; kb < KB; kb++) {
-                if (!mbar_wait(empty_x(s), ph ^ 1u, abort_flag)) break;
-                mbar_expect_tx(full_x(s), WA_X_BYTES);
-                // byte coordinates: the map describes x as [M][2K bytes]
-                tma_load_2d(smem_u32(x_ring + (size_t)s * WA_X_BYTES), &map_x, (k_base + kb * BK) * 2, m0, full_x(s));
-                if (++s == S) { s = 0; ph ^= 1u; }
+            for (int u = 0; u < U; u++) {
+                if (!mbar_wait_relaxed(empty(s), ph ^ 1u, abort_flag)) break;
+                TRACE(10);
+                mbar_expect_tx(full(s), WA_UNIT_X_BYTES);
+                // byte coordinates: the map describes x as [M][2K bytes]; two 64-K boxes per unit
+                const uint32_t dst = smem_u32(x_ring + (size_t)s * WA_UNIT_X_BYTES);
+                const int kbyte = (k_base + u * WA_UNIT_K) * 2;
+                tma_load_2d(dst, &map_x, kbyte, m0, full(s));
+                tma_load_2d(dst + WA_X_BYTES, &map_x, kbyte + 128, m0, full(s));
+                if (++s == P) { s = 0; ph ^= 1u; }
             }
         }
     } else if (warp == 1) {
         // =============================== MMA issuer =====================================
+        // One wait, eight MMAs and one commit per unit: a satisfied mbarrier wait and a commit
+        // cost this thread ~200 and ~100 cycles, so they are paid once per 128 K, not per 64.
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc(BF16, WA_BN);
-            int s = 0, sa = 0;
-            uint32_t ph = 0, pha = 0;
-            for (int kb = 0; kb < KB && ok; kb++) {
-                ok = mbar_wait(full_x(s), ph, abort_flag) && mbar_wait(full_a(sa), pha, abort_flag);
+            int s = 0;
+            uint32_t ph = 0;
+            for (int u = 0; u < U; u++) {
+                ok = mbar_wait(full(s), ph, abort_flag);
                 if (!ok) break;
+                TRACE(20);
                 tc_fence_after();
-                const uint64_t b_desc = make_kmajor_sw128_desc(smem_u32(x_ring + (size_t)s * WA_X_BYTES));
-                const uint32_t a_tmem = tmem_a0 + (uint32_t)(sa * WA_A_COLS);
+                const uint64_t b_desc = make_kmajor_sw128_desc(smem_u32(x_ring + (size_t)s * WA_UNIT_X_BYTES));
+                const uint32_t a_tmem = tmem_a0 + (uint32_t)(s * WA_UNIT_A_COLS);
 #pragma unroll
-                for (int k = 0; k < BK / 16; k++)
-                    umma_f16_ts(tmem_base, a_tmem + (uint32_t)(k * 8), b_desc + (uint64_t)(2 * k), idesc,
-                                (kb | k) != 0 ? 1u : 0u);
-                umma_commit(empty_x(s));      // x tile and A block reusable once these MMAs have read them
-                umma_commit(empty_a(sa));
-                if (++s == S) { s = 0; ph ^= 1u; }
-                if (++sa == WA_A_STAGES) { sa = 0; pha ^= 1u; }
+                for (int k = 0; k < WA_UNIT_K / 16; k++) {
+                    // 16 K = 8 TMEM columns of A; in x: +32 bytes inside the 128-byte swizzle row
+                    // (+2 in the 16-byte address field), the second 64-K box 32 KB (+2048) further on
+                    const uint64_t b_off = (uint64_t)((k >> 2) * (WA_X_BYTES >> 4) + 2 * (k & 3));
+                    umma_f16_ts(tmem_base, a_tmem + (uint32_t)(k * 8), b_desc + b_off, idesc, (u | k) != 0 ? 1u : 0u);
+                }
+                TRACE(21);
+                umma_commit(empty(s));        // x unit and A unit reusable once these MMAs have read them
+                TRACE(22);
+                if (++s == P) { s = 0; ph ^= 1u; }
             }
             if (ok) umma_commit(acc_full);
         }
     } else {
         // =============================== converters =====================================
-        const int grp = (warp - 2) >> 2;
-        const int quad = warp & 3;                          // TMEM lane quarter of this warp
-        const int wrow = n0 + quad * 32 + lane;             // this thread's weight row
-        const int NG = p.groups;
-        const int QG = KB / 2;                              // quantization groups in this CTA's K range
-        const int g_base = k_base >> 7;
-        const uint8_t* wp = p.w + (size_t)wrow * (p.K / 2) + (k_base >> 1);
-        const __half* sp = p.scales + (size_t)wrow * p.G + g_base;
-        const uint8_t* zp_row = p.zeros ? p.zeros + (size_t)wrow * p.ZS : nullptr;
-
-        uint4 nq[4];                                        // next group's 64 packed bytes
-        __half nsh = __float2half(0.f);
-        uint32_t nzp = 8u;
-        auto fetch = [&](int qg) {
-            const uint4* src = reinterpret_cast<const uint4*>(wp + (size_t)qg * 64);
-#pragma unroll
-            for (int i = 0; i < 4; i++) nq[i] = __ldg(src + i);
-            nsh = __ldg(sp + qg);
-            if (zp_row) {
-                const int g = g_base + qg;
-                nzp = ((uint32_t)__ldg(zp_row + (g >> 1)) >> ((g & 1) * 4)) & 0xFu;
-            }
-        };
-        if (grp < QG) fetch(grp);
-        for (int qg = grp; qg < QG && ok; qg += NG) {
+        // Group `grp` takes units grp, grp + NG, ...; NG <= P keeps a group at most one lap of the
+        // ring ahead of the commit it waits for, which is what a one-bit phase can tell apart.
+        for (int u = grp; u < U && ok; u += NG) {
             uint4 cq[4];
 #pragma unroll
             for (int i = 0; i < 4; i++) cq[i] = nq[i];
             uint32_t zc, sa, sb;
             group_consts<BF16>(nsh, nzp, zc, sa, sb);
-            if (qg + NG < QG) fetch(qg + NG);
+            if (u + NG < U) fetch(u + NG);
+            const int s = u % P;
+            const uint32_t ph = (uint32_t)(u / P) & 1u;
+            const uint32_t a_dst = tmem_a0 + ((uint32_t)(quad * 32) << 16) + (uint32_t)(s * WA_UNIT_A_COLS);
 #pragma unroll
             for (int h = 0; h < 2; h++) {
-                const int kb = 2 * qg + h;
-                // A ring of 8 blocks: a group moves 2 * NG <= 8 blocks from one of its blocks to the
-                // next, so it is never more than one lap ahead of the commits it waits for
-                const int s = kb & (WA_A_STAGES - 1);
-                const uint32_t ph = (uint32_t)(kb / WA_A_STAGES) & 1u;
+                TRACE(30);
                 const uint32_t words[8] = {cq[2 * h].x, cq[2 * h].y, cq[2 * h].z, cq[2 * h].w,
                                            cq[2 * h + 1].x, cq[2 * h + 1].y, cq[2 * h + 1].z, cq[2 * h + 1].w};
                 uint32_t out[32];
@@ -210,79 +247,115 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
                     const uint4 v = BF16 ? dequant_word_bf16(words[j], zc, sa, sb) : dequant_word_f16(words[j], zc, sa);
                     out[4 * j + 0] = v.x; out[4 * j + 1] = v.y; out[4 * j + 2] = v.z; out[4 * j + 3] = v.w;
                 }
-                ok = warp_wait(empty_a(s), ph ^ 1u, abort_flag, lane);   // A block s free (warp-uniform outcome)
-                if (!ok) break;
-                tc_fence_after();
-                tmem_st32(tmem_a0 + ((uint32_t)(quad * 32) << 16) + (uint32_t)(s * WA_A_COLS), out);
-                tmem_st_wait();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(full_a(s));
+                if (h == 0) {
+                    TRACE(31);
+                    ok = warp_wait_relaxed(empty(s), ph ^ 1u, abort_flag, lane);   // A unit s free (warp-uniform outcome)
+                    if (!ok) break;
+                    TRACE(32);
+                    tc_fence_after();
+                }
+                tmem_st32(a_dst + (uint32_t)(h * WA_A_COLS), out);
             }
+            if (!ok) break;
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full(s));
+            TRACE(33);
         }
         if (ok && warp < 10) ok = warp_wait(acc_full, 0u, abort_flag, lane);
         if (ok) tc_fence_after();
     }
     __syncwarp();
+    TRACE(40);
 
     // =============================== epilogue ===========================================
     // Warps 2..9: quarter `quad` of the lanes (weight rows), half `eh` of the columns handled.
-    const int quad = warp & 3;
+    // The ring is idle by now and is reused: [0, 64 KB) partial sums received from the peer
+    // (KS == 2), then the narrowed output tile staged for row-wise 16-byte stores.
     const int eh = (warp - 2) >> 2;
     const bool ep_warp = warp >= 2 && warp < 10;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
-    float* recv = reinterpret_cast<float*>(x_ring);            // [128 columns][128 lanes] f32, KS == 2 only
+    const int my_row = quad * 32 + lane;
     const int keep0 = KS == 1 ? 0 : ksplit * (WA_BN / 2);       // first accumulator column this CTA writes
     constexpr int KEEP = WA_BN / KS;                            // columns this CTA writes
     constexpr int PER_WARP = KEEP / 2;                          // per epilogue warp
+    // received partial sums: 16 bytes (4 columns) per weight row, rows consecutive, so that a
+    // warp's remote store is one contiguous 512-byte piece
+    unsigned char* recv = x_ring;
+    unsigned char* stage = x_ring + (KS == 2 ? (WA_BN / 2) * BM * 4 : 0);   // [column][WA_STAGE_PITCH bytes]
 
     if (KS == 2) {
         cluster_sync_all();          // both CTAs are done with their rings
+        TRACE(41);
         if (ep_warp && ok) {
             const int send0 = (1 - ksplit) * (WA_BN / 2);
-            const uint32_t peer = map_to_cta(smem_u32(recv), (uint32_t)(1 - ksplit));
+            const uint32_t peer = map_to_cta(smem_u32(recv), (uint32_t)(1 - ksplit)) + (uint32_t)(my_row * 16);
 #pragma unroll 1
             for (int c0 = eh * PER_WARP; c0 < (eh + 1) * PER_WARP; c0 += 32) {
                 uint32_t acc[32];
                 tmem_ld32(lane_addr + (uint32_t)(send0 + c0), acc);
                 tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < 32; i++)
-                    st_cluster_f32(peer + (uint32_t)(((c0 + i) * BM + quad * 32 + lane) * 4), __uint_as_float(acc[i]));
+                for (int i = 0; i < 32; i += 4)
+                    st_cluster_v4(peer + (uint32_t)(((c0 + i) >> 2) * (BM * 16)), acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
             }
         }
+        TRACE(42);
         cluster_sync_all();          // the peer's partial sums have arrived
+        TRACE(43);
     }
-    if (ep_warp && ok) {
-        const bool odd = lane & 1;
-        // lanes pair up: the even lane writes (row, row + 1) of the even columns, the odd lane of the odd ones
-        const int wr = n0 + quad * 32 + (lane & ~1);
+    if (ep_warp) {
+        if (ok) {
+            const bool odd = lane & 1;
+            // lanes pair up: the even lane stages (row, row + 1) of the even columns, the odd lane of the odd ones
+            unsigned char* srow = stage + (quad * 32 + (lane & ~1)) * 2;
 #pragma unroll 1
-        for (int c0 = eh * PER_WARP; c0 < (eh + 1) * PER_WARP; c0 += 32) {
-            uint32_t acc[32];
-            tmem_ld32(lane_addr + (uint32_t)(keep0 + c0), acc);
-            tmem_ld_wait();
-            if (KS == 2) {
+            for (int c0 = eh * PER_WARP; c0 < (eh + 1) * PER_WARP; c0 += 32) {
+                uint32_t acc[32];
+                tmem_ld32(lane_addr + (uint32_t)(keep0 + c0), acc);
+                tmem_ld_wait();
+                if (KS == 2) {
 #pragma unroll
-                for (int i = 0; i < 32; i++)
-                    acc[i] = __float_as_uint(__uint_as_float(acc[i]) + recv[(c0 + i) * BM + quad * 32 + lane]);
-            }
+                    for (int i = 0; i < 8; i++) {
+                        const float4 r = *reinterpret_cast<const float4*>(recv + (((c0 >> 2) + i) * BM + my_row) * 16);
+                        acc[4 * i + 0] = __float_as_uint(__uint_as_float(acc[4 * i + 0]) + r.x);
+                        acc[4 * i + 1] = __float_as_uint(__uint_as_float(acc[4 * i + 1]) + r.y);
+                        acc[4 * i + 2] = __float_as_uint(__uint_as_float(acc[4 * i + 2]) + r.z);
+                        acc[4 * i + 3] = __float_as_uint(__uint_as_float(acc[4 * i + 3]) + r.w);
+                    }
+                }
 #pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-                const float mine = __uint_as_float(odd ? acc[i + 1] : acc[i]);
-                const float give = __uint_as_float(odd ? acc[i] : acc[i + 1]);
-                const float got = __shfl_xor_sync(0xffffffffu, give, 1);
-                const int m = m0 + keep0 + c0 + i + (odd ? 1 : 0);
-                if (m < p.M) {
+                for (int i = 0; i < 32; i += 2) {
+                    const float mine = __uint_as_float(odd ? acc[i + 1] : acc[i]);
+                    const float give = __uint_as_float(odd ? acc[i] : acc[i + 1]);
+                    const float got = __shfl_xor_sync(0xffffffffu, give, 1);
                     const uint32_t v = odd ? pack2<BF16>(got, mine) : pack2<BF16>(mine, got);
-                    *reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned char*>(p.y) + ((size_t)m * p.N + wr) * 2) = v;
+                    *reinterpret_cast<uint32_t*>(srow + (c0 + i + (odd ? 1 : 0)) * WA_STAGE_PITCH) = v;
+                }
+            }
+            tc_fence_before();
+        }
+        // the eight epilogue warps (and only they) meet here on every path
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        TRACE(46);
+        if (ok) {
+            // one batch row of the tile = 128 weight rows = 256 contiguous bytes of y: 16 lanes x 16 bytes
+            const int sub = lane >> 4, l16 = lane & 15;
+#pragma unroll 4
+            for (int c = (warp - 2) * 2 + sub; c < KEEP; c += 16) {
+                const int m = m0 + keep0 + c;
+                if (m < p.M) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(stage + c * WA_STAGE_PITCH + l16 * 16);
+                    *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(p.y) + ((size_t)m * p.N + n0 + l16 * 8) * 2) = v;
                 }
             }
         }
-        tc_fence_before();
     }
 
+    TRACE(44);
     __syncthreads();
+    TRACE(45);
     if (*abort_flag) {
         if (tid == 0 && p.status) atomicOr(p.status, 0x7C050002u);
         for (int i = 0; i < 64; i++) __nanosleep(1000);
@@ -335,9 +408,10 @@ LuxBackendError launch_qgemm_i4_tc_wa(Context* ctx, const QArgs& a) {
     const int tiles = (a.N / BM) * ((a.M + WA_BN - 1) / WA_BN);
     int ks = (tiles * 2 <= ctx->sm_count && a.K % 256 == 0) ? 2 : 1;
     if (g_tune.gemm_tc_splitk == 1 || (g_tune.gemm_tc_splitk == 2 && a.K % 256 == 0)) ks = g_tune.gemm_tc_splitk;
-    int groups = g_tune.gemm_tc_groups >= 2 && g_tune.gemm_tc_groups <= WA_MAX_GROUPS ? g_tune.gemm_tc_groups : 4;
-    int stages = g_tune.gemm_tc_stages >= 2 && g_tune.gemm_tc_stages <= 7 ? g_tune.gemm_tc_stages : 6;
-    const size_t smem = 1024 + (size_t)stages * WA_X_BYTES + 512;
+    const int stages = g_tune.gemm_tc_stages >= 2 && g_tune.gemm_tc_stages <= WA_MAX_UNITS ? g_tune.gemm_tc_stages : WA_MAX_UNITS;
+    int groups = g_tune.gemm_tc_groups >= 2 && g_tune.gemm_tc_groups <= WA_MAX_GROUPS ? g_tune.gemm_tc_groups : 2;
+    groups = std::min(groups, stages);
+    const size_t smem = 1024 + (size_t)stages * WA_UNIT_X_BYTES + 512;
 
     CUtensorMap mx;
     const uint64_t dims[2] = {(uint64_t)a.K * 2, (uint64_t)a.M};
@@ -365,6 +439,12 @@ LuxBackendError launch_qgemm_i4_tc_wa(Context* ctx, const QArgs& a) {
     count_launch(bf16 ? "lux_qgemm_i4_tc_wa_bf16" : "lux_qgemm_i4_tc_wa_f16");
     return map_cuda(e, "lux_qgemm_i4_tc_wa");
 }
+
+#ifdef LUX_WA_TRACE
+extern "C" __attribute__((visibility("default"))) int lux_cuda_debug_wa_trace(unsigned long long* out, int n) {
+    return (int)cudaMemcpyFromSymbol(out, g_wa_trace, sizeof(unsigned long long) * (size_t)n);
+}
+#endif
 
 const void* kernel_addr_qgemm_i4_tc_wa_bf16() { return (const void*)lux_qgemm_i4_tc_wa<true, 2>; }
 

@@ -46,6 +46,31 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     *abort_flag = 1u;
     return false;
 }
+// The same wait for roles that run ahead of the tensor core: a failed poll is followed by a
+// short sleep, so that threads waiting for a ring slot do not keep the mbarrier unit busy while
+// the MMA-issuing thread needs it (its satisfied polls took 300-400 cycles next to nine
+// spinning threads, 20 alone).
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+    for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if ((it & 31u) == 31u && *abort_flag) return false;
+        __nanosleep(128);
+    }
+    *abort_flag = 1u;
+    return false;
+}
+__device__ __forceinline__ bool warp_wait_relaxed(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, int lane) {
+    bool ok = true;
+    if (lane == 0) ok = mbar_wait_relaxed(bar, parity, abort_flag);
+    __syncwarp();
+    return __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+}
 // Warp-level wait: lane 0 polls (32 lanes polling the same barrier word are served one by
 // one), the outcome is broadcast, and __syncwarp orders the other lanes' later reads after
 // lane 0's acquire.  Must be called by a converged warp.
@@ -218,8 +243,8 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(d) : "r"(smem_addr), "r"(rank));
     return d;
 }
-__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
-    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+__device__ __forceinline__ void st_cluster_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 // Hardware barrier over all threads of the cluster (not a spin: every thread of every CTA
 // reaches it on every path, aborted ones included).
