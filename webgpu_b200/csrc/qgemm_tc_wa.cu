@@ -126,6 +126,15 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
     auto empty = [&](int s) { return bar0 + 8u * (uint32_t)(P + s); };
     const uint32_t acc_full = bar0 + 8u * (uint32_t)(2 * P);
 
+    auto load_x_unit = [&](int u, int s) {
+        mbar_expect_tx(full(s), WA_UNIT_X_BYTES);
+        // byte coordinates: the map describes x as [M][2K bytes]; two 64-K boxes per unit
+        const uint32_t dst = smem_u32(x_ring + (size_t)s * WA_UNIT_X_BYTES);
+        const int kbyte = (k_base + u * WA_UNIT_K) * 2;
+        tma_load_2d(dst, &map_x, kbyte, m0, full(s));
+        tma_load_2d(dst + WA_X_BYTES, &map_x, kbyte + 128, m0, full(s));
+    };
+
     // Converter state, set up before the CTA-wide barrier so that the first weight bytes are
     // already on their way while the barriers and the tensor memory are being set up.
     const int grp = (warp - 2) >> 2;
@@ -133,7 +142,7 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
     const int NG = p.groups;
     uint4 nq[4];                                        // next unit's 64 packed bytes of this thread's row
     __half nsh = __float2half(0.f);
-    uint32_t nzp = 8u;
+    uint32_t nzb = 0x88u;                               // byte holding the next unit's zero-point nibble (raw: no use of a loaded value inside fetch)
     const uint8_t* wp = nullptr;
     const __half* sp = nullptr;
     const uint8_t* zrow = nullptr;
@@ -142,10 +151,7 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
 #pragma unroll
         for (int i = 0; i < 4; i++) nq[i] = __ldg(src + i);
         nsh = __ldg(sp + u);
-        if (zrow) {
-            const int g = g_base + u;
-            nzp = ((uint32_t)__ldg(zrow + (g >> 1)) >> ((g & 1) * 4)) & 0xFu;
-        }
+        if (zrow) nzb = (uint32_t)__ldg(zrow + ((g_base + u) >> 1));
     };
     if (warp >= 2) {
         const int wrow = n0 + quad * 32 + lane;         // this thread's weight row
@@ -163,6 +169,9 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
         mbar_init(acc_full, 1);
         *abort_flag = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // first lap of the x ring: every slot is free, nothing to wait for, and the loads need
+        // neither the tensor memory nor the other warps, so they start before the CTA barrier
+        for (int u = 0; u < P && u < U; u++) load_x_unit(u, u);
     }
     if (warp == 1) {
         tmem_alloc(smem_u32(tmem_slot), WA_TMEM_COLS);
@@ -180,16 +189,11 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
         // =============================== TMA producer of x ==============================
         if (lane == 0) {
             int s = 0;
-            uint32_t ph = 0;
-            for (int u = 0; u < U; u++) {
+            uint32_t ph = 1;                  // second lap onwards: the first was issued above
+            for (int u = P; u < U; u++) {
                 if (!mbar_wait_relaxed(empty(s), ph ^ 1u, abort_flag)) break;
                 TRACE(10);
-                mbar_expect_tx(full(s), WA_UNIT_X_BYTES);
-                // byte coordinates: the map describes x as [M][2K bytes]; two 64-K boxes per unit
-                const uint32_t dst = smem_u32(x_ring + (size_t)s * WA_UNIT_X_BYTES);
-                const int kbyte = (k_base + u * WA_UNIT_K) * 2;
-                tma_load_2d(dst, &map_x, kbyte, m0, full(s));
-                tma_load_2d(dst + WA_X_BYTES, &map_x, kbyte + 128, m0, full(s));
+                load_x_unit(u, s);
                 if (++s == P) { s = 0; ph ^= 1u; }
             }
         }
@@ -231,7 +235,7 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
 #pragma unroll
             for (int i = 0; i < 4; i++) cq[i] = nq[i];
             uint32_t zc, sa, sb;
-            group_consts<BF16>(nsh, nzp, zc, sa, sb);
+            group_consts<BF16>(nsh, (nzb >> (((g_base + u) & 1) * 4)) & 0xFu, zc, sa, sb);
             if (u + NG < U) fetch(u + NG);
             const int s = u % P;
             const uint32_t ph = (uint32_t)(u / P) & 1u;
