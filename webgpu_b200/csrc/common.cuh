@@ -11,6 +11,7 @@
 #include <cstdio>
 #include <mutex>
 #include <string>
+#include <utility>
 
 #include "lux/gpu/backend_plugin.h"
 #include "lux/gpu/qmatmul_ext.h"
@@ -99,10 +100,53 @@ struct Tunables {
     int gemm_tc_stages = 0;
     int gemm_tc_splitk = 0;      // weights-in-TMEM GEMM: K splits over a CTA pair, 1 or 2 (0 = choose)
     int gemm_tc_groups = 0;      // weights-in-TMEM GEMM: converter groups of four warps, 2..4
+    int pdl = 0;                 // programmatic dependent launch of the persistent kernels: 0/1 on, 2 off
     int gemm_tc_kernel = 0;      // 0 auto, 1 lux_qgemm_i4_tc, 2 lux_qgemm_i4_tc_wa wherever it applies
     int gemm_tc_ma = 0;          // GEMM: batch tiles (128 rows) per CTA, 1 or 2 (0 = choose)
 };
 extern Tunables g_tune;
+
+// ---- programmatic dependent launch --------------------------------------------------------
+// The persistent GEMV kernels and the weights-in-TMEM GEMM are launched with the programmatic
+// stream serialization attribute: the grid may be set up while the previous kernel of the stream
+// is still running, so that its CTAs start the moment SMs free up instead of one launch latency
+// after the previous grid has drained.  Each of these kernels
+//   * calls pdl_launch_dependents() first (the next such kernel may be set up behind it), and
+//   * touches only static model state (weights, scales, zero-points) until pdl_wait(), which
+//     returns when every earlier kernel of the stream has completed and its writes are visible;
+//     activations are read, and anything is written, only after it.
+// In a kernel launched without the attribute both calls do nothing.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kfn)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, unsigned cluster_z,
+                              Args&&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    unsigned n = 0;
+    if (cluster_z > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = 1;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = cluster_z;
+        n++;
+    }
+    if (g_tune.pdl != 2) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        n++;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    return cudaLaunchKernelEx(&cfg, kfn, std::forward<Args>(args)...);
+}
+#endif
 
 // ---- kernel launchers (defined in the .cu file named after each kernel family) ------
 

@@ -112,6 +112,7 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
 
     TRACE_DECL;
     TRACE(1);
+    pdl_launch_dependents();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.x * BM;                 // first weight row of the tile
     const int m0 = blockIdx.y * WA_BN;              // first batch row of the tile
@@ -170,7 +171,11 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
         *abort_flag = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         // first lap of the x ring: every slot is free, nothing to wait for, and the loads need
-        // neither the tensor memory nor the other warps, so they start before the CTA barrier
+        // neither the tensor memory nor the other warps, so they start before the CTA barrier.
+        // x may come from the previous kernel of the stream (the weights fetched above are
+        // static): wait for it here; the CTA barrier below orders every other thread's later
+        // reads and the output stores behind this wait.
+        pdl_wait();
         for (int u = 0; u < P && u < U; u++) load_x_unit(u, u);
     }
     if (warp == 1) {
@@ -382,19 +387,7 @@ cudaError_t launch_wa(const CUtensorMap& mx, const WaParams& p, dim3 grid, int t
         if (e != cudaSuccess) return e;
         configured[dev].store(smem, std::memory_order_relaxed);
     }
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = grid;
-    cfg.blockDim = dim3((unsigned)threads);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = KS;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kfn, mx, p);
+    return launch_pdl(kfn, grid, dim3((unsigned)threads), smem, st, (unsigned)KS, mx, p);
 }
 
 }  // namespace

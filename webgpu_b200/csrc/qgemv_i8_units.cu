@@ -148,13 +148,9 @@ lux_qgemv_i8_g32_units_fx(const __grid_constant__ CUtensorMap map_w, const I8Uni
     const int my_chunks = my_units * NC;
     const int nrows = ntiles * 16;
 
-    // the first 32 bytes of x this thread converts: requested before anything else
+    pdl_launch_dependents();
     const int npieces = p.M * p.K / 8;                   // pieces of 8 floats, (m, group, quarter)
-    uint4 xa = make_uint4(0u, 0u, 0u, 0u), xb = xa;
-    if (tid < npieces) {
-        xa = __ldg(reinterpret_cast<const uint4*>(p.x) + 2 * tid);
-        xb = __ldg(reinterpret_cast<const uint4*>(p.x) + 2 * tid + 1);
-    }
+    uint4 xa, xb;
 
     // ---- barriers and the first weight request: the very first thing every warp does ----------
     uint64_t policy = 0;
@@ -207,12 +203,13 @@ lux_qgemv_i8_g32_units_fx(const __grid_constant__ CUtensorMap map_w, const I8Uni
         asm volatile("cp.async.commit_group;" ::: "memory");
     }
 
+    // Everything above read static model state only; x may come from the previous kernel.
+    pdl_wait();
+
     // ---- x -> block fixed point, three signed byte planes in K order -----------------------------
     for (int c = tid; c < npieces; c += UW * 32) {
-        if (c != tid) {
-            xa = __ldg(reinterpret_cast<const uint4*>(p.x) + 2 * c);
-            xb = __ldg(reinterpret_cast<const uint4*>(p.x) + 2 * c + 1);
-        }
+        xa = __ldg(reinterpret_cast<const uint4*>(p.x) + 2 * c);
+        xb = __ldg(reinterpret_cast<const uint4*>(p.x) + 2 * c + 1);
         const int per_row = p.K / 8;
         const int m = (MM == 2 && c >= per_row) ? 1 : 0, cr = c - m * per_row;
         const int grp = cr >> 2, l4 = cr & 3;
@@ -388,8 +385,7 @@ cudaError_t launch_inst(const CUtensorMap& map, const I8UnitsParams& p, int grid
         if (e != cudaSuccess) return e;
         configured[dev & 63].store(smem, std::memory_order_relaxed);
     }
-    kfn<<<grid, UW * 32, smem, st>>>(map, p);
-    return cudaGetLastError();
+    return launch_pdl(kfn, dim3((unsigned)grid), dim3(UW * 32), smem, st, 1, map, p);
 }
 
 }  // namespace

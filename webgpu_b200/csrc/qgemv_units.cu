@@ -539,10 +539,8 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
     const int my_chunks = my_units * NC;
     const int rows_half = ntiles * 16;
 
-    // the first 16 bytes of x this thread converts: requested before anything else
+    pdl_launch_dependents();
     const int npieces = p.M * p.G * 16;                  // 16-byte pieces of x, (m, group, 16th)
-    uint4 x_first = make_uint4(0u, 0u, 0u, 0u);
-    if (tid < npieces) x_first = __ldg(reinterpret_cast<const uint4*>(p.x) + tid);
 
     // ---- barriers and the first weight request: the very first thing every warp does ----------
     // exact division of a small number by a small constant: multiply by ceil(2^32 / d)
@@ -613,9 +611,12 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
             reinterpret_cast<uint32_t*>(zsm)[i] = 0x88888888u;
     TRACE(11);
 
+    // Everything above read static model state only; x may come from the previous kernel.
+    pdl_wait();
+
     // ---- x -> block fixed point, three signed byte planes in B-fragment order -----------------
     for (int c = tid; c < npieces; c += UW * 32) {
-        const uint4 s4 = c == tid ? x_first : __ldg(reinterpret_cast<const uint4*>(p.x) + c);
+        const uint4 s4 = __ldg(reinterpret_cast<const uint4*>(p.x) + c);
         const int m = (MM == 2 && c >= p.G * 16) ? 1 : 0, cg16 = c - m * p.G * 16;
         const int grp = cg16 >> 4, l16 = cg16 & 15;
         float v[8];
@@ -926,8 +927,7 @@ cudaError_t launch_units_fx_inst(const CUtensorMap& map, const UnitsParams& p, i
         if (e != cudaSuccess) return e;
         configured[dev & 63].store(smem, std::memory_order_relaxed);
     }
-    kfn<<<grid, UW * 32, smem, st>>>(map, p);
-    return cudaGetLastError();
+    return launch_pdl(kfn, dim3((unsigned)grid), dim3(UW * 32), smem, st, 1, map, p);
 }
 
 template <int MM, bool SW>
