@@ -52,6 +52,7 @@ constexpr int WA_MAX_UNITS = 3;            // ring depth: 3 x 64 KB of x in shar
 constexpr int WA_MAX_GROUPS = 3;           // converter groups <= ring depth
 constexpr int WA_MAX_THREADS = (2 + 4 * WA_MAX_GROUPS) * 32;
 constexpr uint32_t WA_TMEM_COLS = 512;     // accumulator [0, 256) + A units [256, 448)
+constexpr int WA_RECV_BYTES = 64 * BM * 4;  // one round of the split-K exchange: 2 column halves x 32 columns x 128 rows x f32
 constexpr int WA_STAGE_PITCH = 320;        // bytes per batch row of the staged output tile: 256 + 64, so that the
                                            // even and the odd lanes of a staging store use different banks
 
@@ -105,7 +106,7 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const int P = p.stages;                          // ring depth in units of 128 K
     unsigned char* x_ring = smem;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(x_ring + (size_t)P * WA_UNIT_X_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(x_ring + (size_t)P * WA_UNIT_X_BYTES + (KS == 2 ? WA_RECV_BYTES : 0));
     // bars[0..P) full, [P..2P) empty, [2P] acc_full
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * P + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
@@ -113,6 +114,7 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
     TRACE_DECL;
     TRACE(1);
     pdl_launch_dependents();
+    if (KS == 2) cluster_arrive();                  // matched by cluster_wait() before the first remote store
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.x * BM;                 // first weight row of the tile
     const int m0 = blockIdx.y * WA_BN;              // first batch row of the tile
@@ -175,13 +177,17 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
         // x may come from the previous kernel of the stream (the weights fetched above are
         // static): wait for it here; the CTA barrier below orders every other thread's later
         // reads and the output stores behind this wait.
+        TRACE(6);
         pdl_wait();
+        TRACE(4);
         for (int u = 0; u < P && u < U; u++) load_x_unit(u, u);
+        TRACE(5);
     }
     if (warp == 1) {
         tmem_alloc(smem_u32(tmem_slot), WA_TMEM_COLS);
         tmem_relinquish();
     }
+    TRACE(3);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -279,9 +285,12 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
     TRACE(40);
 
     // =============================== epilogue ===========================================
-    // Warps 2..9: quarter `quad` of the lanes (weight rows), half `eh` of the columns handled.
-    // The ring is idle by now and is reused: [0, 64 KB) partial sums received from the peer
-    // (KS == 2), then the narrowed output tile staged for row-wise 16-byte stores.
+    // Warps 2..9: quarter `quad` of the lanes (weight rows), half `eh` of the columns handled,
+    // in chunks of 32 columns.  KS == 2: the peer's partial sums arrive in two rounds of 32 KB,
+    // the first into a buffer of its own behind the ring (it can be sent before anything is
+    // known about the peer's progress), the second into the peer's ring once the first cluster
+    // barrier has shown it idle; the narrowed output tile is then staged in the ring for
+    // row-wise 16-byte stores.
     const int eh = (warp - 2) >> 2;
     const bool ep_warp = warp >= 2 && warp < 10;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
@@ -289,62 +298,73 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
     const int keep0 = KS == 1 ? 0 : ksplit * (WA_BN / 2);       // first accumulator column this CTA writes
     constexpr int KEEP = WA_BN / KS;                            // columns this CTA writes
     constexpr int PER_WARP = KEEP / 2;                          // per epilogue warp
-    // received partial sums: 16 bytes (4 columns) per weight row, rows consecutive, so that a
-    // warp's remote store is one contiguous 512-byte piece
-    unsigned char* recv = x_ring;
-    unsigned char* stage = x_ring + (KS == 2 ? (WA_BN / 2) * BM * 4 : 0);   // [column][WA_STAGE_PITCH bytes]
+    // received partial sums of a round: 16 bytes (4 columns) per weight row, rows consecutive, so
+    // that a warp's remote store is one contiguous 512-byte piece; [16 column quads][128 rows]
+    unsigned char* recv1 = x_ring + (size_t)P * WA_UNIT_X_BYTES;             // round 1 (KS == 2 only)
+    unsigned char* recv2 = x_ring;                                           // round 2
+    unsigned char* stage = x_ring + (KS == 2 ? WA_RECV_BYTES : 0);           // [column][WA_STAGE_PITCH bytes]
+    const bool odd = lane & 1;
+    // lanes pair up: the even lane stages (row, row + 1) of the even columns, the odd lane of the odd ones
+    unsigned char* srow = stage + (quad * 32 + (lane & ~1)) * 2;
+
+    // 32 accumulator columns of the peer's half -> the peer's receive buffer `dst` (a
+    // shared::cluster address of the buffer's start), column quad q0 onwards
+    auto send_chunk = [&](int col, uint32_t dst, int q0) {
+        uint32_t acc[32];
+        tmem_ld32(lane_addr + (uint32_t)col, acc);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i += 4)
+            st_cluster_v4(dst + (uint32_t)(((q0 + (i >> 2)) * BM + my_row) * 16), acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+    };
+    // 32 columns c0.. of this CTA's own half: add what the peer sent (column quad q0 onwards of
+    // `rsrc`), narrow once, stage
+    auto finalize_chunk = [&](int c0, const unsigned char* rsrc, int q0) {
+        uint32_t acc[32];
+        tmem_ld32(lane_addr + (uint32_t)(keep0 + c0), acc);
+        tmem_ld_wait();
+        if (KS == 2) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const float4 r = *reinterpret_cast<const float4*>(rsrc + ((q0 + i) * BM + my_row) * 16);
+                acc[4 * i + 0] = __float_as_uint(__uint_as_float(acc[4 * i + 0]) + r.x);
+                acc[4 * i + 1] = __float_as_uint(__uint_as_float(acc[4 * i + 1]) + r.y);
+                acc[4 * i + 2] = __float_as_uint(__uint_as_float(acc[4 * i + 2]) + r.z);
+                acc[4 * i + 3] = __float_as_uint(__uint_as_float(acc[4 * i + 3]) + r.w);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+            const float mine = __uint_as_float(odd ? acc[i + 1] : acc[i]);
+            const float give = __uint_as_float(odd ? acc[i] : acc[i + 1]);
+            const float got = __shfl_xor_sync(0xffffffffu, give, 1);
+            const uint32_t v = odd ? pack2<BF16>(got, mine) : pack2<BF16>(mine, got);
+            *reinterpret_cast<uint32_t*>(srow + (c0 + i + (odd ? 1 : 0)) * WA_STAGE_PITCH) = v;
+        }
+    };
 
     if (KS == 2) {
-        cluster_sync_all();          // both CTAs are done with their rings
+        const int send0 = (1 - ksplit) * (WA_BN / 2);
+        const uint32_t peer1 = map_to_cta(smem_u32(recv1), (uint32_t)(1 - ksplit));
+        const uint32_t peer2 = map_to_cta(smem_u32(recv2), (uint32_t)(1 - ksplit));
+        cluster_wait();              // completes the arrival made at kernel start: the peer CTA runs
+        if (ep_warp && ok) send_chunk(send0 + eh * PER_WARP, peer1, eh * 8);
         TRACE(41);
-        if (ep_warp && ok) {
-            const int send0 = (1 - ksplit) * (WA_BN / 2);
-            const uint32_t peer = map_to_cta(smem_u32(recv), (uint32_t)(1 - ksplit)) + (uint32_t)(my_row * 16);
-#pragma unroll 1
-            for (int c0 = eh * PER_WARP; c0 < (eh + 1) * PER_WARP; c0 += 32) {
-                uint32_t acc[32];
-                tmem_ld32(lane_addr + (uint32_t)(send0 + c0), acc);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 32; i += 4)
-                    st_cluster_v4(peer + (uint32_t)(((c0 + i) >> 2) * (BM * 16)), acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
-            }
-        }
+        cluster_sync_all();          // both CTAs are done with their rings; round 1 has arrived
         TRACE(42);
-        cluster_sync_all();          // the peer's partial sums have arrived
+        if (ep_warp && ok) {
+            send_chunk(send0 + eh * PER_WARP + 32, peer2, eh * 8);
+            finalize_chunk(eh * PER_WARP, recv1, eh * 8);
+        }
+        cluster_sync_all();          // round 2 has arrived
         TRACE(43);
+        if (ep_warp && ok) finalize_chunk(eh * PER_WARP + 32, recv2, eh * 8);
+    } else if (ep_warp && ok) {
+#pragma unroll 1
+        for (int c0 = eh * PER_WARP; c0 < (eh + 1) * PER_WARP; c0 += 32) finalize_chunk(c0, nullptr, 0);
     }
     if (ep_warp) {
-        if (ok) {
-            const bool odd = lane & 1;
-            // lanes pair up: the even lane stages (row, row + 1) of the even columns, the odd lane of the odd ones
-            unsigned char* srow = stage + (quad * 32 + (lane & ~1)) * 2;
-#pragma unroll 1
-            for (int c0 = eh * PER_WARP; c0 < (eh + 1) * PER_WARP; c0 += 32) {
-                uint32_t acc[32];
-                tmem_ld32(lane_addr + (uint32_t)(keep0 + c0), acc);
-                tmem_ld_wait();
-                if (KS == 2) {
-#pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        const float4 r = *reinterpret_cast<const float4*>(recv + (((c0 >> 2) + i) * BM + my_row) * 16);
-                        acc[4 * i + 0] = __float_as_uint(__uint_as_float(acc[4 * i + 0]) + r.x);
-                        acc[4 * i + 1] = __float_as_uint(__uint_as_float(acc[4 * i + 1]) + r.y);
-                        acc[4 * i + 2] = __float_as_uint(__uint_as_float(acc[4 * i + 2]) + r.z);
-                        acc[4 * i + 3] = __float_as_uint(__uint_as_float(acc[4 * i + 3]) + r.w);
-                    }
-                }
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const float mine = __uint_as_float(odd ? acc[i + 1] : acc[i]);
-                    const float give = __uint_as_float(odd ? acc[i] : acc[i + 1]);
-                    const float got = __shfl_xor_sync(0xffffffffu, give, 1);
-                    const uint32_t v = odd ? pack2<BF16>(got, mine) : pack2<BF16>(mine, got);
-                    *reinterpret_cast<uint32_t*>(srow + (c0 + i + (odd ? 1 : 0)) * WA_STAGE_PITCH) = v;
-                }
-            }
-            tc_fence_before();
-        }
+        if (ok) tc_fence_before();
         // the eight epilogue warps (and only they) meet here on every path
         asm volatile("bar.sync 1, 256;" ::: "memory");
         TRACE(46);
@@ -408,7 +428,7 @@ LuxBackendError launch_qgemm_i4_tc_wa(Context* ctx, const QArgs& a) {
     const int stages = g_tune.gemm_tc_stages >= 2 && g_tune.gemm_tc_stages <= WA_MAX_UNITS ? g_tune.gemm_tc_stages : WA_MAX_UNITS;
     int groups = g_tune.gemm_tc_groups >= 2 && g_tune.gemm_tc_groups <= WA_MAX_GROUPS ? g_tune.gemm_tc_groups : 2;
     groups = std::min(groups, stages);
-    const size_t smem = 1024 + (size_t)stages * WA_UNIT_X_BYTES + 512;
+    const size_t smem = 1024 + (size_t)stages * WA_UNIT_X_BYTES + (ks == 2 ? WA_RECV_BYTES : 0) + 512;
 
     CUtensorMap mx;
     const uint64_t dims[2] = {(uint64_t)a.K * 2, (uint64_t)a.M};
