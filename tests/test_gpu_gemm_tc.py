@@ -66,8 +66,8 @@ def test_gemm_tile_and_stage_choices(ctx, backend, bn, stages, ma):
 
 @pytest.mark.parametrize("M", [129, 256, 300, 512])
 def test_gemm_two_batch_tiles(ctx, backend, M):
-    """Batches above 128 rows use two batch tiles per CTA by default (one converted weight tile,
-    two accumulators); ragged last tiles included."""
+    """Batches above 128 rows, ragged last tiles included, with whichever kernel and tile choice
+    is the default for them."""
     x = synth.activations(M, 512, "f16", 33, f"g2.x{M}")
     layer = synth.int4_layer(192, 512, 33, "g2")
     ref = _oracle(x, layer)

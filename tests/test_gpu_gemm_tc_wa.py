@@ -45,7 +45,8 @@ class _Tuned:
 
 @pytest.mark.parametrize("dtype", ["bf16", "f16"])
 @pytest.mark.parametrize("splitk", [1, 2])
-@pytest.mark.parametrize("M,N,K", [(256, 128, 256), (129, 128, 512), (300, 256, 512), (512, 384, 1024), (40, 128, 256)])
+@pytest.mark.parametrize("M,N,K", [(256, 128, 256), (129, 128, 512), (300, 256, 512), (512, 384, 1024), (40, 128, 256),
+                                   (33, 256, 512), (64, 128, 1024), (100, 256, 256), (128, 128, 512), (200, 128, 256)])
 def test_wa_shapes(ctx, backend, dtype, splitk, M, N, K):
     """Whole and ragged batch tiles, one and several weight tiles, both K splits; the kernel is
     forced (gemm_tc_kernel = 2) so that batches of 128 rows and fewer run it too."""
@@ -83,7 +84,7 @@ def test_wa_symmetric_weights(ctx, backend):
     assert orc.rel_l2(y, _oracle(x, layer)) < TOL_16
 
 
-def test_wa_is_default_above_128_rows(ctx, backend):
+def test_wa_is_default_for_plain_gemms(ctx, backend):
     """Config 3 (512 x 4096 x 4096, bf16) takes this kernel by default and agrees with the
     other tcgen05 kernel to accumulation order."""
     x, layer = synth.config3()

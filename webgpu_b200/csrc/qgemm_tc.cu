@@ -82,7 +82,8 @@ lux_qgemm_i4_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     unsigned char* b_ring = a_ring + (size_t)S * A_BYTES;
     unsigned char* q_ring = b_ring + (size_t)S * B_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(q_ring + (size_t)S * Q_BYTES);
-    // bars[0..S) full_ld, [S..2S) full_b, [2S..3S) empty, [3S] acc_full, [3S+1] meta_full
+    // bars[0..S) full_ld (per stage), [S..S+S/2) full_b and [2S..2S+S/2) empty (per PAIR of
+    // stages = 128 K), [3S] acc_full, [3S+1] meta_full.  S is even.
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * S + 2);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     unsigned char* meta = reinterpret_cast<unsigned char*>(bars) + 512;      // 16-byte aligned
@@ -102,8 +103,10 @@ lux_qgemm_i4_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     if (tid == 0) {
         for (int s = 0; s < S; s++) {
             mbar_init(full_ld(s), 1);
-            mbar_init(full_b(s), NUM_DQ_WARPS);
-            mbar_init(empty(s), 1);
+            if ((s & 1) == 0) {
+                mbar_init(full_b(s >> 1), 2 * NUM_DQ_WARPS);   // every converting warp, once per stage of the pair
+                mbar_init(empty(s >> 1), 1);
+            }
         }
         mbar_init(acc_full, 1);
         mbar_init(meta_full, 1);
@@ -139,7 +142,7 @@ lux_qgemm_i4_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             int s = 0;
             uint32_t ph = 0;
             for (int kb = 0; kb < KB; kb++) {
-                if (!mbar_wait(empty(s), ph ^ 1u, abort_flag)) break;
+                if ((s & 1) == 0 && !mbar_wait_relaxed(empty(s >> 1), ph ^ 1u, abort_flag)) break;
                 mbar_expect_tx(full_ld(s), A_BYTES + Q_BYTES);
                 tma_load_2d(smem_u32(a_ring + (size_t)s * A_BYTES), &map_x, kb * BK, m0, full_ld(s));
                 tma_load_2d(smem_u32(q_ring + (size_t)s * Q_BYTES), &map_w, kb * (BK / 2), n0, full_ld(s));
@@ -154,25 +157,34 @@ lux_qgemm_i4_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc(BF16, NB);
             bool ok = true;
+            // One wait and one commit per PAIR of stages (128 K): a satisfied mbarrier wait costs
+            // this thread 200-250 cycles and a commit ~100, which per 64-K stage (with a second
+            // wait for the loads) added up to more than the stage's MMAs.  The converters wait
+            // for a stage's loads (x tile included) before they arrive, so their barrier alone
+            // tells that the x tile has landed too.
             int s = 0;
             uint32_t ph = 0;
-            for (int kb = 0; kb < KB && ok; kb++) {
-                ok = mbar_wait(full_ld(s), ph, abort_flag) && mbar_wait(full_b(s), ph, abort_flag);
+            for (int kb = 0; kb < KB && ok; kb += 2) {
+                ok = mbar_wait(full_b(s >> 1), ph, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
-                const uint64_t a_desc = make_kmajor_sw128_desc(smem_u32(a_ring + (size_t)s * A_BYTES));
-                const uint64_t b_desc = make_kmajor_sw128_desc(smem_u32(b_ring + (size_t)s * B_BYTES));
 #pragma unroll
-                for (int k = 0; k < BK / 16; k++) {
-                    // +32 bytes per 16 K inside the swizzle row: +2 in the 16-byte address field;
-                    // batch tile a is 16 KB (1024 in the address field) further on
+                for (int b = 0; b < 2; b++) {
+                    const uint64_t a_desc = make_kmajor_sw128_desc(smem_u32(a_ring + (size_t)(s + b) * A_BYTES));
+                    const uint64_t b_desc = make_kmajor_sw128_desc(smem_u32(b_ring + (size_t)(s + b) * B_BYTES));
 #pragma unroll
-                    for (int a = 0; a < MA; a++)
-                        umma_f16(tmem_base + (uint32_t)(a * NB), a_desc + (uint64_t)(a * 1024 + 2 * k),
-                                 b_desc + (uint64_t)(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
+                    for (int k = 0; k < BK / 16; k++) {
+                        // +32 bytes per 16 K inside the swizzle row: +2 in the 16-byte address field;
+                        // batch tile a is 16 KB (1024 in the address field) further on
+#pragma unroll
+                        for (int a = 0; a < MA; a++)
+                            umma_f16(tmem_base + (uint32_t)(a * NB), a_desc + (uint64_t)(a * 1024 + 2 * k),
+                                     b_desc + (uint64_t)(2 * k), idesc, (kb | b | k) != 0 ? 1u : 0u);
+                    }
                 }
-                umma_commit(empty(s));        // stage reusable once these MMAs have read it
-                if (++s == S) { s = 0; ph ^= 1u; }
+                umma_commit(empty(s >> 1));   // both stages reusable once these MMAs have read them
+                s += 2;
+                if (s == S) { s = 0; ph ^= 1u; }
             }
             if (ok) umma_commit(acc_full);    // accumulators complete
         }
@@ -247,7 +259,7 @@ lux_qgemm_i4_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             }
             fence_proxy_async_smem();          // generic-proxy stores -> visible to the tensor core
             __syncwarp();
-            if (lane == 0) mbar_arrive(full_b(s));
+            if (lane == 0) mbar_arrive(full_b(s >> 1));
             if (++s == S) { s = 0; ph ^= 1u; }
         }
 
@@ -385,28 +397,37 @@ LuxBackendError launch_qgemm_i4_tc(Context* ctx, const QArgs& a) {
     const int nout = a.swiglu ? a.N / 2 : a.N;
     if (a.K % 128 || nout % 8) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
 
-    int bn = g_tune.gemm_tc_bn > 0 ? g_tune.gemm_tc_bn : 128;
+    // Tile choice (measured on B200; the conversion of the weight tile is what bounds this kernel).
+    // SwiGLU above 128 batch rows: 64 outputs (128 weight rows) per CTA and two batch tiles, so a
+    // converted tile serves 256 rows (Llama-70B gate_up quarter at M = 256: 74 us against 107 us
+    // with 128 outputs and one batch tile).  Otherwise 128 weight rows and one batch tile: two
+    // batch tiles leave a 128-wide tile only two pairs of stages (config 3: 56 us against 40 us).
+    const bool wide_batch = a.swiglu && a.M > BM;
+    int bn = g_tune.gemm_tc_bn > 0 ? g_tune.gemm_tc_bn : (wide_batch ? 64 : 128);
     bn = (bn >= 128 && !a.swiglu) ? 128 : (a.swiglu ? (bn >= 128 ? 128 : 64) : 64);
     const int nb = a.swiglu ? 2 * bn : bn;
-    // Two batch tiles per CTA (256 rows share one converted weight tile) when the batch has them
-    // and two accumulators fit TMEM (2 * nb <= 512 columns): the conversion of a weight tile, the
-    // instruction-bound part of the kernel, is then paid once per 256 rows instead of per 128.
-    int ma = (a.M > BM && 2 * nb <= 512) ? 2 : 1;
-    if (g_tune.gemm_tc_ma == 1 || g_tune.gemm_tc_ma == 2) ma = (g_tune.gemm_tc_ma == 2 && 2 * nb <= 512) ? 2 : 1;
+    // Two batch tiles per CTA need two accumulators in TMEM (2 * nb <= 512 columns) and, because
+    // the ring is handed over in pairs of stages, room for four stages.
+    int ma = wide_batch ? 2 : 1;
+    if (g_tune.gemm_tc_ma == 1 || g_tune.gemm_tc_ma == 2) ma = g_tune.gemm_tc_ma;
+    if (ma == 2 && (2 * nb > 512 ||
+                    1024 + 4 * ((size_t)2 * BM * 128 + (size_t)nb * 128 + (size_t)nb * 32) + 512 > (size_t)226 * 1024))
+        ma = 1;
     const size_t stage_bytes = (size_t)ma * BM * 128 + (size_t)nb * 128 + (size_t)nb * 32;
     // Scales and zero-points of the CTA's rows go to shared memory when every block is a
-    // 16-byte aligned, 16-byte multiple copy and the table leaves room for >= 3 stages.
+    // 16-byte aligned, 16-byte multiple copy and the table leaves room for >= 4 stages.
     const int zs = (a.G + 1) / 2;
     const size_t meta_scale_bytes = (size_t)nb * a.G * 2;
     const size_t meta_bytes = meta_scale_bytes + (a.zeros ? (size_t)nb * zs : 0);
     const size_t budget = 226 * 1024;
     bool meta_smem = nout % bn == 0 && ((size_t)bn * a.G * 2) % 16 == 0 && ((size_t)bn * zs) % 16 == 0 &&
                      (!a.swiglu || (((size_t)nout * a.G * 2) % 16 == 0 && ((size_t)nout * zs) % 16 == 0)) &&
-                     1024 + 3 * stage_bytes + 512 + meta_bytes <= budget;
+                     1024 + 4 * stage_bytes + 512 + meta_bytes <= budget;
     const size_t tail = 512 + (meta_smem ? meta_bytes : 0);
     int stages = g_tune.gemm_tc_stages > 0 ? g_tune.gemm_tc_stages : 6;
     while (stages > 2 && 1024 + (size_t)stages * stage_bytes + tail > budget) stages--;
     stages = std::min(stages, std::max(2, a.K / BK));
+    stages &= ~1;                                     // the ring is handed over in pairs of stages (128 K)
     const size_t smem = 1024 + (size_t)stages * stage_bytes + tail;
 
     CUtensorMap mx, mw;

@@ -1,5 +1,5 @@
 // int4 g128 weight-only GEMM on tcgen05 with the converted WEIGHTS as the tensor-memory A
-// operand, for prefill batches above 128 rows.
+// operand: the default for every batch the tensor-core route takes (M >= 33) without SwiGLU.
 //
 //   y[M, N] = x[M, K] . dequant(W[N, K])^T      x, y bf16 or f16; f32 accumulate in TMEM
 //
@@ -80,6 +80,7 @@ struct WaParams {
     int M, N, K, G, ZS;
     int stages;               // ring depth in units of 128 K (x in shared memory, A in TMEM)
     int groups;               // converter groups of four warps, <= stages
+    int ncols;                // batch rows per tile = UMMA N: 256, or the batch rounded up to 16 when it is smaller
 };
 
 // Group constants of one weight row: zero-point pair and the scale (bf16: split in two).
@@ -130,7 +131,7 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
     const uint32_t acc_full = bar0 + 8u * (uint32_t)(2 * P);
 
     auto load_x_unit = [&](int u, int s) {
-        mbar_expect_tx(full(s), WA_UNIT_X_BYTES);
+        mbar_expect_tx(full(s), (uint32_t)(2 * p.ncols * 128));
         // byte coordinates: the map describes x as [M][2K bytes]; two 64-K boxes per unit
         const uint32_t dst = smem_u32(x_ring + (size_t)s * WA_UNIT_X_BYTES);
         const int kbyte = (k_base + u * WA_UNIT_K) * 2;
@@ -213,7 +214,7 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
         // One wait, eight MMAs and one commit per unit: a satisfied mbarrier wait and a commit
         // cost this thread ~200 and ~100 cycles, so they are paid once per 128 K, not per 64.
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(BF16, WA_BN);
+            const uint32_t idesc = make_idesc(BF16, p.ncols);
             int s = 0;
             uint32_t ph = 0;
             for (int u = 0; u < U; u++) {
@@ -309,7 +310,9 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
 
     // 32 accumulator columns of the peer's half -> the peer's receive buffer `dst` (a
     // shared::cluster address of the buffer's start), column quad q0 onwards
+    // (chunks that lie entirely beyond the batch's columns are skipped, by sender and receiver alike)
     auto send_chunk = [&](int col, uint32_t dst, int q0) {
+        if (col >= p.ncols) return;
         uint32_t acc[32];
         tmem_ld32(lane_addr + (uint32_t)col, acc);
         tmem_ld_wait();
@@ -320,6 +323,7 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
     // 32 columns c0.. of this CTA's own half: add what the peer sent (column quad q0 onwards of
     // `rsrc`), narrow once, stage
     auto finalize_chunk = [&](int c0, const unsigned char* rsrc, int q0) {
+        if (keep0 + c0 >= p.ncols) return;
         uint32_t acc[32];
         tmem_ld32(lane_addr + (uint32_t)(keep0 + c0), acc);
         tmem_ld_wait();
@@ -412,8 +416,8 @@ cudaError_t launch_wa(const CUtensorMap& mx, const WaParams& p, dim3 grid, int t
 
 }  // namespace
 
-// Takes plain (no SwiGLU, no push) int4 GEMMs whose weight rows come in whole tiles of 128 and
-// whose batch is above 128 rows; everything else stays with lux_qgemm_i4_tc.
+// Takes plain (no SwiGLU, no push) int4 GEMMs whose weight rows come in whole tiles of 128;
+// everything else stays with lux_qgemm_i4_tc.
 LuxBackendError launch_qgemm_i4_tc_wa(Context* ctx, const QArgs& a) {
     if (a.swiglu || a.push || a.N % BM || a.K % 128 || a.M < 1) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
     if (a.scale_dtype != LUX_QDTYPE_F16 || a.x_dtype != a.y_dtype) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
@@ -433,7 +437,8 @@ LuxBackendError launch_qgemm_i4_tc_wa(Context* ctx, const QArgs& a) {
     CUtensorMap mx;
     const uint64_t dims[2] = {(uint64_t)a.K * 2, (uint64_t)a.M};
     const uint64_t strides[1] = {(uint64_t)a.K * 2};
-    const uint32_t box[2] = {128, (uint32_t)WA_BN};
+    const int ncols = a.M >= WA_BN ? WA_BN : (a.M + 15) / 16 * 16;
+    const uint32_t box[2] = {128, (uint32_t)ncols};
     if (!encode_tensor_map_u8(&mx, 2, a.x, dims, strides, box, true)) return LUX_BACKEND_ERROR_INTERNAL;
 
     WaParams p{};
@@ -445,6 +450,7 @@ LuxBackendError launch_qgemm_i4_tc_wa(Context* ctx, const QArgs& a) {
     p.M = a.M; p.N = a.N; p.K = a.K; p.G = a.G; p.ZS = (a.G + 1) / 2;
     p.stages = stages;
     p.groups = groups;
+    p.ncols = ncols;
 
     dim3 grid(a.N / BM, (a.M + WA_BN - 1) / WA_BN, ks);
     const int threads = (2 + 4 * groups) * 32;                  // groups >= 2: the epilogue needs warps 2..9
