@@ -97,3 +97,45 @@ def test_wa_is_default_for_plain_gemms(ctx, backend):
         assert backend.last_kernel_name() == "lux_qgemm_i4_tc_bf16"
     assert orc.rel_l2(y, y_old) < 1e-3
     assert ctx.last_device_status() == 0
+
+
+def _run_swiglu(ctx, x, gate_up):
+    L = ctx.upload_layer(gate_up)
+    xb = ctx.upload(x)
+    M, n_out = x.shape[0], gate_up.N // 2
+    hb = ctx.alloc(M * n_out * 2)
+    ctx.qmatmul(xb, L, hb, M, B.np_dtype_code(x), flags=B.FLAG_SWIGLU)
+    return hb.to_host(x.dtype, (M, n_out))
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+@pytest.mark.parametrize("splitk", [1, 2])
+@pytest.mark.parametrize("M,K,I", [(256, 512, 128), (96, 256, 64), (300, 512, 192), (33, 1024, 64)])
+def test_wa_swiglu_epilogue(ctx, backend, dtype, splitk, M, K, I):
+    """gate_up with the SwiGLU epilogue (steel_gemm_fused.wgsl:91-94, 452-558): gate rows on TMEM
+    lanes 0..63, up rows on 64..127, combined in the write-out pass; whole and ragged batch tiles,
+    one and several output tiles, both K splits."""
+    gate_up, _ = synth.mlp_layers(K, I, 128, 44, f"wasw.{K}.{I}")
+    x = synth.activations(M, K, dtype, 44, f"wasw.x.{M}.{K}")
+    with _Tuned(backend, gemm_tc_kernel=2, gemm_tc_splitk=splitk):
+        h = _run_swiglu(ctx, x, gate_up)
+        assert backend.last_kernel_name().startswith("lux_qgemm_i4_tc_wa")
+    code = orc.dtype_code(x)
+    gu = orc.qmatmul(x, *gate_up.triple, bits=4, group=128, y_code=orc.F32, w_round=code)
+    assert orc.rel_l2(h, orc.swiglu(gu, h_code=code)) < TOL_16
+    assert ctx.last_device_status() == 0
+
+
+def test_wa_mlp_m256(ctx, backend):
+    """The FFN at 256 batch rows: both of its GEMMs take this kernel by default."""
+    gate_up, down = synth.mlp_layers(512, 768, 256, 45, "wamlp")
+    x = synth.activations(256, 512, "f16", 45, "wamlp.x")
+    G, D = ctx.upload_layer(gate_up), ctx.upload_layer(down)
+    xb = ctx.upload(x)
+    hb, yb = ctx.alloc(256 * 768 * 2), ctx.alloc(256 * 256 * 2)
+    ctx.qmlp(xb, G, D, hb, yb, 256, B.F16)
+    assert backend.last_kernel_name() == "lux_qgemm_i4_tc_wa_f16"
+    y = yb.to_host(np.float16, (256, 256))
+    assert orc.rel_l2(y, orc.mlp(x, gate_up.triple, down.triple, fused=True, w_round=orc.F16)) < TOL_16
+    assert ctx.last_device_status() == 0
+

@@ -35,6 +35,7 @@
 #include "tc_ptx.cuh"
 
 #include <algorithm>
+#include <type_traits>
 
 namespace luxcuda {
 
@@ -77,9 +78,10 @@ struct WaParams {
     const uint8_t* zeros;     // [N, ZS] or null
     void* y;                  // [M, N]
     uint32_t* status;
-    int M, N, K, G, ZS;
+    int M, Nout, K, G, ZS;    // Nout = outputs = row pitch of y (half the weight rows with SwiGLU)
     int stages;               // ring depth in units of 128 K (x in shared memory, A in TMEM)
     int groups;               // converter groups of four warps, <= stages
+    int up_row_offset;        // SwiGLU: weight row of `up` = weight row of `gate` + this (= number of outputs)
     int ncols;                // batch rows per tile = UMMA N: 256, or the batch rounded up to 16 when it is smaller
 };
 
@@ -100,7 +102,7 @@ __device__ __forceinline__ void group_consts(__half sh, uint32_t zp, uint32_t& z
     }
 }
 
-template <bool BF16, int KS>
+template <bool BF16, int KS, bool SW>
 __global__ void __launch_bounds__(WA_MAX_THREADS, 1)
 lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) {
     extern __shared__ unsigned char smem_raw[];
@@ -117,7 +119,8 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
     pdl_launch_dependents();
     if (KS == 2) cluster_arrive();                  // matched by cluster_wait() before the first remote store
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n0 = blockIdx.x * BM;                 // first weight row of the tile
+    constexpr int OUT_W = SW ? BM / 2 : BM;         // outputs per tile: with SwiGLU lanes 0..63 hold gate rows, 64..127 up rows
+    const int n0 = blockIdx.x * OUT_W;              // first output (= first gate / weight row) of the tile
     const int m0 = blockIdx.y * WA_BN;              // first batch row of the tile
     const int ksplit = KS == 1 ? 0 : (int)blockIdx.z;
     const int k_len = p.K / KS;
@@ -158,7 +161,8 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
         if (zrow) nzb = (uint32_t)__ldg(zrow + ((g_base + u) >> 1));
     };
     if (warp >= 2) {
-        const int wrow = n0 + quad * 32 + lane;         // this thread's weight row
+        const int r = quad * 32 + lane;                 // this thread's TMEM lane and its weight row
+        const int wrow = SW ? (r < OUT_W ? n0 + r : p.up_row_offset + n0 + r - OUT_W) : n0 + r;
         wp = p.w + (size_t)wrow * (p.K / 2) + (k_base >> 1);
         sp = p.scales + (size_t)wrow * p.G + g_base;
         zrow = p.zeros ? p.zeros + (size_t)wrow * p.ZS : nullptr;
@@ -337,13 +341,21 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
                 acc[4 * i + 3] = __float_as_uint(__uint_as_float(acc[4 * i + 3]) + r.w);
             }
         }
+        if constexpr (SW) {
+            // gate and up of one output sit on different lanes (r and r + 64): the sums go to
+            // shared memory as f32, [column][128 rows], and are combined in the write-out pass
+            float* fcol = reinterpret_cast<float*>(stage) + my_row;
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-            const float mine = __uint_as_float(odd ? acc[i + 1] : acc[i]);
-            const float give = __uint_as_float(odd ? acc[i] : acc[i + 1]);
-            const float got = __shfl_xor_sync(0xffffffffu, give, 1);
-            const uint32_t v = odd ? pack2<BF16>(got, mine) : pack2<BF16>(mine, got);
-            *reinterpret_cast<uint32_t*>(srow + (c0 + i + (odd ? 1 : 0)) * WA_STAGE_PITCH) = v;
+            for (int i = 0; i < 32; i++) fcol[(c0 + i) * BM] = __uint_as_float(acc[i]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                const float mine = __uint_as_float(odd ? acc[i + 1] : acc[i]);
+                const float give = __uint_as_float(odd ? acc[i] : acc[i + 1]);
+                const float got = __shfl_xor_sync(0xffffffffu, give, 1);
+                const uint32_t v = odd ? pack2<BF16>(got, mine) : pack2<BF16>(mine, got);
+                *reinterpret_cast<uint32_t*>(srow + (c0 + i + (odd ? 1 : 0)) * WA_STAGE_PITCH) = v;
+            }
         }
     };
 
@@ -372,7 +384,26 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
         // the eight epilogue warps (and only they) meet here on every path
         asm volatile("bar.sync 1, 256;" ::: "memory");
         TRACE(46);
-        if (ok) {
+        if (ok && SW) {
+            // one batch row of the tile = 64 outputs = 128 contiguous bytes of y: 8 lanes x 16 bytes,
+            // each lane combining eight (gate, up) pairs: silu(gate) * up, narrowed once
+            // (steel_gemm_fused.wgsl:91-94, 452-558)
+            const int sub = lane >> 3, l8 = lane & 7;
+#pragma unroll 2
+            for (int c = (warp - 2) * 4 + sub; c < KEEP; c += 32) {
+                const int m = m0 + keep0 + c;
+                if (m < p.M && keep0 + c < p.ncols) {
+                    const float4* gp = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(stage) + c * BM + l8 * 8);
+                    const float4 g0 = gp[0], g1 = gp[1], u0 = gp[OUT_W / 4], u1 = gp[OUT_W / 4 + 1];
+                    uint4 v;
+                    v.x = pack2<BF16>(silu_f32(g0.x) * u0.x, silu_f32(g0.y) * u0.y);
+                    v.y = pack2<BF16>(silu_f32(g0.z) * u0.z, silu_f32(g0.w) * u0.w);
+                    v.z = pack2<BF16>(silu_f32(g1.x) * u1.x, silu_f32(g1.y) * u1.y);
+                    v.w = pack2<BF16>(silu_f32(g1.z) * u1.z, silu_f32(g1.w) * u1.w);
+                    *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(p.y) + ((size_t)m * p.Nout + n0 + l8 * 8) * 2) = v;
+                }
+            }
+        } else if (ok) {
             // one batch row of the tile = 128 weight rows = 256 contiguous bytes of y: 16 lanes x 16 bytes
             const int sub = lane >> 4, l16 = lane & 15;
 #pragma unroll 4
@@ -380,7 +411,7 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
                 const int m = m0 + keep0 + c;
                 if (m < p.M) {
                     const uint4 v = *reinterpret_cast<const uint4*>(stage + c * WA_STAGE_PITCH + l16 * 16);
-                    *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(p.y) + ((size_t)m * p.N + n0 + l16 * 8) * 2) = v;
+                    *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(p.y) + ((size_t)m * p.Nout + n0 + l16 * 8) * 2) = v;
                 }
             }
         }
@@ -400,9 +431,9 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
     }
 }
 
-template <bool BF16, int KS>
+template <bool BF16, int KS, bool SW>
 cudaError_t launch_wa(const CUtensorMap& mx, const WaParams& p, dim3 grid, int threads, size_t smem, cudaStream_t st) {
-    auto kfn = lux_qgemm_i4_tc_wa<BF16, KS>;
+    auto kfn = lux_qgemm_i4_tc_wa<BF16, KS, SW>;
     static std::atomic<size_t> configured[64];
     int dev = 0;
     cudaGetDevice(&dev);
@@ -416,17 +447,19 @@ cudaError_t launch_wa(const CUtensorMap& mx, const WaParams& p, dim3 grid, int t
 
 }  // namespace
 
-// Takes plain (no SwiGLU, no push) int4 GEMMs whose weight rows come in whole tiles of 128;
-// everything else stays with lux_qgemm_i4_tc.
+// Takes int4 GEMMs without a push epilogue whose outputs come in whole tiles (128 weight rows;
+// with SwiGLU 64 outputs = 64 gate + 64 up rows); everything else stays with lux_qgemm_i4_tc.
 LuxBackendError launch_qgemm_i4_tc_wa(Context* ctx, const QArgs& a) {
-    if (a.swiglu || a.push || a.N % BM || a.K % 128 || a.M < 1) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+    const int nout = a.swiglu ? a.N / 2 : a.N;
+    const int out_w = a.swiglu ? BM / 2 : BM;                   // outputs per tile
+    if (a.push || nout % out_w || a.K % 128 || a.M < 1) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
     if (a.scale_dtype != LUX_QDTYPE_F16 || a.x_dtype != a.y_dtype) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
     if (a.x_dtype != LUX_QDTYPE_BF16 && a.x_dtype != LUX_QDTYPE_F16) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
     if ((reinterpret_cast<uintptr_t>(a.w) & 15u) || (a.K / 2) % 16) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
     const bool bf16 = a.x_dtype == LUX_QDTYPE_BF16;
 
     // Split K over a pair of CTAs when whole tiles alone would leave most SMs idle.
-    const int tiles = (a.N / BM) * ((a.M + WA_BN - 1) / WA_BN);
+    const int tiles = (nout / out_w) * ((a.M + WA_BN - 1) / WA_BN);
     int ks = (tiles * 2 <= ctx->sm_count && a.K % 256 == 0) ? 2 : 1;
     if (g_tune.gemm_tc_splitk == 1 || (g_tune.gemm_tc_splitk == 2 && a.K % 256 == 0)) ks = g_tune.gemm_tc_splitk;
     const int stages = g_tune.gemm_tc_stages >= 2 && g_tune.gemm_tc_stages <= WA_MAX_UNITS ? g_tune.gemm_tc_stages : WA_MAX_UNITS;
@@ -447,18 +480,23 @@ LuxBackendError launch_qgemm_i4_tc_wa(Context* ctx, const QArgs& a) {
     p.zeros = a.zeros;
     p.y = a.y;
     p.status = ctx->d_status;
-    p.M = a.M; p.N = a.N; p.K = a.K; p.G = a.G; p.ZS = (a.G + 1) / 2;
+    p.M = a.M; p.Nout = nout; p.K = a.K; p.G = a.G; p.ZS = (a.G + 1) / 2;
+    p.up_row_offset = a.swiglu ? nout : 0;
     p.stages = stages;
     p.groups = groups;
     p.ncols = ncols;
 
-    dim3 grid(a.N / BM, (a.M + WA_BN - 1) / WA_BN, ks);
+    dim3 grid(nout / out_w, (a.M + WA_BN - 1) / WA_BN, ks);
     const int threads = (2 + 4 * groups) * 32;                  // groups >= 2: the epilogue needs warps 2..9
+    auto go = [&](auto bf_tag, auto sw_tag) {
+        constexpr bool BF_ = decltype(bf_tag)::value;
+        constexpr bool SW_ = decltype(sw_tag)::value;
+        return ks == 2 ? launch_wa<BF_, 2, SW_>(mx, p, grid, threads, smem, ctx->stream)
+                       : launch_wa<BF_, 1, SW_>(mx, p, grid, threads, smem, ctx->stream);
+    };
     cudaError_t e;
-    if (ks == 2) e = bf16 ? launch_wa<true, 2>(mx, p, grid, threads, smem, ctx->stream)
-                          : launch_wa<false, 2>(mx, p, grid, threads, smem, ctx->stream);
-    else         e = bf16 ? launch_wa<true, 1>(mx, p, grid, threads, smem, ctx->stream)
-                          : launch_wa<false, 1>(mx, p, grid, threads, smem, ctx->stream);
+    if (a.swiglu) e = bf16 ? go(std::true_type{}, std::true_type{}) : go(std::false_type{}, std::true_type{});
+    else          e = bf16 ? go(std::true_type{}, std::false_type{}) : go(std::false_type{}, std::false_type{});
     count_launch(bf16 ? "lux_qgemm_i4_tc_wa_bf16" : "lux_qgemm_i4_tc_wa_f16");
     return map_cuda(e, "lux_qgemm_i4_tc_wa");
 }
@@ -469,6 +507,6 @@ extern "C" __attribute__((visibility("default"))) int lux_cuda_debug_wa_trace(un
 }
 #endif
 
-const void* kernel_addr_qgemm_i4_tc_wa_bf16() { return (const void*)lux_qgemm_i4_tc_wa<true, 2>; }
+const void* kernel_addr_qgemm_i4_tc_wa_bf16() { return (const void*)lux_qgemm_i4_tc_wa<true, 2, false>; }
 
 }  // namespace luxcuda
