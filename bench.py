@@ -481,6 +481,16 @@ def bench_tp(args, peaks):
                     "d2h_bytes_per_step": int(M * d["H"] * 2), "us_per_step": e2e_sec * 1e6, "path": e2e_path},
             "gpu_launches": (3 if peer is not None else 2) * args.steps, "clocks": clocks, "parity_rel_l2": parity,
         }
+    if line is not None and M >= 12:
+        # From 12 batch rows on both FFN kernels run on the tensor cores: the roofline that bounds
+        # them is the dense 16-bit tensor peak, not HBM (the weights are read once either way).
+        flops = 2.0 * M * (2 * (d["I"] // world) * d["K"] + d["H"] * (d["I"] // world))
+        tf = flops / sec_compute / 1e12
+        line["roofline"] = {"bound": "tensor", "achieved": tf, "peak": peaks["bf16"], "unit": "TFLOP/s",
+                            "frac": tf / peaks["bf16"], "frac_of_sustained": tf / peaks["bf16_sustained"], "traffic": None,
+                            "peak_source": peaks["source"], "note": "per GPU, both FFN kernels, without the all-reduce",
+                            "us_compute_only": sec_compute * 1e6, "us_with_allreduce": sec * 1e6,
+                            "weights_gbs": per_gpu_alg / sec_compute / 1e9}
     ctx.sync()                       # raises if a bounded device-side wait gave up during the run
     if peer is not None:
         peer.close()

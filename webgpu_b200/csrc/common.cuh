@@ -101,6 +101,7 @@ struct Tunables {
     int gemm_tc_splitk = 0;      // weights-in-TMEM GEMM: K splits over a CTA pair, 1 or 2 (0 = choose)
     int gemm_tc_groups = 0;      // weights-in-TMEM GEMM: converter groups of four warps, 2..4
     int pdl = 0;                 // programmatic dependent launch of the persistent kernels: 0/1 on, 2 off
+    int gemm_min_m = 0;          // smallest batch the weights-in-TMEM GEMM takes from the streaming kernels (0 = built-in)
     int gemm_tc_kernel = 0;      // 0 auto, 1 lux_qgemm_i4_tc, 2 lux_qgemm_i4_tc_wa wherever it applies
     int gemm_tc_ma = 0;          // GEMM: batch tiles (128 rows) per CTA, 1 or 2 (0 = choose)
 };

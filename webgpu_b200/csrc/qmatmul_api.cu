@@ -96,6 +96,15 @@ LuxBackendError dispatch(Context* ctx, const Checked& c) {
                 LuxBackendError e = launch_qgemv_i4_units(ctx, a);
                 if (e != LUX_BACKEND_ERROR_NOT_SUPPORTED || g_tune.gemv_i4_kernel == 3) return e;
             }
+            // From a handful of batch rows on, the tensor-core kernel with the weights in tensor
+            // memory streams the weights faster than the mma.sync kernels below, whose unpacking
+            // grows with the batch: config 4 gate_up / o at batch 12: 41 / 12.7 us against 47 / 13.4 us, at batch
+            // 32: 41 / 12.8 us against 138 / 37 us; below 12 the streaming kernels win.
+            const int min_m = g_tune.gemm_min_m > 0 ? g_tune.gemm_min_m : 12;
+            if (a.M >= min_m && g_tune.gemv_i4_kernel == 0 && g_tune.gemm_tc_kernel != 1 && !a.push) {
+                LuxBackendError e = launch_qgemm_i4_tc_wa(ctx, a);
+                if (e != LUX_BACKEND_ERROR_NOT_SUPPORTED) return e;
+            }
             const size_t wbytes = (size_t)a.N * a.K / 2;
             const bool prefer_ring = a.M >= 4 || a.K >= 8192 || wbytes >= ((size_t)40 << 20);
             if (g_tune.gemv_i4_kernel == 2 || (g_tune.gemv_i4_kernel == 0 && prefer_ring)) {
@@ -344,7 +353,7 @@ LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_tune_set(const char* key, int val
         {"gemv_i4_kernel", &g_tune.gemv_i4_kernel}, {"gemv_stream_cg", &g_tune.gemv_stream_cg},
         {"gemv_stream_stages", &g_tune.gemv_stream_stages}, {"gemv_stream_warps", &g_tune.gemv_stream_warps},
         {"gemv_units_ks", &g_tune.gemv_units_ks}, {"gemv_units_stages", &g_tune.gemv_units_stages}, {"gemv_units_cg", &g_tune.gemv_units_cg}, {"gemv_units_pre", &g_tune.gemv_units_pre}, {"gemv_units_fx", &g_tune.gemv_units_fx},
-        {"gemm_tc_stages", &g_tune.gemm_tc_stages}, {"gemm_tc_splitk", &g_tune.gemm_tc_splitk}, {"gemm_tc_ma", &g_tune.gemm_tc_ma}, {"gemm_tc_groups", &g_tune.gemm_tc_groups}, {"gemm_tc_kernel", &g_tune.gemm_tc_kernel}, {"pdl", &g_tune.pdl},
+        {"gemm_tc_stages", &g_tune.gemm_tc_stages}, {"gemm_tc_splitk", &g_tune.gemm_tc_splitk}, {"gemm_tc_ma", &g_tune.gemm_tc_ma}, {"gemm_tc_groups", &g_tune.gemm_tc_groups}, {"gemm_tc_kernel", &g_tune.gemm_tc_kernel}, {"gemm_min_m", &g_tune.gemm_min_m}, {"pdl", &g_tune.pdl},
     };
     for (auto& t : table)
         if (std::strcmp(t.k, key) == 0) { *t.v = value; return LUX_BACKEND_OK; }
