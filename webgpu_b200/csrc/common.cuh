@@ -43,6 +43,8 @@ struct Context {
     void*          d_stage = nullptr;       // device staging for host-pointer ops
     size_t         d_stage_bytes = 0;
     uint32_t       last_status = 0;
+    void*          d_splitk = nullptr;      // split-K exchange of the weights-in-TMEM GEMM: 128 KB per CTA pair,
+    size_t         d_splitk_bytes = 0;      // allocated with the context (no entry point allocates for it)
     std::mutex     mu;                      // guards the staging buffers
     int            sm_count = 148;
 };

@@ -102,8 +102,15 @@ static LuxBackendContext* cuda_create_context(int device_index) {
     // stream wait without another copy.
     ok = ok && cudaHostAlloc(&ctx->h_status, sizeof(uint32_t), cudaHostAllocMapped) == cudaSuccess;
     ok = ok && cudaHostGetDevicePointer((void**)&ctx->d_status, ctx->h_status, 0) == cudaSuccess;
+    // Split-K partial sums of the tensor-core GEMM: one 128 KB slot per CTA pair, at most one pair
+    // per two SMs.  Allocated here so that no matmul entry point ever allocates device memory.
+    if (ok) {
+        ctx->d_splitk_bytes = (size_t)(ctx->prop.multiProcessorCount / 2) * (128u << 10);
+        ok = cudaMalloc(&ctx->d_splitk, ctx->d_splitk_bytes) == cudaSuccess;
+    }
     if (!ok) {
         cudaGetLastError();
+        if (ctx->d_splitk) cudaFree(ctx->d_splitk);
         if (ctx->h_status) cudaFreeHost(ctx->h_status);
         if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
         delete ctx;
@@ -123,6 +130,7 @@ static void cuda_destroy_context(LuxBackendContext* context) {
     cudaStreamSynchronize(ctx->stream);
     if (ctx->h_stage) cudaFreeHost(ctx->h_stage);
     if (ctx->d_stage) cudaFree(ctx->d_stage);
+    if (ctx->d_splitk) cudaFree(ctx->d_splitk);
     if (ctx->h_status) cudaFreeHost(ctx->h_status);
     if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
     cudaGetLastError();

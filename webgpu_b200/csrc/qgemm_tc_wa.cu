@@ -27,9 +27,10 @@
 //   warps 2..9    epilogue.
 //
 // Split-K: with KS = 2 the two CTAs of a cluster take the two halves of K for the same tile;
-// each then sends the accumulator columns the other one finishes through distributed shared
-// memory (st.shared::cluster into the peer's idle x ring), adds what it received to its own half
-// and writes it.  No multicast anywhere.  Every mbarrier wait is bounded; the cluster barriers are
+// each then leaves the accumulator columns the other one finishes in the pair's slot of a
+// context-owned exchange buffer in global memory (L2-resident; no entry point allocates), one
+// cluster barrier publishes both halves, and each adds what it found to its own half and writes
+// it.  No multicast anywhere.  Every mbarrier wait is bounded; the cluster barriers are
 // hardware barriers that every thread reaches on every path.
 #include "common.cuh"
 #include "tc_ptx.cuh"
@@ -53,7 +54,7 @@ constexpr int WA_MAX_UNITS = 3;            // ring depth: 3 x 64 KB of x in shar
 constexpr int WA_MAX_GROUPS = 3;           // converter groups <= ring depth
 constexpr int WA_MAX_THREADS = (2 + 4 * WA_MAX_GROUPS) * 32;
 constexpr uint32_t WA_TMEM_COLS = 512;     // accumulator [0, 256) + A units [256, 448)
-constexpr int WA_RECV_BYTES = 64 * BM * 4;  // one round of the split-K exchange: 2 column halves x 32 columns x 128 rows x f32
+constexpr int WA_HALF_SLOT = 128 * BM * 4;  // split-K exchange: the 128 columns x 128 rows x f32 one CTA leaves for its peer
 constexpr int WA_STAGE_PITCH = 320;        // bytes per batch row of the staged output tile: 256 + 64, so that the
                                            // even and the odd lanes of a staging store use different banks
 
@@ -78,6 +79,7 @@ struct WaParams {
     const uint8_t* zeros;     // [N, ZS] or null
     void* y;                  // [M, N]
     uint32_t* status;
+    unsigned char* splitk;    // KS == 2: one 128 KB slot per CTA pair for the exchange of partial sums
     int M, Nout, K, G, ZS;    // Nout = outputs = row pitch of y (half the weight rows with SwiGLU)
     int stages;               // ring depth in units of 128 K (x in shared memory, A in TMEM)
     int groups;               // converter groups of four warps, <= stages
@@ -109,7 +111,7 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const int P = p.stages;                          // ring depth in units of 128 K
     unsigned char* x_ring = smem;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(x_ring + (size_t)P * WA_UNIT_X_BYTES + (KS == 2 ? WA_RECV_BYTES : 0));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(x_ring + (size_t)P * WA_UNIT_X_BYTES);
     // bars[0..P) full, [P..2P) empty, [2P] acc_full
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * P + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
@@ -117,7 +119,6 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
     TRACE_DECL;
     TRACE(1);
     pdl_launch_dependents();
-    if (KS == 2) cluster_arrive();                  // matched by cluster_wait() before the first remote store
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     constexpr int OUT_W = SW ? BM / 2 : BM;         // outputs per tile: with SwiGLU lanes 0..63 hold gate rows, 64..127 up rows
     const int n0 = blockIdx.x * OUT_W;              // first output (= first gate / weight row) of the tile
@@ -291,11 +292,11 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
 
     // =============================== epilogue ===========================================
     // Warps 2..9: quarter `quad` of the lanes (weight rows), half `eh` of the columns handled,
-    // in chunks of 32 columns.  KS == 2: the peer's partial sums arrive in two rounds of 32 KB,
-    // the first into a buffer of its own behind the ring (it can be sent before anything is
-    // known about the peer's progress), the second into the peer's ring once the first cluster
-    // barrier has shown it idle; the narrowed output tile is then staged in the ring for
-    // row-wise 16-byte stores.
+    // in chunks of 32 columns.  KS == 2: each CTA writes the 128 columns the peer finishes to the
+    // pair's slot in global memory (it stays in L2), one cluster barrier publishes both halves, and
+    // each adds what the peer left for it.  (Through distributed shared memory the same 64 KB took
+    // 2 us per CTA, by remote stores and by bulk copies alike; the barrier's release waits for them.)
+    // The narrowed output tile is staged in the idle ring for row-wise 16-byte stores.
     const int eh = (warp - 2) >> 2;
     const bool ep_warp = warp >= 2 && warp < 10;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
@@ -303,30 +304,34 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
     const int keep0 = KS == 1 ? 0 : ksplit * (WA_BN / 2);       // first accumulator column this CTA writes
     constexpr int KEEP = WA_BN / KS;                            // columns this CTA writes
     constexpr int PER_WARP = KEEP / 2;                          // per epilogue warp
-    // received partial sums of a round: 16 bytes (4 columns) per weight row, rows consecutive, so
-    // that a warp's remote store is one contiguous 512-byte piece; [16 column quads][128 rows]
-    unsigned char* recv1 = x_ring + (size_t)P * WA_UNIT_X_BYTES;             // round 1 (KS == 2 only)
-    unsigned char* recv2 = x_ring;                                           // round 2
-    unsigned char* stage = x_ring + (KS == 2 ? WA_RECV_BYTES : 0);           // [column][WA_STAGE_PITCH bytes]
+    // a half slot: 16 bytes (4 columns) per weight row, rows consecutive, [32 column quads][128 rows]:
+    // a warp's store or load is one contiguous 512-byte piece
+    unsigned char* slot = KS == 2 ? p.splitk + (size_t)(blockIdx.x + gridDim.x * blockIdx.y) * (2 * WA_HALF_SLOT) : nullptr;
+    unsigned char* stage = x_ring;                                           // [column][WA_STAGE_PITCH bytes]
     const bool odd = lane & 1;
     // lanes pair up: the even lane stages (row, row + 1) of the even columns, the odd lane of the odd ones
     unsigned char* srow = stage + (quad * 32 + (lane & ~1)) * 2;
 
-    // 32 accumulator columns of the peer's half -> the peer's receive buffer `dst` (a
-    // shared::cluster address of the buffer's start), column quad q0 onwards
+    // 32 accumulator columns of the peer's half -> the peer's half slot `dst`, column quad q0 onwards
     // (chunks that lie entirely beyond the batch's columns are skipped, by sender and receiver alike)
-    auto send_chunk = [&](int col, uint32_t dst, int q0) {
+    auto send_chunk = [&](int col, unsigned char* dst, int q0) {
         if (col >= p.ncols) return;
         uint32_t acc[32];
         tmem_ld32(lane_addr + (uint32_t)col, acc);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; i += 4)
-            st_cluster_v4(dst + (uint32_t)(((q0 + (i >> 2)) * BM + my_row) * 16), acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+            __stcg(reinterpret_cast<uint4*>(dst + ((q0 + (i >> 2)) * BM + my_row) * 16), make_uint4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]));
     };
     // 32 columns c0.. of this CTA's own half: add what the peer sent (column quad q0 onwards of
     // `rsrc`), narrow once, stage
-    auto finalize_chunk = [&](int c0, const unsigned char* rsrc, int q0) {
+    // what the peer left for 32 of this CTA's columns (requested for both chunks before either is used)
+    auto load_peer = [&](float4 (&r)[8], int c0, const unsigned char* rsrc, int q0) {
+        if (keep0 + c0 >= p.ncols) return;
+#pragma unroll
+        for (int i = 0; i < 8; i++) r[i] = __ldcg(reinterpret_cast<const float4*>(rsrc + ((q0 + i) * BM + my_row) * 16));
+    };
+    auto finalize_chunk = [&](int c0, const float4 (&peer)[8]) {
         if (keep0 + c0 >= p.ncols) return;
         uint32_t acc[32];
         tmem_ld32(lane_addr + (uint32_t)(keep0 + c0), acc);
@@ -334,7 +339,7 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
         if (KS == 2) {
 #pragma unroll
             for (int i = 0; i < 8; i++) {
-                const float4 r = *reinterpret_cast<const float4*>(rsrc + ((q0 + i) * BM + my_row) * 16);
+                const float4 r = peer[i];
                 acc[4 * i + 0] = __float_as_uint(__uint_as_float(acc[4 * i + 0]) + r.x);
                 acc[4 * i + 1] = __float_as_uint(__uint_as_float(acc[4 * i + 1]) + r.y);
                 acc[4 * i + 2] = __float_as_uint(__uint_as_float(acc[4 * i + 2]) + r.z);
@@ -361,23 +366,28 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
 
     if (KS == 2) {
         const int send0 = (1 - ksplit) * (WA_BN / 2);
-        const uint32_t peer1 = map_to_cta(smem_u32(recv1), (uint32_t)(1 - ksplit));
-        const uint32_t peer2 = map_to_cta(smem_u32(recv2), (uint32_t)(1 - ksplit));
-        cluster_wait();              // completes the arrival made at kernel start: the peer CTA runs
-        if (ep_warp && ok) send_chunk(send0 + eh * PER_WARP, peer1, eh * 8);
-        TRACE(41);
-        cluster_sync_all();          // both CTAs are done with their rings; round 1 has arrived
-        TRACE(42);
+        unsigned char* theirs = slot + (size_t)(1 - ksplit) * WA_HALF_SLOT;
+        const unsigned char* mine = slot + (size_t)ksplit * WA_HALF_SLOT;
         if (ep_warp && ok) {
-            send_chunk(send0 + eh * PER_WARP + 32, peer2, eh * 8);
-            finalize_chunk(eh * PER_WARP, recv1, eh * 8);
+            send_chunk(send0 + eh * PER_WARP, theirs, eh * 16);
+            send_chunk(send0 + eh * PER_WARP + 32, theirs, eh * 16 + 8);
         }
-        cluster_sync_all();          // round 2 has arrived
+        TRACE(41);
+        cluster_sync_all();          // release / acquire at cluster scope: both halves are published
         TRACE(43);
-        if (ep_warp && ok) finalize_chunk(eh * PER_WARP + 32, recv2, eh * 8);
+        if (ep_warp && ok) {
+            float4 ra[8], rb[8];
+            load_peer(ra, eh * PER_WARP, mine, eh * 16);
+            load_peer(rb, eh * PER_WARP + 32, mine, eh * 16 + 8);
+            finalize_chunk(eh * PER_WARP, ra);
+            finalize_chunk(eh * PER_WARP + 32, rb);
+        }
     } else if (ep_warp && ok) {
 #pragma unroll 1
-        for (int c0 = eh * PER_WARP; c0 < (eh + 1) * PER_WARP; c0 += 32) finalize_chunk(c0, nullptr, 0);
+        for (int c0 = eh * PER_WARP; c0 < (eh + 1) * PER_WARP; c0 += 32) {
+            const float4 none[8] = {};
+            finalize_chunk(c0, none);
+        }
     }
     if (ep_warp) {
         if (ok) tc_fence_before();
@@ -460,12 +470,13 @@ LuxBackendError launch_qgemm_i4_tc_wa(Context* ctx, const QArgs& a) {
 
     // Split K over a pair of CTAs when whole tiles alone would leave most SMs idle.
     const int tiles = (nout / out_w) * ((a.M + WA_BN - 1) / WA_BN);
-    int ks = (tiles * 2 <= ctx->sm_count && a.K % 256 == 0) ? 2 : 1;
-    if (g_tune.gemm_tc_splitk == 1 || (g_tune.gemm_tc_splitk == 2 && a.K % 256 == 0)) ks = g_tune.gemm_tc_splitk;
+    const bool can_split = a.K % 256 == 0 && (size_t)tiles * (2 * WA_HALF_SLOT) <= ctx->d_splitk_bytes;
+    int ks = (tiles * 2 <= ctx->sm_count && can_split) ? 2 : 1;
+    if (g_tune.gemm_tc_splitk == 1 || (g_tune.gemm_tc_splitk == 2 && can_split)) ks = g_tune.gemm_tc_splitk;
     const int stages = g_tune.gemm_tc_stages >= 2 && g_tune.gemm_tc_stages <= WA_MAX_UNITS ? g_tune.gemm_tc_stages : WA_MAX_UNITS;
     int groups = g_tune.gemm_tc_groups >= 2 && g_tune.gemm_tc_groups <= WA_MAX_GROUPS ? g_tune.gemm_tc_groups : 2;
     groups = std::min(groups, stages);
-    const size_t smem = 1024 + (size_t)stages * WA_UNIT_X_BYTES + (ks == 2 ? WA_RECV_BYTES : 0) + 512;
+    const size_t smem = 1024 + (size_t)stages * WA_UNIT_X_BYTES + 512;
 
     CUtensorMap mx;
     const uint64_t dims[2] = {(uint64_t)a.K * 2, (uint64_t)a.M};
@@ -480,6 +491,7 @@ LuxBackendError launch_qgemm_i4_tc_wa(Context* ctx, const QArgs& a) {
     p.zeros = a.zeros;
     p.y = a.y;
     p.status = ctx->d_status;
+    p.splitk = (unsigned char*)ctx->d_splitk;
     p.M = a.M; p.Nout = nout; p.K = a.K; p.G = a.G; p.ZS = (a.G + 1) / 2;
     p.up_row_offset = a.swiglu ? nout : 0;
     p.stages = stages;
