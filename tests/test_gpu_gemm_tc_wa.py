@@ -139,3 +139,33 @@ def test_wa_mlp_m256(ctx, backend):
     assert orc.rel_l2(y, orc.mlp(x, gate_up.triple, down.triple, fused=True, w_round=orc.F16)) < TOL_16
     assert ctx.last_device_status() == 0
 
+
+@pytest.mark.parametrize("M,expect", [(8, "lux_qgemv_i4_g128_stream"), (12, "lux_qgemm_i4_tc_wa_f16"), (32, "lux_qgemm_i4_tc_wa_f16")])
+def test_small_batches_cross_over_at_12(ctx, backend, M, expect):
+    """Below 12 batch rows the streaming kernels keep the shape, from 12 up the tensor-core
+    kernel takes it (config 4's `o` layer); both agree with the oracle."""
+    x, layer = synth.config4("o", M)
+    y = _run(ctx, x, layer)
+    assert backend.last_kernel_name() == expect
+    rows = np.arange(0, M, max(1, M // 4))
+    assert orc.rel_l2(y[rows], orc.qmatmul(x[rows], *layer.triple, bits=4, group=128)) < TOL_16
+    assert ctx.last_device_status() == 0
+
+
+def test_programmatic_dependent_launch_is_transparent(ctx, backend):
+    """The same bits with and without the programmatic stream serialization attribute, for a chain
+    of dependent launches (each FFN's down projection reads what its gate_up wrote)."""
+    gate_up, down = synth.mlp_layers(512, 768, 256, 46, "pdl")
+    x = synth.activations(256, 512, "f16", 46, "pdl.x")
+    G, D = ctx.upload_layer(gate_up), ctx.upload_layer(down)
+    xb = ctx.upload(x)
+    hb, yb = ctx.alloc(256 * 768 * 2), ctx.alloc(256 * 256 * 2)
+    outs = []
+    for pdl in (0, 2):
+        with _Tuned(backend, pdl=pdl):
+            for _ in range(3):
+                ctx.qmlp(xb, G, D, hb, yb, 256, B.F16)
+        outs.append(yb.to_host(np.float16, (256, 256)).copy())
+    assert np.array_equal(outs[0].view(np.uint16), outs[1].view(np.uint16))
+    assert ctx.last_device_status() == 0
+
