@@ -44,11 +44,12 @@ class _Tuned:
 
 
 @pytest.mark.parametrize("dtype", ["bf16", "f16"])
-@pytest.mark.parametrize("splitk", [1, 2])
+@pytest.mark.parametrize("splitk", [1, 2, 4])
 @pytest.mark.parametrize("M,N,K", [(256, 128, 256), (129, 128, 512), (300, 256, 512), (512, 384, 1024), (40, 128, 256),
                                    (33, 256, 512), (64, 128, 1024), (100, 256, 256), (128, 128, 512), (200, 128, 256)])
 def test_wa_shapes(ctx, backend, dtype, splitk, M, N, K):
-    """Whole and ragged batch tiles, one and several weight tiles, both K splits; the kernel is
+    """Whole and ragged batch tiles, one and several weight tiles, one, two and four K splits (a split K does not divide falls back to
+    the built-in choice); the kernel is
     forced (gemm_tc_kernel = 2) so that batches of 128 rows and fewer run it too."""
     x = synth.activations(M, K, dtype, 41, f"wa.{M}.{K}")
     layer = synth.int4_layer(N, K, 41, f"wa.{N}.{K}")
@@ -109,7 +110,7 @@ def _run_swiglu(ctx, x, gate_up):
 
 
 @pytest.mark.parametrize("dtype", ["f16", "bf16"])
-@pytest.mark.parametrize("splitk", [1, 2])
+@pytest.mark.parametrize("splitk", [1, 2, 4])
 @pytest.mark.parametrize("M,K,I", [(256, 512, 128), (96, 256, 64), (300, 512, 192), (33, 1024, 64)])
 def test_wa_swiglu_epilogue(ctx, backend, dtype, splitk, M, K, I):
     """gate_up with the SwiGLU epilogue (steel_gemm_fused.wgsl:91-94, 452-558): gate rows on TMEM

@@ -100,7 +100,7 @@ struct Tunables {
     int gemv_units_fx = 0;       // units kernel, batch <= 2: 0/1 block-fixed-point int8 variant, 2 f16 variant
     int gemm_tc_bn = 0;          // N tile of the tcgen05 GEMM
     int gemm_tc_stages = 0;
-    int gemm_tc_splitk = 0;      // weights-in-TMEM GEMM: K splits over a CTA pair, 1 or 2 (0 = choose)
+    int gemm_tc_splitk = 0;      // weights-in-TMEM GEMM: K splits over a CTA cluster, 1, 2 or 4 (0 = choose)
     int gemm_tc_groups = 0;      // weights-in-TMEM GEMM: converter groups of four warps, 2..4
     int pdl = 0;                 // programmatic dependent launch of the persistent kernels: 0/1 on, 2 off
     int gemm_min_m = 0;          // smallest batch the weights-in-TMEM GEMM takes from the streaming kernels (0 = built-in)

@@ -105,7 +105,9 @@ static LuxBackendContext* cuda_create_context(int device_index) {
     // Split-K partial sums of the tensor-core GEMM: one 128 KB slot per CTA pair, at most one pair
     // per two SMs.  Allocated here so that no matmul entry point ever allocates device memory.
     if (ok) {
-        ctx->d_splitk_bytes = (size_t)(ctx->prop.multiProcessorCount / 2) * (128u << 10);
+        // two K splits: 128 KB per pair, a pair per two SMs; four: 384 KB per quartet, one per four SMs
+        ctx->d_splitk_bytes = std::max((size_t)(ctx->prop.multiProcessorCount / 2) * (128u << 10),
+                                       (size_t)(ctx->prop.multiProcessorCount / 4) * (384u << 10));
         ok = cudaMalloc(&ctx->d_splitk, ctx->d_splitk_bytes) == cudaSuccess;
     }
     if (!ok) {

@@ -26,7 +26,7 @@
 //                 units g, g + NG, ... of the CTA's K range.
 //   warps 2..9    epilogue.
 //
-// Split-K: with KS = 2 the two CTAs of a cluster take the two halves of K for the same tile;
+// Split-K: with KS = 2 (or 4) the CTAs of a cluster take the halves (quarters) of K for the same tile;
 // each then leaves the accumulator columns the other one finishes in the pair's slot of a
 // context-owned exchange buffer in global memory (L2-resident; no entry point allocates), one
 // cluster barrier publishes both halves, and each adds what it found to its own half and writes
@@ -55,6 +55,7 @@ constexpr int WA_MAX_GROUPS = 3;           // converter groups <= ring depth
 constexpr int WA_MAX_THREADS = (2 + 4 * WA_MAX_GROUPS) * 32;
 constexpr uint32_t WA_TMEM_COLS = 512;     // accumulator [0, 256) + A units [256, 448)
 constexpr int WA_HALF_SLOT = 128 * BM * 4;  // split-K exchange: the 128 columns x 128 rows x f32 one CTA leaves for its peer
+constexpr int WA_QUARTER_SLOT = 64 * BM * 4;   // four K splits: 64 columns per block, twelve blocks per tile
 constexpr int WA_STAGE_PITCH = 320;        // bytes per batch row of the staged output tile: 256 + 64, so that the
                                            // even and the odd lanes of a staging store use different banks
 
@@ -301,12 +302,12 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
     const bool ep_warp = warp >= 2 && warp < 10;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
     const int my_row = quad * 32 + lane;
-    const int keep0 = KS == 1 ? 0 : ksplit * (WA_BN / 2);       // first accumulator column this CTA writes
     constexpr int KEEP = WA_BN / KS;                            // columns this CTA writes
+    const int keep0 = ksplit * KEEP;                            // the first of them
     constexpr int PER_WARP = KEEP / 2;                          // per epilogue warp
     // a half slot: 16 bytes (4 columns) per weight row, rows consecutive, [32 column quads][128 rows]:
     // a warp's store or load is one contiguous 512-byte piece
-    unsigned char* slot = KS == 2 ? p.splitk + (size_t)(blockIdx.x + gridDim.x * blockIdx.y) * (2 * WA_HALF_SLOT) : nullptr;
+    unsigned char* slot = KS == 2 ? p.splitk + (size_t)(blockIdx.x + gridDim.x * blockIdx.y) * (2 * WA_HALF_SLOT) : nullptr;   // KS == 4: see below
     unsigned char* stage = x_ring;                                           // [column][WA_STAGE_PITCH bytes]
     const bool odd = lane & 1;
     // lanes pair up: the even lane stages (row, row + 1) of the even columns, the odd lane of the odd ones
@@ -331,20 +332,30 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
 #pragma unroll
         for (int i = 0; i < 8; i++) r[i] = __ldcg(reinterpret_cast<const float4*>(rsrc + ((q0 + i) * BM + my_row) * 16));
     };
-    auto finalize_chunk = [&](int c0, const float4 (&peer)[8]) {
+    auto acc_add = [&](uint32_t (&acc)[32], const float4 (&r4)[8]) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const float4 r = r4[i];
+            acc[4 * i + 0] = __float_as_uint(__uint_as_float(acc[4 * i + 0]) + r.x);
+            acc[4 * i + 1] = __float_as_uint(__uint_as_float(acc[4 * i + 1]) + r.y);
+            acc[4 * i + 2] = __float_as_uint(__uint_as_float(acc[4 * i + 2]) + r.z);
+            acc[4 * i + 3] = __float_as_uint(__uint_as_float(acc[4 * i + 3]) + r.w);
+        }
+    };
+    // the accumulator columns keep0 + c0 .. + 32 of this thread's row, plus up to three peers' sums
+    auto finalize_chunk = [&](int c0, const float4 (&peer)[8], const unsigned char* more = nullptr, int q0 = 0) {
         if (keep0 + c0 >= p.ncols) return;
         uint32_t acc[32];
         tmem_ld32(lane_addr + (uint32_t)(keep0 + c0), acc);
         tmem_ld_wait();
-        if (KS == 2) {
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const float4 r = peer[i];
-                acc[4 * i + 0] = __float_as_uint(__uint_as_float(acc[4 * i + 0]) + r.x);
-                acc[4 * i + 1] = __float_as_uint(__uint_as_float(acc[4 * i + 1]) + r.y);
-                acc[4 * i + 2] = __float_as_uint(__uint_as_float(acc[4 * i + 2]) + r.z);
-                acc[4 * i + 3] = __float_as_uint(__uint_as_float(acc[4 * i + 3]) + r.w);
-            }
+        if (KS >= 2) acc_add(acc, peer);
+        if (KS == 4) {
+            // sources 1 and 2 of this CTA's slot row (source 0 came in `peer`)
+            float4 r1[8], r2[8];
+            load_peer(r1, c0, more, q0);
+            load_peer(r2, c0, more + WA_QUARTER_SLOT, q0);
+            acc_add(acc, r1);
+            acc_add(acc, r2);
         }
         if constexpr (SW) {
             // gate and up of one output sit on different lanes (r and r + 64): the sums go to
@@ -364,7 +375,27 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
         }
     };
 
-    if (KS == 2) {
+    if (KS == 4) {
+        // four CTAs, four quarters of K: CTA r finishes columns [64 r, 64 r + 64); block (d, s) of the
+        // tile's slot holds what the s-th CTA after d (cyclically) leaves for d
+        unsigned char* slot4 = p.splitk + (size_t)(blockIdx.x + gridDim.x * blockIdx.y) * (12 * WA_QUARTER_SLOT);
+        if (ep_warp && ok) {
+#pragma unroll 1
+            for (int dd = 1; dd < 4; dd++) {
+                const int d = (ksplit + dd) & 3;                    // destination; this CTA is its source 3 - dd
+                send_chunk(d * KEEP + eh * PER_WARP, slot4 + (size_t)(d * 3 + 3 - dd) * WA_QUARTER_SLOT, eh * 8);
+            }
+        }
+        TRACE(41);
+        cluster_sync_all();          // release / acquire at cluster scope: every block is published
+        TRACE(43);
+        if (ep_warp && ok) {
+            const unsigned char* row = slot4 + (size_t)(ksplit * 3) * WA_QUARTER_SLOT;
+            float4 r0[8];
+            load_peer(r0, eh * PER_WARP, row, eh * 8);
+            finalize_chunk(eh * PER_WARP, r0, row + WA_QUARTER_SLOT, eh * 8);
+        }
+    } else if (KS == 2) {
         const int send0 = (1 - ksplit) * (WA_BN / 2);
         unsigned char* theirs = slot + (size_t)(1 - ksplit) * WA_HALF_SLOT;
         const unsigned char* mine = slot + (size_t)ksplit * WA_HALF_SLOT;
@@ -471,8 +502,10 @@ LuxBackendError launch_qgemm_i4_tc_wa(Context* ctx, const QArgs& a) {
     // Split K over a pair of CTAs when whole tiles alone would leave most SMs idle.
     const int tiles = (nout / out_w) * ((a.M + WA_BN - 1) / WA_BN);
     const bool can_split = a.K % 256 == 0 && (size_t)tiles * (2 * WA_HALF_SLOT) <= ctx->d_splitk_bytes;
-    int ks = (tiles * 2 <= ctx->sm_count && can_split) ? 2 : 1;
-    if (g_tune.gemm_tc_splitk == 1 || (g_tune.gemm_tc_splitk == 2 && can_split)) ks = g_tune.gemm_tc_splitk;
+    const bool can_split4 = a.K % 512 == 0 && (size_t)tiles * (12 * WA_QUARTER_SLOT) <= ctx->d_splitk_bytes;
+    int ks = (tiles * 4 <= ctx->sm_count && can_split4) ? 4 : (tiles * 2 <= ctx->sm_count && can_split) ? 2 : 1;
+    if (g_tune.gemm_tc_splitk == 1 || (g_tune.gemm_tc_splitk == 2 && can_split) || (g_tune.gemm_tc_splitk == 4 && can_split4))
+        ks = g_tune.gemm_tc_splitk;
     const int stages = g_tune.gemm_tc_stages >= 2 && g_tune.gemm_tc_stages <= WA_MAX_UNITS ? g_tune.gemm_tc_stages : WA_MAX_UNITS;
     int groups = g_tune.gemm_tc_groups >= 2 && g_tune.gemm_tc_groups <= WA_MAX_GROUPS ? g_tune.gemm_tc_groups : 2;
     groups = std::min(groups, stages);
@@ -503,7 +536,8 @@ LuxBackendError launch_qgemm_i4_tc_wa(Context* ctx, const QArgs& a) {
     auto go = [&](auto bf_tag, auto sw_tag) {
         constexpr bool BF_ = decltype(bf_tag)::value;
         constexpr bool SW_ = decltype(sw_tag)::value;
-        return ks == 2 ? launch_wa<BF_, 2, SW_>(mx, p, grid, threads, smem, ctx->stream)
+        return ks == 4 ? launch_wa<BF_, 4, SW_>(mx, p, grid, threads, smem, ctx->stream)
+             : ks == 2 ? launch_wa<BF_, 2, SW_>(mx, p, grid, threads, smem, ctx->stream)
                        : launch_wa<BF_, 1, SW_>(mx, p, grid, threads, smem, ctx->stream);
     };
     cudaError_t e;
