@@ -1,4 +1,5 @@
-"""GPU parity of the tcgen05/TMEM int4 GEMM (batch >= 33) against the CPU oracle.
+"""GPU parity of the tcgen05/TMEM int4 GEMM with the converted weights as the shared-memory B
+operand (lux_qgemm_i4_tc; batch >= 33) against the CPU oracle.
 
 The tensor-core path multiplies 16-bit operands: weights are dequantized to the
 activation type with ONE rounding (the same bits lux_cuda_qdequant writes), so the
@@ -14,6 +15,15 @@ from webgpu_b200 import synth
 
 pytestmark = pytest.mark.gpu
 TOL_16 = 5e-3
+
+
+@pytest.fixture(autouse=True)
+def _b_operand_kernel(backend):
+    """This file covers lux_qgemm_i4_tc (converted weights as the shared-memory B operand), which
+    by default only takes the shapes lux_qgemm_i4_tc_wa does not: select it for every test here."""
+    backend.tune("gemm_tc_kernel", 1)
+    yield
+    backend.tune("gemm_tc_kernel", 0)
 
 
 def _run(ctx, x, layer, flags=0):
@@ -76,9 +86,10 @@ def test_gemm_two_batch_tiles(ctx, backend, M):
     assert ctx.last_device_status() == 0
 
 
-def test_config3_prefill_gemm(ctx):
+def test_config3_prefill_gemm(ctx, backend):
     x, layer = synth.config3()
     y = _run(ctx, x, layer)
+    assert backend.last_kernel_name() == "lux_qgemm_i4_tc_bf16"
     ref = _oracle(x, layer)
     err = orc.rel_l2(y, ref)
     assert err < TOL_16, err
