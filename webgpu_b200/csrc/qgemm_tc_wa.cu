@@ -497,6 +497,9 @@ LuxBackendError launch_qgemm_i4_tc_wa(Context* ctx, const QArgs& a) {
     if (a.scale_dtype != LUX_QDTYPE_F16 || a.x_dtype != a.y_dtype) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
     if (a.x_dtype != LUX_QDTYPE_BF16 && a.x_dtype != LUX_QDTYPE_F16) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
     if ((reinterpret_cast<uintptr_t>(a.w) & 15u) || (a.K / 2) % 16) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+    // x is fetched by TMA and y written in 16-byte pieces: a caller's oddly offset view stays with the
+    // kernels that use plain loads and stores
+    if ((reinterpret_cast<uintptr_t>(a.x) & 15u) || (reinterpret_cast<uintptr_t>(a.y) & 15u)) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
     const bool bf16 = a.x_dtype == LUX_QDTYPE_BF16;
 
     // Split K over a pair of CTAs when whole tiles alone would leave most SMs idle.
