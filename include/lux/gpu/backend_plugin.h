@@ -1,8 +1,8 @@
 /*
  * lux/gpu/backend_plugin.h -- backend plugin boundary of luxcpp/gpu, RECONSTRUCTED.
  *
- * The original header lives in the sibling project luxcpp/gpu and is not available
- * to this build.  Every declaration below was rebuilt from the way the WebGPU plugin
+ * The original header belongs to the sibling project luxcpp/gpu and is not shipped with
+ * luxcpp/webgpu.  Every declaration below was rebuilt from the way the WebGPU plugin
  * uses it (citations are paths inside luxcpp/webgpu):
  *
  *   - vtable slot order and signatures ..... src/webgpu_plugin.cpp:4022-4123 and the
@@ -175,18 +175,26 @@ typedef struct lux_gpu_backend_vtbl {
     /* ecrecover (:3960) */
     LuxBackendError (*op_ecrecover_batch)(LuxBackendContext*, const void*, void*, size_t);
 
-    /* post-quantum / threshold / Schnorr batches (:3973-4016): every one is a
-     * NOT_SUPPORTED stub in the plugin; parameter lists beyond the context are not
-     * relied on here, so they are declared pointer-sized. */
-    void* op_mldsa_verify_batch;
-    void* op_mlkem_decapsulate_batch;
-    void* op_slhdsa_verify_batch;
-    void* op_ringtail_partial_sign_batch;
-    void* op_ringtail_combine_batch;
-    void* op_frost_partial_verify_batch;
-    void* op_cggmp21_partial_sign_batch;
-    void* op_ed25519_verify_batch;
-    void* op_sr25519_verify_batch;
+    /* post-quantum / threshold / Schnorr batches (:3973-4016): every one is a callable
+     * NOT_SUPPORTED stub in the plugin ("CPU backend handles these"), with these parameters. */
+    LuxBackendError (*op_mldsa_verify_batch)(LuxBackendContext*, const uint8_t* const* pks, const uint8_t* const* msgs,
+                                             const uint8_t* const* sigs, bool* results, size_t n);
+    LuxBackendError (*op_mlkem_decapsulate_batch)(LuxBackendContext*, const uint8_t* const* sks, const uint8_t* const* cts,
+                                                  uint8_t** shared, size_t n);
+    LuxBackendError (*op_slhdsa_verify_batch)(LuxBackendContext*, const uint8_t* const* pks, const uint8_t* const* msgs,
+                                              const uint8_t* const* sigs, bool* results, size_t n);
+    LuxBackendError (*op_ringtail_partial_sign_batch)(LuxBackendContext*, const uint8_t* const* shares,
+                                                      const uint8_t* const* msgs, uint8_t** partials, size_t n);
+    LuxBackendError (*op_ringtail_combine_batch)(LuxBackendContext*, const uint8_t* const* partials, const int32_t* indices,
+                                                 uint8_t** sigs, size_t n, size_t threshold);
+    LuxBackendError (*op_frost_partial_verify_batch)(LuxBackendContext*, const uint8_t* const*, const uint8_t* const*,
+                                                     const uint8_t* const*, const uint8_t* const*, bool* results, size_t n);
+    LuxBackendError (*op_cggmp21_partial_sign_batch)(LuxBackendContext*, const uint8_t* const* shares, const uint8_t* msg_hash,
+                                                     uint8_t** partials, size_t n);
+    LuxBackendError (*op_ed25519_verify_batch)(LuxBackendContext*, const uint8_t* const* pks, const uint8_t* const* msgs,
+                                               const uint8_t* const* sigs, bool* results, size_t n);
+    LuxBackendError (*op_sr25519_verify_batch)(LuxBackendContext*, const uint8_t* const* pks, const uint8_t* const* msgs,
+                                               const uint8_t* const* sigs, bool* results, size_t n);
 } lux_gpu_backend_vtbl;
 
 #define LUX_GPU_BACKEND_VTBL_SLOTS 65

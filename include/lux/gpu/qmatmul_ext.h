@@ -56,7 +56,16 @@ enum {
     /* W holds [gate ; up] stacked on the output axis (N = 2*I).  The kernel writes
      * y[M, I] = silu(x.gate^T) * (x.up^T), both products kept in f32
      * (steel_gemm_silu_mul, steel/gemm/steel_gemm_fused.wgsl:452-558). */
-    LUX_QMATMUL_FLAG_SWIGLU  = 1u << 1
+    LUX_QMATMUL_FLAG_SWIGLU  = 1u << 1,
+    /* The weight, scale or zero-point buffer of this call may still be being written by
+     * earlier work on the same stream (a dequantize / unpack / quantize call made with
+     * NO_SYNC, a caller's own kernel, an asynchronous copy).  Without this flag the matmul
+     * kernels may be launched so that their prologue -- which requests weights, scales and
+     * zero-points, never activations -- overlaps the tail of the previous kernel on the
+     * stream (programmatic dependent launch); with it the launch is ordered after all
+     * earlier work like any other.  The library sets it by itself after its own writer
+     * calls; a caller whose own stream work produces these operands must set it. */
+    LUX_QMATMUL_FLAG_WEIGHTS_VOLATILE = 1u << 2
 };
 
 typedef struct LuxQMatmulDesc {

@@ -63,12 +63,22 @@ def test_vtable_slots(backend):
                   "buffer_copy_from_host", "buffer_get_host_ptr", "op_add_f32", "op_sub_f32", "op_mul_f32",
                   "op_matmul_f32", "op_ntt_forward", "op_msm", "op_kzg_verify", "op_ecrecover_batch"):
         assert getattr(raw, field), field
+    # the post-quantum / threshold / Schnorr batches are callable stubs in the reference
+    # (src/webgpu_plugin.cpp:3973-4016, 4110-4122), so a loader may call them without a null check
+    for field in B.VTBL_FIELDS[56:]:
+        assert getattr(raw, field), field
 
 
 def test_out_of_scope_slots_answer_not_supported(backend):
     # the reference's "fall back to CPU" signal (src/webgpu_plugin.cpp:2087-2092)
     assert backend.vt["op_ntt_forward"](None, None, 0, 0) == B.NOT_SUPPORTED
     assert backend.vt["op_msm"](None, None, None, None, 0, 0) == B.NOT_SUPPORTED
+    for field in ("op_mldsa_verify_batch", "op_slhdsa_verify_batch", "op_ed25519_verify_batch", "op_sr25519_verify_batch"):
+        assert backend.vt[field](None, None, None, None, None, 0) == B.NOT_SUPPORTED, field
+    for field in ("op_mlkem_decapsulate_batch", "op_ringtail_partial_sign_batch", "op_cggmp21_partial_sign_batch"):
+        assert backend.vt[field](None, None, None, None, 0) == B.NOT_SUPPORTED, field
+    assert backend.vt["op_ringtail_combine_batch"](None, None, None, None, 0, 0) == B.NOT_SUPPORTED
+    assert backend.vt["op_frost_partial_verify_batch"](None, None, None, None, None, None, 0) == B.NOT_SUPPORTED
 
 
 def test_argument_validation_without_device(backend):
@@ -107,6 +117,9 @@ def test_routing(backend, kw, has_zeros, code, route):
 def test_kernel_table_without_device(backend):
     names = backend.kernel_names()
     assert "lux_qskinny_i4_g128" in names and "lux_qgemm_i4_tc_bf16" in names
+    # every name lux_cuda_last_kernel_name can report for a default route is in the table
+    for n in ("lux_qgemm_i4_tc_wa_f16", "lux_qgemm_i4_tc_wa_bf16", "lux_qgemv_i4_g128_units_fx", "lux_qgemv_i8_g32_units_fx"):
+        assert n in names, n
     L = backend.lib
     assert L.lux_cuda_kernel_get(b"no_such_kernel") is None
     assert L.lux_cuda_kernel_get(None) is None

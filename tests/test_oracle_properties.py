@@ -102,3 +102,21 @@ def test_config_shapes():
     assert l1.w.dtype == np.int8 and l1.scales.shape == (4096, 128) and l1.w.min() >= -127
     # determinism: same seed, same bytes
     assert np.array_equal(synth.config2()[1].w[:4], l.w[:4])
+
+
+def test_cpu_baseline_agrees_with_the_oracle():
+    """The timed CPU baseline (oracle/cpu_baseline.c: scale and zero-point hoisted per group,
+    vectorised, multi-threaded) computes the oracle's arithmetic in another summation order."""
+    from oracle import cpu_baseline as cb
+
+    x = synth.activations(3, 1024, "f16", 9, "cb.x")
+    for symmetric in (False, True):
+        layer = synth.int4_layer(160, 1024, 9, "cb", symmetric=symmetric)
+        ref = orc.qmatmul(x, *layer.triple, bits=4, group=128)
+        for threads in (0, 1):
+            assert orc.rel_l2(cb.qmatmul_i4(x, *layer.triple, threads=threads), ref) < 1e-3
+    gate_up, down = synth.mlp_layers(512, 768, 256, 9, "cb.mlp")
+    xm = synth.activations(2, 512, "f16", 9, "cb.xm")
+    assert orc.rel_l2(cb.mlp_i4(xm, gate_up.triple, down.triple),
+                      orc.mlp(xm, gate_up.triple, down.triple, fused=True)) < 1e-3
+    assert cb.num_procs() >= 1

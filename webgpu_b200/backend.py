@@ -146,6 +146,15 @@ _SIGS = {   # vtable slot -> (restype, argtypes); unwired slots are not callable
     "op_matmul_f32": (_int, [_vp, _vp, _vp, _vp, _int, _int, _int]),
     "op_ntt_forward": (_int, [_vp, _vp, _sz, C.c_uint64]),
     "op_msm": (_int, [_vp, _vp, _vp, _vp, _sz, _int]),
+    "op_mldsa_verify_batch": (_int, [_vp, _vp, _vp, _vp, _vp, _sz]),
+    "op_mlkem_decapsulate_batch": (_int, [_vp, _vp, _vp, _vp, _sz]),
+    "op_slhdsa_verify_batch": (_int, [_vp, _vp, _vp, _vp, _vp, _sz]),
+    "op_ringtail_partial_sign_batch": (_int, [_vp, _vp, _vp, _vp, _sz]),
+    "op_ringtail_combine_batch": (_int, [_vp, _vp, _vp, _vp, _sz, _sz]),
+    "op_frost_partial_verify_batch": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _sz]),
+    "op_cggmp21_partial_sign_batch": (_int, [_vp, _vp, _vp, _vp, _sz]),
+    "op_ed25519_verify_batch": (_int, [_vp, _vp, _vp, _vp, _vp, _sz]),
+    "op_sr25519_verify_batch": (_int, [_vp, _vp, _vp, _vp, _vp, _sz]),
 }
 
 

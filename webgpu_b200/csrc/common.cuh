@@ -47,6 +47,11 @@ struct Context {
     size_t         d_splitk_bytes = 0;      // allocated with the context (no entry point allocates for it)
     std::mutex     mu;                      // guards the staging buffers
     int            sm_count = 148;
+    // A kernel of this library that WRITES a buffer a later matmul may bind as weights, scales or
+    // zero-points (unpack, dequantize, quantize) has been enqueued without a wait.  The next matmul
+    // is then launched without the programmatic-launch attribute, because its prologue reads those
+    // operands before griddepcontrol.wait (see launch_pdl below).
+    bool           writer_pending = false;
 };
 
 inline Context* as_ctx(LuxBackendContext* c) { return reinterpret_cast<Context*>(c); }
@@ -123,9 +128,17 @@ extern Tunables g_tune;
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+//
+// Contract for the operands read before pdl_wait(): weights, scales and zero-points must be complete
+// when the call is enqueued -- or the call carries LUX_QMATMUL_FLAG_WEIGHTS_VOLATILE, or the tunable
+// pdl = 2 is set.  Where the library can see the hazard itself (one of its own writer kernels is
+// pending on the context) it drops the attribute for the next launch on its own: pdl_allowed().
+struct Context;
+inline bool pdl_allowed(Context* ctx, bool weights_volatile);
+
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_pdl(void (*kfn)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, unsigned cluster_z,
-                              Args&&... args) {
+inline cudaError_t launch_pdl(bool allow, void (*kfn)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              unsigned cluster_z, Args&&... args) {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -140,7 +153,7 @@ inline cudaError_t launch_pdl(void (*kfn)(KArgs...), dim3 grid, dim3 block, size
         attr[n].val.clusterDim.z = cluster_z;
         n++;
     }
-    if (g_tune.pdl != 2) {
+    if (allow) {
         attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[n].val.programmaticStreamSerializationAllowed = 1;
         n++;
@@ -172,7 +185,18 @@ struct QArgs {
     int x_dtype, scale_dtype, y_dtype;
     bool swiglu;
     const PushTarget* push = nullptr;   // set: push the outputs into the peers' windows instead of writing y
+    bool weights_volatile = false;      // LUX_QMATMUL_FLAG_WEIGHTS_VOLATILE: w / scales / zeros may still be being written
 };
+
+// Whether the next matmul launch on `ctx` may carry the programmatic-launch attribute.  A launch
+// without it waits for everything before it on the stream, so it also clears the pending-writer mark.
+inline bool pdl_allowed(Context* ctx, bool weights_volatile) {
+    if (weights_volatile || ctx->writer_pending) {
+        ctx->writer_pending = false;
+        return false;
+    }
+    return g_tune.pdl != 2;
+}
 
 // allreduce_push.cu: the push target of a connected communicator (false if it cannot take `count`
 // 16-bit elements), and the all-reduce launch with or without its own push phase

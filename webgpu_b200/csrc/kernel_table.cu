@@ -24,6 +24,11 @@ const void* kernel_addr_qdequant_i8();
 const void* kernel_addr_qgemm_i4_tc_bf16();
 const void* kernel_addr_qgemm_i4_tc_f16();
 const void* kernel_addr_qgemm_i4_tc_wa_bf16();
+const void* kernel_addr_qgemm_i4_tc_wa_f16();
+const void* kernel_addr_qgemm_i4_tc_wa_bf16_swiglu();
+const void* kernel_addr_qgemm_i4_tc_wa_f16_swiglu();
+const void* kernel_addr_qgemv_i4_units_fx_swiglu();
+const void* kernel_addr_qgemv_i4_units_fx_batch2();
 }  // namespace luxcuda
 
 namespace {
@@ -48,6 +53,11 @@ const Entry kTable[] = {
     {"lux_qgemm_i4_tc_bf16",       luxcuda::kernel_addr_qgemm_i4_tc_bf16,   320, 1, 1},
     {"lux_qgemm_i4_tc_f16",        luxcuda::kernel_addr_qgemm_i4_tc_f16,    320, 1, 1},
     {"lux_qgemm_i4_tc_wa_bf16",    luxcuda::kernel_addr_qgemm_i4_tc_wa_bf16, 320, 1, 1},
+    {"lux_qgemm_i4_tc_wa_f16",     luxcuda::kernel_addr_qgemm_i4_tc_wa_f16,  320, 1, 1},
+    {"lux_qgemm_i4_tc_wa_bf16_swiglu", luxcuda::kernel_addr_qgemm_i4_tc_wa_bf16_swiglu, 320, 1, 1},
+    {"lux_qgemm_i4_tc_wa_f16_swiglu",  luxcuda::kernel_addr_qgemm_i4_tc_wa_f16_swiglu,  320, 1, 1},
+    {"lux_qgemv_i4_g128_units_fx_swiglu", luxcuda::kernel_addr_qgemv_i4_units_fx_swiglu, 512, 1, 1},
+    {"lux_qgemv_i4_g128_units_fx_batch2", luxcuda::kernel_addr_qgemv_i4_units_fx_batch2, 512, 1, 1},
 };
 constexpr size_t kCount = sizeof(kTable) / sizeof(kTable[0]);
 

@@ -28,6 +28,7 @@ LuxBackendError finish_op(Context* ctx, bool no_sync, const char* what) {
         // (src/webgpu_plugin.cpp:1046-1048); a failed stream wait is the CUDA analogue.
         return LUX_BACKEND_ERROR_DEVICE_LOST;
     }
+    ctx->writer_pending = false;             // everything enqueued so far has completed
     if (ctx->h_status && *(volatile uint32_t*)ctx->h_status != 0) {
         ctx->last_status = *(volatile uint32_t*)ctx->h_status;
         *(volatile uint32_t*)ctx->h_status = 0;
@@ -316,6 +317,12 @@ static LuxBackendError ns_kzg_commit(LuxBackendContext*, const void*, const void
 static LuxBackendError ns_kzg_open(LuxBackendContext*, const void*, const void*, const void*, void*, size_t, int) { NS; }
 static LuxBackendError ns_kzg_verify(LuxBackendContext*, const void*, const void*, const void*, const void*, const void*, bool*, int) { NS; }
 static LuxBackendError ns_ecrecover(LuxBackendContext*, const void*, void*, size_t) { NS; }
+// post-quantum, threshold and Schnorr batches: callable stubs in the reference too (:3973-4016)
+static LuxBackendError ns_verify3(LuxBackendContext*, const uint8_t* const*, const uint8_t* const*, const uint8_t* const*, bool*, size_t) { NS; }
+static LuxBackendError ns_batch2_out(LuxBackendContext*, const uint8_t* const*, const uint8_t* const*, uint8_t**, size_t) { NS; }
+static LuxBackendError ns_ringtail_combine(LuxBackendContext*, const uint8_t* const*, const int32_t*, uint8_t**, size_t, size_t) { NS; }
+static LuxBackendError ns_frost_verify(LuxBackendContext*, const uint8_t* const*, const uint8_t* const*, const uint8_t* const*, const uint8_t* const*, bool*, size_t) { NS; }
+static LuxBackendError ns_cggmp21_sign(LuxBackendContext*, const uint8_t* const*, const uint8_t*, uint8_t**, size_t) { NS; }
 #undef NS
 
 // ---------------------------------------------------------------------------------
@@ -396,15 +403,15 @@ static const lux_gpu_backend_vtbl cuda_vtbl = {
 
     .op_ecrecover_batch = ns_ecrecover,
 
-    .op_mldsa_verify_batch          = nullptr,
-    .op_mlkem_decapsulate_batch     = nullptr,
-    .op_slhdsa_verify_batch         = nullptr,
-    .op_ringtail_partial_sign_batch = nullptr,
-    .op_ringtail_combine_batch      = nullptr,
-    .op_frost_partial_verify_batch  = nullptr,
-    .op_cggmp21_partial_sign_batch  = nullptr,
-    .op_ed25519_verify_batch        = nullptr,
-    .op_sr25519_verify_batch        = nullptr,
+    .op_mldsa_verify_batch          = ns_verify3,
+    .op_mlkem_decapsulate_batch     = ns_batch2_out,
+    .op_slhdsa_verify_batch         = ns_verify3,
+    .op_ringtail_partial_sign_batch = ns_batch2_out,
+    .op_ringtail_combine_batch      = ns_ringtail_combine,
+    .op_frost_partial_verify_batch  = ns_frost_verify,
+    .op_cggmp21_partial_sign_batch  = ns_cggmp21_sign,
+    .op_ed25519_verify_batch        = ns_verify3,
+    .op_sr25519_verify_batch        = ns_verify3,
 };
 
 static_assert(sizeof(lux_gpu_backend_vtbl) == LUX_GPU_BACKEND_VTBL_SLOTS * sizeof(void*),

@@ -59,20 +59,6 @@ constexpr int WA_QUARTER_SLOT = 64 * BM * 4;   // four K splits: 64 columns per 
 constexpr int WA_STAGE_PITCH = 320;        // bytes per batch row of the staged output tile: 256 + 64, so that the
                                            // even and the odd lanes of a staging store use different banks
 
-// Optional timeline for kernel development: built only with -DLUX_WA_TRACE (the product build
-// leaves it out).  CTA (0,0,0) records clock64() per warp at each step into g_wa_trace.
-#ifdef LUX_WA_TRACE
-__device__ unsigned long long g_wa_trace[32 * 128];
-#define TRACE_DECL int tr_i = 0
-#define TRACE(tag)                                                                   \
-    do {                                                                             \
-        if ((blockIdx.x | blockIdx.y | blockIdx.z) == 0 && (threadIdx.x & 31) == 0 && tr_i < 128)                  \
-            g_wa_trace[(threadIdx.x >> 5) * 128 + tr_i++] = ((unsigned long long)(tag) << 56) | (clock64() & 0xFFFFFFFFFFFFFFull); \
-    } while (0)
-#else
-#define TRACE_DECL
-#define TRACE(tag)
-#endif
 
 struct WaParams {
     const uint8_t* w;         // [N, K/2]
@@ -117,8 +103,6 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * P + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
-    TRACE_DECL;
-    TRACE(1);
     pdl_launch_dependents();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     constexpr int OUT_W = SW ? BM / 2 : BM;         // outputs per tile: with SwiGLU lanes 0..63 hold gate rows, 64..127 up rows
@@ -184,22 +168,17 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
         // x may come from the previous kernel of the stream (the weights fetched above are
         // static): wait for it here; the CTA barrier below orders every other thread's later
         // reads and the output stores behind this wait.
-        TRACE(6);
         pdl_wait();
-        TRACE(4);
         for (int u = 0; u < P && u < U; u++) load_x_unit(u, u);
-        TRACE(5);
     }
     if (warp == 1) {
         tmem_alloc(smem_u32(tmem_slot), WA_TMEM_COLS);
         tmem_relinquish();
     }
-    TRACE(3);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    TRACE(2);
     const uint32_t tmem_a0 = tmem_base + (uint32_t)WA_BN;      // first A unit
 
     bool ok = true;
@@ -210,7 +189,6 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
             uint32_t ph = 1;                  // second lap onwards: the first was issued above
             for (int u = P; u < U; u++) {
                 if (!mbar_wait_relaxed(empty(s), ph ^ 1u, abort_flag)) break;
-                TRACE(10);
                 load_x_unit(u, s);
                 if (++s == P) { s = 0; ph ^= 1u; }
             }
@@ -226,7 +204,6 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
             for (int u = 0; u < U; u++) {
                 ok = mbar_wait(full(s), ph, abort_flag);
                 if (!ok) break;
-                TRACE(20);
                 tc_fence_after();
                 const uint64_t b_desc = make_kmajor_sw128_desc(smem_u32(x_ring + (size_t)s * WA_UNIT_X_BYTES));
                 const uint32_t a_tmem = tmem_a0 + (uint32_t)(s * WA_UNIT_A_COLS);
@@ -237,9 +214,7 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
                     const uint64_t b_off = (uint64_t)((k >> 2) * (WA_X_BYTES >> 4) + 2 * (k & 3));
                     umma_f16_ts(tmem_base, a_tmem + (uint32_t)(k * 8), b_desc + b_off, idesc, (u | k) != 0 ? 1u : 0u);
                 }
-                TRACE(21);
                 umma_commit(empty(s));        // x unit and A unit reusable once these MMAs have read them
-                TRACE(22);
                 if (++s == P) { s = 0; ph ^= 1u; }
             }
             if (ok) umma_commit(acc_full);
@@ -260,7 +235,6 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
             const uint32_t a_dst = tmem_a0 + ((uint32_t)(quad * 32) << 16) + (uint32_t)(s * WA_UNIT_A_COLS);
 #pragma unroll
             for (int h = 0; h < 2; h++) {
-                TRACE(30);
                 const uint32_t words[8] = {cq[2 * h].x, cq[2 * h].y, cq[2 * h].z, cq[2 * h].w,
                                            cq[2 * h + 1].x, cq[2 * h + 1].y, cq[2 * h + 1].z, cq[2 * h + 1].w};
                 uint32_t out[32];
@@ -270,10 +244,8 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
                     out[4 * j + 0] = v.x; out[4 * j + 1] = v.y; out[4 * j + 2] = v.z; out[4 * j + 3] = v.w;
                 }
                 if (h == 0) {
-                    TRACE(31);
                     ok = warp_wait_relaxed(empty(s), ph ^ 1u, abort_flag, lane);   // A unit s free (warp-uniform outcome)
                     if (!ok) break;
-                    TRACE(32);
                     tc_fence_after();
                 }
                 tmem_st32(a_dst + (uint32_t)(h * WA_A_COLS), out);
@@ -283,13 +255,11 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(full(s));
-            TRACE(33);
         }
         if (ok && warp < 10) ok = warp_wait(acc_full, 0u, abort_flag, lane);
         if (ok) tc_fence_after();
     }
     __syncwarp();
-    TRACE(40);
 
     // =============================== epilogue ===========================================
     // Warps 2..9: quarter `quad` of the lanes (weight rows), half `eh` of the columns handled,
@@ -386,9 +356,7 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
                 send_chunk(d * KEEP + eh * PER_WARP, slot4 + (size_t)(d * 3 + 3 - dd) * WA_QUARTER_SLOT, eh * 8);
             }
         }
-        TRACE(41);
         cluster_sync_all();          // release / acquire at cluster scope: every block is published
-        TRACE(43);
         if (ep_warp && ok) {
             const unsigned char* row = slot4 + (size_t)(ksplit * 3) * WA_QUARTER_SLOT;
             float4 r0[8];
@@ -403,9 +371,7 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
             send_chunk(send0 + eh * PER_WARP, theirs, eh * 16);
             send_chunk(send0 + eh * PER_WARP + 32, theirs, eh * 16 + 8);
         }
-        TRACE(41);
         cluster_sync_all();          // release / acquire at cluster scope: both halves are published
-        TRACE(43);
         if (ep_warp && ok) {
             float4 ra[8], rb[8];
             load_peer(ra, eh * PER_WARP, mine, eh * 16);
@@ -424,7 +390,6 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
         if (ok) tc_fence_before();
         // the eight epilogue warps (and only they) meet here on every path
         asm volatile("bar.sync 1, 256;" ::: "memory");
-        TRACE(46);
         if (ok && SW) {
             // one batch row of the tile = 64 outputs = 128 contiguous bytes of y: 8 lanes x 16 bytes,
             // each lane combining eight (gate, up) pairs: silu(gate) * up, narrowed once
@@ -458,9 +423,7 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
         }
     }
 
-    TRACE(44);
     __syncthreads();
-    TRACE(45);
     if (*abort_flag) {
         if (tid == 0 && p.status) atomicOr(p.status, 0x7C050002u);
         for (int i = 0; i < 64; i++) __nanosleep(1000);
@@ -473,7 +436,7 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
 }
 
 template <bool BF16, int KS, bool SW>
-cudaError_t launch_wa(const CUtensorMap& mx, const WaParams& p, dim3 grid, int threads, size_t smem, cudaStream_t st) {
+cudaError_t launch_wa(bool pdl, const CUtensorMap& mx, const WaParams& p, dim3 grid, int threads, size_t smem, cudaStream_t st) {
     auto kfn = lux_qgemm_i4_tc_wa<BF16, KS, SW>;
     static std::atomic<size_t> configured[64];
     int dev = 0;
@@ -483,7 +446,7 @@ cudaError_t launch_wa(const CUtensorMap& mx, const WaParams& p, dim3 grid, int t
         if (e != cudaSuccess) return e;
         configured[dev].store(smem, std::memory_order_relaxed);
     }
-    return launch_pdl(kfn, grid, dim3((unsigned)threads), smem, st, (unsigned)KS, mx, p);
+    return launch_pdl(pdl, kfn, grid, dim3((unsigned)threads), smem, st, (unsigned)KS, mx, p);
 }
 
 }  // namespace
@@ -536,12 +499,13 @@ LuxBackendError launch_qgemm_i4_tc_wa(Context* ctx, const QArgs& a) {
 
     dim3 grid(nout / out_w, (a.M + WA_BN - 1) / WA_BN, ks);
     const int threads = (2 + 4 * groups) * 32;                  // groups >= 2: the epilogue needs warps 2..9
+    const bool pdl = pdl_allowed(ctx, a.weights_volatile);
     auto go = [&](auto bf_tag, auto sw_tag) {
         constexpr bool BF_ = decltype(bf_tag)::value;
         constexpr bool SW_ = decltype(sw_tag)::value;
-        return ks == 4 ? launch_wa<BF_, 4, SW_>(mx, p, grid, threads, smem, ctx->stream)
-             : ks == 2 ? launch_wa<BF_, 2, SW_>(mx, p, grid, threads, smem, ctx->stream)
-                       : launch_wa<BF_, 1, SW_>(mx, p, grid, threads, smem, ctx->stream);
+        return ks == 4 ? launch_wa<BF_, 4, SW_>(pdl, mx, p, grid, threads, smem, ctx->stream)
+             : ks == 2 ? launch_wa<BF_, 2, SW_>(pdl, mx, p, grid, threads, smem, ctx->stream)
+                       : launch_wa<BF_, 1, SW_>(pdl, mx, p, grid, threads, smem, ctx->stream);
     };
     cudaError_t e;
     if (a.swiglu) e = bf16 ? go(std::true_type{}, std::true_type{}) : go(std::false_type{}, std::true_type{});
@@ -550,12 +514,10 @@ LuxBackendError launch_qgemm_i4_tc_wa(Context* ctx, const QArgs& a) {
     return map_cuda(e, "lux_qgemm_i4_tc_wa");
 }
 
-#ifdef LUX_WA_TRACE
-extern "C" __attribute__((visibility("default"))) int lux_cuda_debug_wa_trace(unsigned long long* out, int n) {
-    return (int)cudaMemcpyFromSymbol(out, g_wa_trace, sizeof(unsigned long long) * (size_t)n);
-}
-#endif
 
 const void* kernel_addr_qgemm_i4_tc_wa_bf16() { return (const void*)lux_qgemm_i4_tc_wa<true, 2, false>; }
+const void* kernel_addr_qgemm_i4_tc_wa_f16() { return (const void*)lux_qgemm_i4_tc_wa<false, 2, false>; }
+const void* kernel_addr_qgemm_i4_tc_wa_bf16_swiglu() { return (const void*)lux_qgemm_i4_tc_wa<true, 1, true>; }
+const void* kernel_addr_qgemm_i4_tc_wa_f16_swiglu() { return (const void*)lux_qgemm_i4_tc_wa<false, 1, true>; }
 
 }  // namespace luxcuda

@@ -375,7 +375,7 @@ lux_qgemv_i8_g32_units_fx(const __grid_constant__ CUtensorMap map_w, const I8Uni
 }
 
 template <int MM>
-cudaError_t launch_inst(const CUtensorMap& map, const I8UnitsParams& p, int grid, size_t smem, cudaStream_t st) {
+cudaError_t launch_inst(bool pdl, const CUtensorMap& map, const I8UnitsParams& p, int grid, size_t smem, cudaStream_t st) {
     auto kfn = lux_qgemv_i8_g32_units_fx<MM>;
     static std::atomic<size_t> configured[64];
     int dev = 0;
@@ -385,7 +385,7 @@ cudaError_t launch_inst(const CUtensorMap& map, const I8UnitsParams& p, int grid
         if (e != cudaSuccess) return e;
         configured[dev & 63].store(smem, std::memory_order_relaxed);
     }
-    return launch_pdl(kfn, dim3((unsigned)grid), dim3(UW * 32), smem, st, 1, map, p);
+    return launch_pdl(pdl, kfn, dim3((unsigned)grid), dim3(UW * 32), smem, st, 1, map, p);
 }
 
 }  // namespace
@@ -454,8 +454,9 @@ LuxBackendError launch_qgemv_i8_units(Context* ctx, const QArgs& a) {
     const uint64_t strides[2] = {(uint64_t)a.K, 128};
     const uint32_t box[3] = {128, 16, 2};
     if (!encode_tensor_map_u8(&map, 3, a.w, dims, strides, box, true)) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
-    const cudaError_t e = a.M == 1 ? launch_inst<1>(map, p, grid, smem, ctx->stream)
-                                   : launch_inst<2>(map, p, grid, smem, ctx->stream);
+    const bool pdl = pdl_allowed(ctx, a.weights_volatile);
+    const cudaError_t e = a.M == 1 ? launch_inst<1>(pdl, map, p, grid, smem, ctx->stream)
+                                   : launch_inst<2>(pdl, map, p, grid, smem, ctx->stream);
     count_launch("lux_qgemv_i8_g32_units_fx");
     return map_cuda(e, "lux_qgemv_i8_g32_units_fx");
 }

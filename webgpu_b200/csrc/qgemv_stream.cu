@@ -111,19 +111,6 @@ __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1
 }
 __device__ __forceinline__ float silu_f32(float x) { return x / (1.0f + __expf(-x)); }
 
-// Optional timeline for kernel development: built only with -DLUX_STREAM_TRACE (the product
-// build leaves it out).  CTA 0 records clock64() per warp at each step into g_stream_trace.
-#ifdef LUX_STREAM_TRACE
-__device__ unsigned long long g_stream_trace[32 * 64];
-#define TRACE_DECL int tr_i = 0
-#define TRACE(tag)                                                                   \
-    do {                                                                             \
-        if (blockIdx.x == 0 && lane == 0 && tr_i < 64) g_stream_trace[warp * 64 + tr_i++] = ((unsigned long long)(tag) << 56) | (clock64() & 0xFFFFFFFFFFFFFFull); \
-    } while (0)
-#else
-#define TRACE_DECL
-#define TRACE(tag)
-#endif
 
 struct StreamParams {
     const __half* x;        // [M, K]
@@ -183,8 +170,6 @@ lux_qgemv_i4_g128_stream(const __grid_constant__ CUtensorMap map_w, const Stream
     const int S = p.stages;
     const int stage_bytes = p.cg * 1024;               // cg/2 lines x 16 rows x 128 B
     const int slot4 = 8 * p.tmax;                      // float4 per (tile, warp, gate/up, mt)
-    TRACE_DECL;
-    TRACE(1);
 
     unsigned char* ring = smem;
     unsigned char* xs = ring + (size_t)S * stage_bytes;
@@ -227,7 +212,6 @@ lux_qgemv_i4_g128_stream(const __grid_constant__ CUtensorMap map_w, const Stream
             // lines past the end of a row are zero-filled and still counted
             mbar_expect_tx(full(s), (uint32_t)stage_bytes);
             tma_load_3d(smem_u32(ring + (size_t)s * stage_bytes), &map_w, 0, row0, c * lines, full(s), policy);
-            TRACE(10);
             if (++s == S) { s = 0; ph ^= 1u; }
             if (c == 0) {
                 // scales [16, G] and zero-points [16, ZS] of this tile: two contiguous blocks
@@ -295,7 +279,6 @@ lux_qgemv_i4_g128_stream(const __grid_constant__ CUtensorMap map_w, const Stream
             }
         }
         asm volatile("bar.sync 1, %0;" ::"r"(CW * 32) : "memory");
-        TRACE(2);
 
         float res[NACC][MT][4];
         bool ok = true;
@@ -336,13 +319,11 @@ lux_qgemv_i4_g128_stream(const __grid_constant__ CUtensorMap map_w, const Stream
                     for (int c = 0; c < nchunks && ok; c++) {
                         ok = warp_wait(full(s), ph, abort_flag, lane);
                         if (!ok) break;
-                        TRACE(20);
                         if (c == 0) {
                             // this tile's scales / zero-points (issued right after its first stage)
                             ok = warp_wait(meta_full(ms), mph, abort_flag, lane);
                             if (!ok) break;
                         }
-                        TRACE(4);
                         const unsigned char* st = ring + (size_t)s * stage_bytes;
                         const int gi0 = c * p.cg;
                         const int cgs = min(p.cg, p.G - gi0);      // groups of this stage inside the row
@@ -411,7 +392,6 @@ lux_qgemv_i4_g128_stream(const __grid_constant__ CUtensorMap map_w, const Stream
                         // this warp is done reading the stage: hand it back to the producer
                         __syncwarp();
                         if (lane == 0) mbar_arrive(empty(s));
-                        TRACE(5);
                         if (++s == S) { s = 0; ph ^= 1u; }
                         // fold the zero-points back in and apply the group scales (f32)
 #pragma unroll
@@ -427,7 +407,6 @@ lux_qgemv_i4_g128_stream(const __grid_constant__ CUtensorMap map_w, const Stream
                             }
                         }
                     }
-                    TRACE(23);
                     // done with this tile's scale block
                     __syncwarp();
                     if (lane == 0) mbar_arrive(meta_empty(ms));
@@ -440,7 +419,6 @@ lux_qgemv_i4_g128_stream(const __grid_constant__ CUtensorMap map_w, const Stream
                                 make_float4(res[a][mt][0], res[a][mt][1], res[a][mt][2], res[a][mt][3]);
                     }
                 }
-                TRACE(6);
             }
             if (!ok) break;
             // ---- batch finished: every warp's partials are in; reduce them together ---------
@@ -475,13 +453,10 @@ lux_qgemv_i4_g128_stream(const __grid_constant__ CUtensorMap map_w, const Stream
             __syncwarp();
             if (lane == 0) mbar_arrive(batch_empty);
             bph ^= 1u;
-            TRACE(7);
         }
     }
 
-    TRACE(8);
     __syncthreads();
-    TRACE(9);
     if (*abort_flag) {
         // A bounded wait gave up: report it and give copies still in flight time to land in
         // this CTA's shared memory before it is released.
@@ -605,11 +580,6 @@ LuxBackendError launch_qgemv_i4_stream(Context* ctx, const QArgs& a) {
     return cw >= 16 ? launch_stream_cw<16>(ctx, a) : launch_stream_cw<8>(ctx, a);
 }
 
-#ifdef LUX_STREAM_TRACE
-extern "C" __attribute__((visibility("default"))) int lux_cuda_debug_stream_trace(unsigned long long* out, int n) {
-    return (int)cudaMemcpyFromSymbol(out, g_stream_trace, sizeof(unsigned long long) * (size_t)n);
-}
-#endif
 
 const void* kernel_addr_qgemv_i4_stream() { return (const void*)lux_qgemv_i4_g128_stream<1, false, 16, 2>; }
 

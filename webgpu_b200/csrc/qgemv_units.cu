@@ -105,18 +105,6 @@ __device__ __forceinline__ void mma16832_u8s8(int (&d)[4], uint32_t a0, uint32_t
 }
 __device__ __forceinline__ float silu_f32(float x) { return x / (1.0f + __expf(-x)); }
 
-// Optional timeline for kernel development: built only with -DLUX_STREAM_TRACE.
-#ifdef LUX_STREAM_TRACE
-__device__ unsigned long long g_units_trace[32 * 64];
-#define TRACE_DECL int tr_i = 0
-#define TRACE(tag)                                                                   \
-    do {                                                                             \
-        if (blockIdx.x == 0 && lane == 0 && tr_i < 64) g_units_trace[warp * 64 + tr_i++] = ((unsigned long long)(tag) << 56) | (clock64() & 0xFFFFFFFFFFFFFFull); \
-    } while (0)
-#else
-#define TRACE_DECL
-#define TRACE(tag)
-#endif
 
 struct UnitsParams {
     const __half* x;        // [M, K]
@@ -151,8 +139,6 @@ __global__ void __launch_bounds__(UW * 32, 1) lux_qgemv_i4_g128_units(const Unit
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     const int slot4 = MT * 8 * p.tmax;                  // float4 per unit
-    TRACE_DECL;
-    TRACE(1);
 
     unsigned char* xs = smem;
     float2* xsum = reinterpret_cast<float2*>(xs + (size_t)p.M * p.xstride);
@@ -235,9 +221,7 @@ __global__ void __launch_bounds__(UW * 32, 1) lux_qgemv_i4_g128_units(const Unit
     };
 
     // every warp's group-0 requests go out before any warp's weight requests
-    TRACE(10);
     __syncthreads();
-    TRACE(11);
     // Start the FIFO with S0 chunks; it ramps up to S inside the loop.  (A warp whose copy
     // requests exceed what the SM can keep in flight stalls on the request itself, so asking
     // for everything here would keep every warp from computing until most of it had landed.)
@@ -256,9 +240,7 @@ __global__ void __launch_bounds__(UW * 32, 1) lux_qgemv_i4_g128_units(const Unit
     // fragment order in place (the same walk as above), and the per-group sums are formed ------
     for (int i = tid; i < p.G * MPAD; i += UW * 32)
         if ((i % MPAD) >= p.M) xsum[i] = make_float2(0.f, 0.f);
-    TRACE(12);
     cp_async_wait(issued);
-    TRACE(13);
     for (int m = 0; m < p.M; m++) {
         unsigned char* xdst = xs + (size_t)m * p.xstride;
         for (int c = tid; c < p.G * 16; c += UW * 32) {
@@ -284,9 +266,7 @@ __global__ void __launch_bounds__(UW * 32, 1) lux_qgemv_i4_g128_units(const Unit
             if (cc == 0) xsum[grp * MPAD + m] = make_float2(se + so, 960.0f * so);
         }
     }
-    TRACE(2);
     __syncthreads();
-    TRACE(3);
 
     int xm_off[MT];
     bool xm_live[MT];
@@ -418,11 +398,9 @@ __global__ void __launch_bounds__(UW * 32, 1) lux_qgemv_i4_g128_units(const Unit
                 for (int i = 0; i < 4; i++) res[mt][i] = 0.0f;
         }
         advance(ccur);
-        TRACE(5);
     }
 
     // ---- every unit of the CTA is done: add the U partials of each output -------------------
-    TRACE(7);
     __syncthreads();
     const int nout = ntiles * 16 * MPAD;                     // (tile, row, batch column)
     for (int o = tid; o < nout; o += UW * 32) {
@@ -442,7 +420,6 @@ __global__ void __launch_bounds__(UW * 32, 1) lux_qgemv_i4_g128_units(const Unit
         const float out = SWIGLU ? silu_f32(sum[0]) * sum[NACC - 1] : sum[0];
         p.y[(size_t)m * p.Nout + (tile_lo + tl) * 16 + r] = __float2half_rn(out);
     }
-    TRACE(9);
 }
 
 // ---- block-fixed-point variant, batch MM = 1 or 2 ------------------------------------------------
@@ -515,8 +492,6 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
     constexpr int XG = 3 * MM * 128;                    // bytes of xq per group
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
-    TRACE_DECL;
-    TRACE(1);
 
     unsigned char* fifo = smem + (size_t)warp * p.S * CHUNK;
     unsigned char* xq = smem + (size_t)UW * p.S * CHUNK;
@@ -586,7 +561,6 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
         advance(cload);
         issued++;
     };
-    TRACE(10);
 
     // ---- this CTA's scales and zero-points (one cp.async group), requested before the bulk of
     // the weights: small copies queued behind the weight stream would arrive microseconds later -
@@ -609,7 +583,6 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
     if (!p.zeros)                                         // symmetric: every zero-point is 8
         for (int i = tid; i < (NACC * rows_half * p.ZS + 3) / 4; i += UW * 32)
             reinterpret_cast<uint32_t*>(zsm)[i] = 0x88888888u;
-    TRACE(11);
 
     // Everything above read static model state only; x may come from the previous kernel.
     pdl_wait();
@@ -715,15 +688,12 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
             }
         }
     }
-    TRACE(12);
     // fill the rest of the FIFO (the async engine queues the requests: nothing stalls here; asked
     // for before the conversion they only delay the first chunk and the tables: measured slower)
     if (lane == 0)
         for (int s0 = 1; s0 < p.S && issued < my_chunks; s0++) issue_chunk(s0);
     cp_async_wait(0);                                    // the scales and zero-points have landed
-    TRACE(2);
     __syncthreads();
-    TRACE(3);
 
     // lanes of column g >= 3*MM multiply garbage that nobody reads: point them at a valid column
     const int col = min(g, 3 * MM - 1);
@@ -739,7 +709,6 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
     for (int q = 0; q < my_chunks; q++) {
         ok = warp_wait(bar0 + 8u * (uint32_t)slot, ph, abort_flag, lane);
         if (!ok) break;
-        TRACE(4);
         uint4 wq[2 * CG];
         {
             const unsigned char* st = fifo + (size_t)slot * CHUNK + rg * 128;
@@ -785,7 +754,6 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
         }
 #pragma unroll
         for (int u = 0; u < CG; u++) {
-            TRACE(20 + u);
             const uint4 qa = wq[2 * u], qb = wq[2 * u + 1];
             const unsigned char* xg = xq + (size_t)(gi0 + u) * XG + xcol_off;
             const uint4 xlo = *reinterpret_cast<const uint4*>(xg);          // even k: word pairs 0, 1
@@ -842,10 +810,8 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
             res[0][0] = res[0][1] = res[1][0] = res[1][1] = 0.0f;
         }
         advance(ccur);
-        TRACE(5);
     }
 
-    TRACE(7);
     __syncthreads();
     if (*abort_flag) {
         // A bounded wait gave up: report it and give copies still in flight time to land in
@@ -881,7 +847,6 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
                 asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(pk), "r"(epoch) : "memory");
             }
         }
-        TRACE(9);
         return;
     }
     const int nout = ntiles * 16 * MM;
@@ -898,7 +863,6 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
         const float out = SWIGLU ? silu_f32(sum[0]) * sum[NACC - 1] : sum[0];
         p.y[(size_t)m * p.Nout + (tile_lo + tl) * 16 + r] = __float2half_rn(out);
     }
-    TRACE(9);
 }
 
 template <int MT, bool SW, bool M1, int CG>
@@ -917,7 +881,7 @@ cudaError_t launch_units_inst(const UnitsParams& p, int grid, size_t smem, cudaS
 }
 
 template <int MM, bool SW, int CG>
-cudaError_t launch_units_fx_inst(const CUtensorMap& map, const UnitsParams& p, int grid, size_t smem, cudaStream_t st) {
+cudaError_t launch_units_fx_inst(bool pdl, const CUtensorMap& map, const UnitsParams& p, int grid, size_t smem, cudaStream_t st) {
     auto kfn = lux_qgemv_i4_g128_units_fx<MM, SW, CG>;
     static std::atomic<size_t> configured[64];
     int dev = 0;
@@ -927,13 +891,13 @@ cudaError_t launch_units_fx_inst(const CUtensorMap& map, const UnitsParams& p, i
         if (e != cudaSuccess) return e;
         configured[dev & 63].store(smem, std::memory_order_relaxed);
     }
-    return launch_pdl(kfn, dim3((unsigned)grid), dim3(UW * 32), smem, st, 1, map, p);
+    return launch_pdl(pdl, kfn, dim3((unsigned)grid), dim3(UW * 32), smem, st, 1, map, p);
 }
 
 template <int MM, bool SW>
-cudaError_t launch_units_fx_cg(int cg, const CUtensorMap& map, const UnitsParams& p, int grid, size_t smem, cudaStream_t st) {
-    return cg == 4 ? launch_units_fx_inst<MM, SW, 4>(map, p, grid, smem, st)
-                   : launch_units_fx_inst<MM, SW, 2>(map, p, grid, smem, st);
+cudaError_t launch_units_fx_cg(bool pdl, int cg, const CUtensorMap& map, const UnitsParams& p, int grid, size_t smem, cudaStream_t st) {
+    return cg == 4 ? launch_units_fx_inst<MM, SW, 4>(pdl, map, p, grid, smem, st)
+                   : launch_units_fx_inst<MM, SW, 2>(pdl, map, p, grid, smem, st);
 }
 
 template <int MT, bool SW, bool M1>
@@ -1052,12 +1016,13 @@ LuxBackendError launch_qgemv_i4_units(Context* ctx, const QArgs& a) {
         const uint64_t strides[2] = {(uint64_t)a.K / 2, 128};
         const uint32_t box[3] = {128, 16, (uint32_t)cg / 2};
         if (!encode_tensor_map_u8(&map, 3, a.w, dims, strides, box, true)) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+        const bool pdl = pdl_allowed(ctx, a.weights_volatile);
         if (a.M == 1)
-            e = a.swiglu ? launch_units_fx_cg<1, true>(cg, map, p, grid, smem, ctx->stream)
-                         : launch_units_fx_cg<1, false>(cg, map, p, grid, smem, ctx->stream);
+            e = a.swiglu ? launch_units_fx_cg<1, true>(pdl, cg, map, p, grid, smem, ctx->stream)
+                         : launch_units_fx_cg<1, false>(pdl, cg, map, p, grid, smem, ctx->stream);
         else
-            e = a.swiglu ? launch_units_fx_cg<2, true>(cg, map, p, grid, smem, ctx->stream)
-                         : launch_units_fx_cg<2, false>(cg, map, p, grid, smem, ctx->stream);
+            e = a.swiglu ? launch_units_fx_cg<2, true>(pdl, cg, map, p, grid, smem, ctx->stream)
+                         : launch_units_fx_cg<2, false>(pdl, cg, map, p, grid, smem, ctx->stream);
     } else if (a.M == 1) {
         e = a.swiglu ? launch_units_cg<1, true, true>(cg, p, grid, smem, ctx->stream)
                      : launch_units_cg<1, false, true>(cg, p, grid, smem, ctx->stream);
@@ -1072,13 +1037,10 @@ LuxBackendError launch_qgemv_i4_units(Context* ctx, const QArgs& a) {
     return map_cuda(e, "lux_qgemv_i4_g128_units");
 }
 
-#ifdef LUX_STREAM_TRACE
-extern "C" __attribute__((visibility("default"))) int lux_cuda_debug_units_trace(unsigned long long* out, int n) {
-    return (int)cudaMemcpyFromSymbol(out, g_units_trace, sizeof(unsigned long long) * (size_t)n);
-}
-#endif
 
 const void* kernel_addr_qgemv_i4_units() { return (const void*)lux_qgemv_i4_g128_units<1, false, false, 4>; }
 const void* kernel_addr_qgemv_i4_units_fx() { return (const void*)lux_qgemv_i4_g128_units_fx<1, false, 4>; }
+const void* kernel_addr_qgemv_i4_units_fx_swiglu() { return (const void*)lux_qgemv_i4_g128_units_fx<1, true, 4>; }
+const void* kernel_addr_qgemv_i4_units_fx_batch2() { return (const void*)lux_qgemv_i4_g128_units_fx<2, false, 4>; }
 
 }  // namespace luxcuda

@@ -55,6 +55,7 @@ LuxBackendError check_desc(const LuxQMatmulDesc* d, bool has_zeros, bool need_x,
     a.M = (int)d->M; a.N = (int)d->N; a.K = (int)d->K; a.G = (int)(d->K / d->group_size);
     a.x_dtype = (int)d->x_dtype; a.scale_dtype = (int)d->scale_dtype; a.y_dtype = (int)d->y_dtype;
     a.swiglu = swiglu;
+    a.weights_volatile = (d->flags & LUX_QMATMUL_FLAG_WEIGHTS_VOLATILE) != 0;
     return LUX_BACKEND_OK;
 }
 
@@ -67,7 +68,8 @@ LuxBackendError bind_weights(Checked& c, Buffer* w, Buffer* scales, Buffer* zero
     const size_t z_bytes = (size_t)a.N * ((a.G + 1) / 2);
     if (w->size < w_bytes || scales->size < s_bytes) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
     if (zeros && zeros->size < z_bytes) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
-    if (!aligned16(w->ptr) || !aligned16(scales->ptr)) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    // several kernels fetch rows of all three tables with 16-byte bulk copies
+    if (!aligned16(w->ptr) || !aligned16(scales->ptr) || (zeros && !aligned16(zeros->ptr))) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
     a.w = (const uint8_t*)w->ptr;
     a.scales = scales->ptr;
     a.zeros = zeros ? (const uint8_t*)zeros->ptr : nullptr;
@@ -240,6 +242,7 @@ LuxBackendError lux_cuda_qdequant(LuxBackendContext* context, const LuxQMatmulDe
     cudaSetDevice(ctx->device);
     e = launch_qdequant(ctx, c.a, c.bits);
     if (e != LUX_BACKEND_OK) return e;
+    ctx->writer_pending = true;          // cleared by the wait in finish_op unless NO_SYNC
     return finish_op(ctx, c.no_sync, "lux_cuda_qdequant");
 }
 
@@ -263,6 +266,7 @@ LuxBackendError lux_cuda_qunpack(LuxBackendContext* context, const LuxQMatmulDes
     cudaSetDevice(ctx->device);
     e = launch_qunpack(ctx, a, c.bits);
     if (e != LUX_BACKEND_OK) return e;
+    ctx->writer_pending = true;          // cleared by the wait in finish_op unless NO_SYNC
     return finish_op(ctx, c.no_sync, "lux_cuda_qunpack");
 }
 
