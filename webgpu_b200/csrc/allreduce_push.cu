@@ -1,33 +1,43 @@
-// lux_peer_allreduce_push -- one-node, one-shot all-reduce (sum) of a small 16-bit tensor over
-// peer memory, for the tensor-parallel FFN's partial outputs (16 KB at batch 1): the payload is
-// far below the size where a ring or tree pays, and latency is everything.
+// lux_peer_allreduce_push -- one-node, one-shot all-reduce (sum) of a 16-bit tensor over peer
+// memory, for the tensor-parallel FFN's partial outputs (16 KB at batch 1, 4 MB at batch 256):
+// at these sizes latency, not link bandwidth, is what a ring or a tree would lose.
 //
 // Every rank owns a WINDOW in its own HBM that its peers can write (CUDA IPC mapping, or plain
 // peer pointers inside one process):
 //
 //     [2 parities][world source ranks][slot: one 8-byte word {2 elements, epoch} per 2 elements]
 //
-// One kernel per call, one CTA:
-//   1. push   every thread packs its share of the local tensor into 8-byte words
-//             {two 16-bit elements, epoch} and stores them (two words per 16-byte store) into
-//             slot [parity][my rank] of EVERY rank's window, its own included.  An aligned 8-byte
-//             store arrives whole, so a word whose epoch field matches carries valid data: no
-//             fence and no separate "done" flag are needed (the scheme of NCCL's LL protocol).
-//             Plain stores only -- no loads from peer memory, no TMA, no multicast;
-//   2. reduce every thread polls the words it needs in its OWN window (L1 bypassed) until their
-//             epoch field matches, sums the source ranks in rank order in f32 and writes the local
-//             tensor, so all ranks hold bit-identical results.  Every poll is bounded; if one
-//             gives up the kernel leaves the tensor untouched and sets the context's status word
-//             (the host then reports DEVICE_LOST), nothing else happens.
-// The epoch counter lives in device memory and is advanced by the kernel itself, so the call
-// can be captured in a CUDA graph and replayed.  Two parities suffice: a rank can be at most
-// one epoch ahead of a peer, because finishing epoch n needs every peer's epoch-n words, which
-// a peer stores only after it has finished reading epoch n-1.
+// One kernel per call, as many CTAs as the tensor has 4 KB pieces (at most one per SM); a thread
+// owns 16-byte pieces of the tensor from start to finish:
+//   1. push   it packs a piece into 8-byte words {two 16-bit elements, epoch} and stores them (two
+//             words per 16-byte store) into slot [parity][my rank] of EVERY rank's window, its own
+//             included.  An aligned 8-byte store arrives whole, so a word whose epoch field matches
+//             carries valid data: no fence and no separate "done" flag are needed (the scheme of
+//             NCCL's LL protocol).  Plain stores only -- no loads from peer memory, no TMA, no
+//             multicast;
+//   2. reduce it polls the same piece of every source rank in its OWN window (all loads of a round
+//             issued before any is tested, L1 bypassed) until every epoch field matches, sums the
+//             source ranks in rank order in f32 and writes the piece of the local tensor, so all
+//             ranks hold bit-identical results.
+// The wait is bounded by a deadline on the GPU's nanosecond timer for the whole call (1 s by
+// default).  If it passes, the kernel sets the context's status word (the host then reports
+// DEVICE_LOST) and marks the communicator FAILED in device memory: pieces whose words never came
+// keep their old contents, and every later call on that communicator returns at once with the same
+// status instead of waiting again -- after a failure the ranks' epochs may differ, so the
+// communicator must be destroyed and created anew on every rank.
+// The control words {epoch, CTAs done, failed, CTAs done (fused producer)} live in device memory;
+// the last CTA to finish advances the epoch, so the call can be captured in a CUDA graph and
+// replayed.  Two parities suffice: a rank can be at most one epoch ahead of a peer, because
+// finishing epoch n needs every peer's epoch-n words, which a peer stores only after it has
+// finished reading epoch n-1.
+// The kernel is launched with the programmatic-launch attribute: its CTAs are resident when the
+// kernel that produces the tensor finishes, and wait for it with griddepcontrol.wait.
 //
 // The reference has no multi-device path (no NCCL / MPI call site in luxcpp/webgpu); this is
 // the push all-reduce its tensor-parallel replacement needs.
 #include "common.cuh"
 
+#include <algorithm>
 #include <cstring>
 
 namespace luxcuda {
@@ -35,7 +45,7 @@ namespace luxcuda {
 namespace {
 
 constexpr int MAX_WORLD = 8;
-constexpr int AR_THREADS = 1024;
+constexpr int AR_THREADS = 256;
 
 struct PeerComm {
     int device = 0;
@@ -44,19 +54,19 @@ struct PeerComm {
     unsigned char* window = nullptr;          // this rank's window (owned)
     unsigned char* peer[MAX_WORLD] = {};      // every rank's window as seen from here (peer[rank] == window)
     bool opened[MAX_WORLD] = {};              // mapped with cudaIpcOpenMemHandle (to be closed)
-    uint32_t* epoch = nullptr;                // device counter (owned)
+    uint32_t* ctl = nullptr;                  // device control words (owned): see PEER_CTL_* in common.cuh
     bool connected = false;
 };
 
 struct PushParams {
     unsigned char* peer[MAX_WORLD];
     void* buf;
-    uint32_t* epoch;
+    uint32_t* ctl;
     uint32_t* status;
     unsigned long long max_bytes;
     unsigned long long count;                 // 16-bit elements
+    unsigned long long wait_ns;               // deadline of the whole call
     int rank, world;
-    unsigned int wait_limit;
 };
 
 // a slot holds max_bytes of payload as 8-byte words {4 bytes of payload, 4 bytes of epoch}
@@ -101,66 +111,73 @@ __device__ __forceinline__ uint4 load_words(const uint4* src) {
 }
 
 // count is a multiple of 8 (16-byte pieces of the tensor); buf is 16-byte aligned
-// PUSH = false: the producer kernel's epilogue has already stored this rank's words (same epoch)
-template <bool BF16, bool PUSH>
-__global__ void __launch_bounds__(AR_THREADS, 1) lux_peer_allreduce_push(const PushParams p) {
+template <bool BF16>
+__global__ void __launch_bounds__(AR_THREADS) lux_peer_allreduce_push(const PushParams p) {
     __shared__ int s_failed;
     const int tid = threadIdx.x;
     if (tid == 0) s_failed = 0;
-    const uint32_t epoch = *p.epoch + 1u;                         // the same value for every thread
-    const int parity = (int)(epoch & 1u);
-    const size_t pieces = (size_t)p.count / 8;                    // 16-byte pieces of the tensor
-    const uint4* src = reinterpret_cast<const uint4*>(p.buf);
-
-    // 1. push: piece i becomes four words = two 16-byte stores, into my slot of every window
-    for (size_t i = tid; PUSH && i < pieces; i += AR_THREADS) {
-        const uint4 v = src[i];
-        const uint4 lo = make_uint4(v.x, epoch, v.y, epoch), hi = make_uint4(v.z, epoch, v.w, epoch);
-#pragma unroll 1
-        for (int r = 0; r < p.world; r++) {
-            uint4* dst = reinterpret_cast<uint4*>(slot_ptr(p.peer[r], p.world, p.max_bytes, parity, p.rank)) + 2 * i;
-            store_words(dst, lo);
-            store_words(dst + 1, hi);
-        }
-    }
-    __syncthreads();                                              // s_failed is initialised
-    // 2a. wait (bounded) until every word this thread will read carries this epoch
-    unsigned char* mine = p.peer[p.rank];
-    for (size_t i = tid; i < pieces; i += AR_THREADS) {
-#pragma unroll 1
-        for (int r = 0; r < p.world; r++) {
-            const uint4* w = reinterpret_cast<const uint4*>(slot_ptr(mine, p.world, p.max_bytes, parity, r)) + 2 * i;
-            bool ok = false;
-            for (unsigned int it = 0; it < p.wait_limit; ++it) {
-                const uint4 lo = load_words(w), hi = load_words(w + 1);
-                if (lo.y == epoch && lo.w == epoch && hi.y == epoch && hi.w == epoch) { ok = true; break; }
-                if (*(volatile int*)&s_failed) break;
-                __nanosleep(20);
-            }
-            if (!ok) { atomicExch(&s_failed, 1); break; }
-        }
-        if (*(volatile int*)&s_failed) break;
-    }
-    __syncthreads();
-    if (s_failed) {
-        // a peer never arrived: report it and leave the tensor as it is (the epoch is not
-        // advanced, so the next call starts from the same state)
-        if (tid == 0 && p.status) atomicOr(p.status, 0x7C050005u);
+    pdl_launch_dependents();
+    pdl_wait();                                                   // the producer of buf has finished
+    const uint32_t epoch = peer_ctl_load(p.ctl + PEER_CTL_EPOCH) + 1u;   // the same value in every CTA
+    if (peer_ctl_load(p.ctl + PEER_CTL_FAILED)) {
+        // an earlier call gave up: the ranks' epochs may differ, nothing can be trusted any more
+        if (tid == 0 && blockIdx.x == 0 && p.status) atomicOr(p.status, 0x7C050005u);
         return;
     }
-    // 2b. everything is here: sum the source ranks in rank order
-    for (size_t i = tid; i < pieces; i += AR_THREADS) {
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll 1
-        for (int r = 0; r < p.world; r++) {
-            const uint4* w = reinterpret_cast<const uint4*>(slot_ptr(mine, p.world, p.max_bytes, parity, r)) + 2 * i;
-            const uint4 lo = load_words(w), hi = load_words(w + 1);
-            const uint32_t d[4] = {lo.x, lo.z, hi.x, hi.z};
+    __syncthreads();                                              // s_failed is initialised
+    const int parity = (int)(epoch & 1u);
+    const size_t pieces = (size_t)p.count / 8;                    // 16-byte pieces of the tensor
+    const size_t stride = (size_t)gridDim.x * AR_THREADS;
+    const size_t first = (size_t)blockIdx.x * AR_THREADS + tid;
+    const uint4* src = reinterpret_cast<const uint4*>(p.buf);
+    unsigned char* mine = p.peer[p.rank];
+    const unsigned long long t0 = peer_timer_ns();
+
+    // 1. push: piece i becomes four words = two 16-byte stores, into my slot of every window
+    for (size_t i = first; i < pieces; i += stride) {
+        const uint4 v = src[i];
+        const uint4 lo = make_uint4(v.x, epoch, v.y, epoch), hi = make_uint4(v.z, epoch, v.w, epoch);
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const float2 f = widen2<BF16>(d[j]);
-                acc[2 * j] += f.x;
-                acc[2 * j + 1] += f.y;
+        for (int r = 0; r < MAX_WORLD; r++) {
+            if (r < p.world) {
+                uint4* dst = reinterpret_cast<uint4*>(slot_ptr(p.peer[r], p.world, p.max_bytes, parity, p.rank)) + 2 * i;
+                store_words(dst, lo);
+                store_words(dst + 1, hi);
+            }
+        }
+    }
+    // 2. reduce: every source rank's words of a piece, all requested before any is tested
+    bool failed = false;
+    for (size_t i = first; i < pieces && !failed; i += stride) {
+        uint4 lo[MAX_WORLD], hi[MAX_WORLD];
+        for (uint32_t it = 1;; ++it) {
+            bool all = true;
+#pragma unroll
+            for (int r = 0; r < MAX_WORLD; r++) {
+                if (r < p.world) {
+                    const uint4* w = reinterpret_cast<const uint4*>(slot_ptr(mine, p.world, p.max_bytes, parity, r)) + 2 * i;
+                    lo[r] = load_words(w);
+                    hi[r] = load_words(w + 1);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < MAX_WORLD; r++)
+                if (r < p.world) all = all && lo[r].y == epoch && lo[r].w == epoch && hi[r].y == epoch && hi[r].w == epoch;
+            if (all) break;
+            if ((it & 15u) == 0u && (*(volatile int*)&s_failed || peer_timer_ns() - t0 > p.wait_ns)) { failed = true; break; }
+        }
+        if (failed) break;
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int r = 0; r < MAX_WORLD; r++) {
+            if (r < p.world) {
+                const uint32_t d[4] = {lo[r].x, lo[r].z, hi[r].x, hi[r].z};
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float2 f = widen2<BF16>(d[j]);
+                    acc[2 * j] += f.x;
+                    acc[2 * j + 1] += f.y;
+                }
             }
         }
         uint4 o;
@@ -170,21 +187,29 @@ __global__ void __launch_bounds__(AR_THREADS, 1) lux_peer_allreduce_push(const P
         o.w = narrow2<BF16>(acc[6], acc[7]);
         reinterpret_cast<uint4*>(p.buf)[i] = o;
     }
-    if (tid == 0) *p.epoch = epoch;
+    if (failed) atomicExch(&s_failed, 1);
+    __syncthreads();
+    if (tid == 0) peer_ctl_finish(p.ctl, PEER_CTL_DONE, gridDim.x, epoch, s_failed != 0, p.status);
 }
 
 PeerComm* as_comm(LuxPeerComm* c) { return reinterpret_cast<PeerComm*>(c); }
 
 }  // namespace
 
-const void* kernel_addr_peer_allreduce_push() { return (const void*)lux_peer_allreduce_push<false, true>; }
+const void* kernel_addr_peer_allreduce_push() { return (const void*)lux_peer_allreduce_push<false>; }
+
+unsigned long long peer_wait_ns() {
+    // peer_wait_limit is given in microseconds; the default bounds a whole call to one second
+    return g_tune.peer_wait_limit > 0 ? (unsigned long long)g_tune.peer_wait_limit * 1000ull : 1000000000ull;
+}
 
 bool peer_comm_push_target(LuxPeerComm* comm, size_t count, int device, PushTarget* out) {
     PeerComm* c = reinterpret_cast<PeerComm*>(comm);
     if (!c || !out || c->world < 2 || !c->connected || c->device != device) return false;
     if (count == 0 || count % 8 || count * 2 > c->max_bytes) return false;
     for (int r = 0; r < MAX_WORLD; r++) out->peer[r] = r < c->world ? c->peer[r] : nullptr;
-    out->epoch = c->epoch;
+    out->ctl = c->ctl;
+    out->wait_ns = peer_wait_ns();
     out->max_bytes = c->max_bytes;
     out->rank = c->rank;
     out->world = c->world;
@@ -192,7 +217,7 @@ bool peer_comm_push_target(LuxPeerComm* comm, size_t count, int device, PushTarg
 }
 
 LuxBackendError peer_allreduce_launch(Context* ctx, LuxPeerComm* comm, void* buf, size_t buf_bytes, size_t count,
-                                      int dtype, bool push) {
+                                      int dtype) {
     PeerComm* c = reinterpret_cast<PeerComm*>(comm);
     if (!ctx || !c || !buf || count == 0) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
     if (dtype != LUX_QDTYPE_F16 && dtype != LUX_QDTYPE_BF16) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
@@ -203,21 +228,21 @@ LuxBackendError peer_allreduce_launch(Context* ctx, LuxPeerComm* comm, void* buf
     PushParams p{};
     for (int r = 0; r < c->world; r++) p.peer[r] = c->peer[r];
     p.buf = buf;
-    p.epoch = c->epoch;
+    p.ctl = c->ctl;
     p.status = ctx->d_status;
     p.max_bytes = c->max_bytes;
     p.count = count;
     p.rank = c->rank;
     p.world = c->world;
-    p.wait_limit = g_tune.peer_wait_limit > 0 ? (unsigned)g_tune.peer_wait_limit : (1u << 22);   // ~0.2 s per word
-    const bool bf16 = dtype == LUX_QDTYPE_BF16;
-    if (push) {
-        if (bf16) lux_peer_allreduce_push<true, true><<<1, AR_THREADS, 0, ctx->stream>>>(p);
-        else lux_peer_allreduce_push<false, true><<<1, AR_THREADS, 0, ctx->stream>>>(p);
-    } else {
-        if (bf16) lux_peer_allreduce_push<true, false><<<1, AR_THREADS, 0, ctx->stream>>>(p);
-        else lux_peer_allreduce_push<false, false><<<1, AR_THREADS, 0, ctx->stream>>>(p);
-    }
+    p.wait_ns = peer_wait_ns();
+    // one CTA per 4 KB of the tensor, at most one per SM: 16 KB (batch 1) takes 4 CTAs, 4 MB all SMs
+    const size_t pieces = count / 8;
+    const unsigned grid = (unsigned)std::min<size_t>((size_t)ctx->sm_count, (pieces + AR_THREADS - 1) / AR_THREADS);
+    const bool pdl = g_tune.pdl != 2;          // reads no weight operand: the pending-writer mark does not concern it
+    const cudaError_t le = dtype == LUX_QDTYPE_BF16
+        ? launch_pdl(pdl, lux_peer_allreduce_push<true>, dim3(grid), dim3(AR_THREADS), 0, ctx->stream, 1, p)
+        : launch_pdl(pdl, lux_peer_allreduce_push<false>, dim3(grid), dim3(AR_THREADS), 0, ctx->stream, 1, p);
+    if (le != cudaSuccess) return map_cuda(le, "lux_peer_allreduce_push");
     count_launch("lux_peer_allreduce_push");
     return map_cuda(cudaGetLastError(), "lux_peer_allreduce_push");
 }
@@ -243,14 +268,14 @@ LuxBackendError lux_cuda_peer_comm_create(LuxBackendContext* context, int rank, 
     c->world = world;
     c->max_bytes = max_bytes;
     const size_t bytes = window_alloc_bytes(world, max_bytes);
-    if (cudaMalloc(&c->window, bytes) != cudaSuccess || cudaMalloc(&c->epoch, sizeof(uint32_t)) != cudaSuccess) {
+    if (cudaMalloc(&c->window, bytes) != cudaSuccess || cudaMalloc(&c->ctl, PEER_CTL_WORDS * sizeof(uint32_t)) != cudaSuccess) {
         if (c->window) cudaFree(c->window);
         delete c;
         (void)cudaGetLastError();
         return LUX_BACKEND_ERROR_OUT_OF_MEMORY;
     }
     cudaMemset(c->window, 0, bytes);
-    cudaMemset(c->epoch, 0, sizeof(uint32_t));
+    cudaMemset(c->ctl, 0, PEER_CTL_WORDS * sizeof(uint32_t));
     const WindowTag tag{TAG_MAGIC, (uint32_t)rank, (uint32_t)world, (uint32_t)max_bytes};
     cudaMemcpy(c->window + tag_offset(world, max_bytes), &tag, sizeof tag, cudaMemcpyHostToDevice);
     cudaDeviceSynchronize();
@@ -325,7 +350,7 @@ LuxBackendError lux_cuda_peer_allreduce(LuxBackendContext* context, LuxPeerComm*
     if (!ctx || !comm || !b || !b->ptr) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
     cudaSetDevice(ctx->device);
     std::lock_guard<std::mutex> lock(ctx->mu);
-    LuxBackendError e = peer_allreduce_launch(ctx, comm, b->ptr, b->size, count, (int)dtype, true);
+    LuxBackendError e = peer_allreduce_launch(ctx, comm, b->ptr, b->size, count, (int)dtype);
     if (e != LUX_BACKEND_OK) return e;
     return finish_op(ctx, (flags & LUX_QMATMUL_FLAG_NO_SYNC) != 0, "lux_cuda_peer_allreduce");
 }
@@ -338,7 +363,7 @@ void lux_cuda_peer_comm_destroy(LuxPeerComm* comm) {
     for (int r = 0; r < c->world; r++)
         if (c->opened[r] && c->peer[r]) cudaIpcCloseMemHandle(c->peer[r]);
     if (c->window) cudaFree(c->window);
-    if (c->epoch) cudaFree(c->epoch);
+    if (c->ctl) cudaFree(c->ctl);
     (void)cudaGetLastError();
     delete c;
 }

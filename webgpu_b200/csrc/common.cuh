@@ -170,10 +170,44 @@ inline cudaError_t launch_pdl(bool allow, void (*kfn)(KArgs...), dim3 grid, dim3
 // every rank's window, this rank's number, the communicator's epoch counter.  world <= 1: no push.
 struct PushTarget {
     unsigned char* peer[8];
-    uint32_t* epoch;
+    uint32_t* ctl;                  // the communicator's control words in device memory (PEER_CTL_*)
     unsigned long long max_bytes;
+    unsigned long long wait_ns;     // deadline of a wait for the peers' words
     int rank, world;
 };
+// control words of a push communicator
+enum { PEER_CTL_EPOCH = 0,          // number of completed reductions
+       PEER_CTL_DONE = 1,           // CTAs of the all-reduce kernel that have finished the current one
+       PEER_CTL_FAILED = 2,         // a wait gave up: sticky, every later call returns at once
+       PEER_CTL_DONE_FUSED = 3,     // the same count for a producer kernel that reduces in its epilogue
+       PEER_CTL_WORDS = 4 };
+#ifdef __CUDACC__
+__device__ __forceinline__ uint32_t peer_ctl_load(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned long long peer_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// One thread per CTA, after the CTA's part of a reduction: records a failure, and the last CTA of
+// the grid to arrive advances the epoch (only while the communicator is intact) and re-arms the count.
+__device__ __forceinline__ void peer_ctl_finish(uint32_t* ctl, int done_word, unsigned ctas, uint32_t epoch, bool failed,
+                                                uint32_t* status) {
+    if (failed) {
+        atomicExch(ctl + PEER_CTL_FAILED, 1u);
+        if (status) atomicOr(status, 0x7C050005u);
+    }
+    __threadfence();
+    if (atomicAdd(ctl + done_word, 1u) == ctas - 1u) {
+        atomicExch(ctl + done_word, 0u);
+        if (peer_ctl_load(ctl + PEER_CTL_FAILED) == 0u) atomicExch(ctl + PEER_CTL_EPOCH, epoch);
+        __threadfence();
+    }
+}
+#endif
 
 struct QArgs {
     int M, N, K, G;              // G = K / group
@@ -202,7 +236,7 @@ inline bool pdl_allowed(Context* ctx, bool weights_volatile) {
 // 16-bit elements), and the all-reduce launch with or without its own push phase
 bool peer_comm_push_target(LuxPeerComm* comm, size_t count, int device, PushTarget* out);
 LuxBackendError peer_allreduce_launch(Context* ctx, LuxPeerComm* comm, void* buf, size_t buf_bytes, size_t count,
-                                      int dtype, bool push);
+                                      int dtype);
 
 LuxBackendError launch_qgemv_i8(Context* ctx, const QArgs& a);
 LuxBackendError launch_qgemv_i8_units(Context* ctx, const QArgs& a);    // NOT_SUPPORTED if the shape does not fit

@@ -817,20 +817,30 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
         // A bounded wait gave up: report it and give copies still in flight time to land in
         // this CTA's shared memory before it is released.
         if (tid == 0 && p.status) atomicOr(p.status, 0x7C050003u);
+        if (tid == 0 && !SWIGLU && p.push.world > 1) atomicExch(p.push.ctl + PEER_CTL_FAILED, 1u);   // this rank pushes nothing
         for (int i = 0; i < 64; i++) __nanosleep(1000);
         __syncthreads();
         return;
     }
     if (!SWIGLU && p.push.world > 1) {
-        // Fused collective: instead of writing y, every pair of outputs goes straight into slot
-        // [parity][my rank] of EVERY rank's all-reduce window as one self-validating 8-byte word
-        // {two f16, epoch} (plain stores to peer memory; allreduce_push.cu waits for them and sums).
-        // The epoch is the communicator's counter + 1: the all-reduce kernel that follows on this
-        // stream computes the same value and advances the counter.
-        const uint32_t epoch = *p.push.epoch + 1u;
-        const size_t slot = ((size_t)(epoch & 1u) * p.push.world + p.push.rank) * (2 * p.push.max_bytes);
+        // Fused compute + collective: this kernel IS the all-reduce.  Every pair of outputs goes
+        // straight from the tensor-core partial sums into slot [parity][my rank] of EVERY rank's
+        // window as one self-validating 8-byte word {two f16, epoch} (plain stores to peer memory);
+        // the same thread then waits for the same word of every source rank in its OWN window, adds
+        // them in rank order in f32 (its own contribution as the f16 pair it pushed, so that all
+        // ranks hold identical bits) and writes y.  No second kernel, no launch boundary: a CTA's
+        // peers have pushed these rows by the time its own tiles are done, give or take the skew
+        // between the GPUs.  The wait is bounded by a deadline (allreduce_push.cu describes the
+        // protocol, the failure rule and the control words); the last CTA advances the epoch.
+        const uint32_t epoch = peer_ctl_load(p.push.ctl + PEER_CTL_EPOCH) + 1u;
+        bool failed = peer_ctl_load(p.push.ctl + PEER_CTL_FAILED) != 0u;
+        const size_t slot_sz = 2 * p.push.max_bytes;
+        const size_t par_off = (size_t)(epoch & 1u) * p.push.world * slot_sz;
+        const size_t my_slot = par_off + (size_t)p.push.rank * slot_sz;
+        const unsigned char* mine = p.push.peer[p.push.rank] + par_off;
         const int npairs = ntiles * 8 * MM;
-        for (int o = tid; o < npairs; o += UW * 32) {
+        const unsigned long long t0 = peer_timer_ns();
+        for (int o = tid; o < npairs && !failed; o += UW * 32) {
             const int m = o % MM, r2 = (o / MM) & 7, tl = o / (8 * MM);
             const float* v0 = part + ((size_t)(tl * p.U) * 16 + 2 * r2) * MM + m;
             float s0 = 0.0f, s1 = 0.0f;
@@ -840,13 +850,44 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
             }
             const __half2 h2 = __floats2half2_rn(s0, s1);
             const uint32_t pk = *reinterpret_cast<const uint32_t*>(&h2);
-            const size_t word = ((size_t)m * p.Nout + (size_t)(tile_lo + tl) * 16 + 2 * r2) >> 1;
-#pragma unroll 1
-            for (int r = 0; r < p.push.world; r++) {
-                uint2* dst = reinterpret_cast<uint2*>(p.push.peer[r] + slot) + word;
-                asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(pk), "r"(epoch) : "memory");
+            const size_t col = (size_t)(tile_lo + tl) * 16 + 2 * r2;
+            const size_t word = ((size_t)m * p.Nout + col) >> 1;
+#pragma unroll
+            for (int r = 0; r < 8; r++) {
+                if (r < p.push.world) {
+                    uint2* dst = reinterpret_cast<uint2*>(p.push.peer[r] + my_slot) + word;
+                    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(pk), "r"(epoch) : "memory");
+                }
             }
+            uint32_t got[8];
+            for (uint32_t it = 1;; ++it) {
+                bool all = true;
+#pragma unroll
+                for (int r = 0; r < 8; r++) {
+                    if (r < p.push.world) {
+                        uint32_t ep;
+                        const uint2* src = reinterpret_cast<const uint2*>(mine + (size_t)r * slot_sz) + word;
+                        asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(got[r]), "=r"(ep) : "l"(src) : "memory");
+                        all = all && ep == epoch;
+                    }
+                }
+                if (all) break;
+                if ((it & 15u) == 0u && peer_timer_ns() - t0 > p.push.wait_ns) { failed = true; break; }
+            }
+            if (failed) break;
+            float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll
+            for (int r = 0; r < 8; r++) {
+                if (r < p.push.world) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&got[r]));
+                    a0 += f.x;
+                    a1 += f.y;
+                }
+            }
+            *reinterpret_cast<__half2*>(p.y + (size_t)m * p.Nout + col) = __floats2half2_rn(a0, a1);
         }
+        const int any_failed = __syncthreads_or(failed ? 1 : 0);
+        if (tid == 0) peer_ctl_finish(p.push.ctl, PEER_CTL_DONE_FUSED, gridDim.x, epoch, any_failed != 0, p.status);
         return;
     }
     const int nout = ntiles * 16 * MM;

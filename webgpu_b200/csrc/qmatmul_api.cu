@@ -272,9 +272,9 @@ LuxBackendError lux_cuda_qunpack(LuxBackendContext* context, const LuxQMatmulDes
 
 // The tensor-parallel FFN of one rank: gate_up + SwiGLU, down, and the all-reduce of the partial
 // outputs through the push communicator.  When the down projection runs in the warp-autonomous
-// fixed-point kernel (batch <= 2), its final reduction stores the outputs straight into every
-// rank's window and the second kernel only waits and sums; otherwise down writes y and the
-// all-reduce kernel pushes it.
+// fixed-point kernel (batch <= 2), that kernel is the all-reduce too: its final reduction stores
+// the outputs straight into every rank's window, waits for the peers' and writes the sum (two
+// launches per FFN); otherwise down writes y and the all-reduce kernel follows.
 LuxBackendError lux_cuda_qmlp_tp(LuxBackendContext* context, const LuxQMlpDesc* d, LuxBackendBuffer* x,
                                  LuxBackendBuffer* w_gate_up, LuxBackendBuffer* s_gate_up, LuxBackendBuffer* z_gate_up,
                                  LuxBackendBuffer* w_down, LuxBackendBuffer* s_down, LuxBackendBuffer* z_down,
@@ -319,9 +319,11 @@ LuxBackendError lux_cuda_qmlp_tp(LuxBackendContext* context, const LuxQMlpDesc* 
         e = lux_cuda_qmatmul(context, &dn, h_scratch, w_down, s_down, z_down, y);
         if (e != LUX_BACKEND_OK) return e;
     }
-    cudaSetDevice(ctx->device);
-    e = peer_allreduce_launch(ctx, comm, by->ptr, by->size, count, (int)d->act_dtype, !fused);
-    if (e != LUX_BACKEND_OK) return e;
+    if (!fused) {
+        cudaSetDevice(ctx->device);
+        e = peer_allreduce_launch(ctx, comm, by->ptr, by->size, count, (int)d->act_dtype);
+        if (e != LUX_BACKEND_OK) return e;
+    }
     return finish_op(ctx, (d->flags & LUX_QMATMUL_FLAG_NO_SYNC) != 0, "lux_cuda_qmlp_tp");
 }
 
