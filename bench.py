@@ -148,12 +148,15 @@ class Rig:
         n = max(2, -(-min_bytes // first.weight_bytes))
         return [first] + [self.ctx.upload_layer(layer) for _ in range(n - 1)]
 
-    def time_graph(self, launch, n_variants, steps, warmup, graph_len=None):
+    def time_graph(self, launch, n_variants, steps, warmup, graph_len=None, align=None):
         """Times exactly `steps` launches (launch(i) enqueues one on self.stream) as CUDA-graph
         replays: one graph of all of them up to 240 steps, else graphs of a whole number of
         rotations.  The timed region opens behind a short spin kernel, so that the host's
         submission latency of the first replay is not counted as device time; a synchronize
-        stands on both sides.  Returns (seconds per step, graph)."""
+        stands on both sides.  `align` (multi-GPU) is enqueued behind the spin kernel and before the
+        first event: one more untimed step whose collective brings the ranks' streams to the same
+        point, so that the timed region does not open with one rank waiting for another that is
+        still capturing its graph.  Returns (seconds per step, graph)."""
         torch = self.torch
         if graph_len:
             glen = max(1, min(graph_len, steps))
@@ -180,7 +183,9 @@ class Rig:
             self.stream.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
-            torch.cuda._sleep(200_000)          # ~0.1 ms of spinning: the replays below queue up behind it
+            torch.cuda._sleep(400_000 if align else 200_000)   # 0.1-0.2 ms of spinning: what follows queues up behind it
+            if align is not None:
+                align()
             e0.record(self.stream)
             for _ in range(steps // glen):
                 g.replay()
@@ -455,8 +460,9 @@ def bench_tp(args, peaks):
             if int(flag.item()) != 1:
                 raise RuntimeError(f"rank {rank}: --collective push was asked for but the peer windows could not be "
                                    f"connected on every rank ({why or 'another rank failed'})")
-            collective = ("push all-reduce over peer memory: fused into the down kernel's epilogue (batch <= 2) or "
-                          "lux_peer_allreduce_push (larger batches); f16 partials, f32 sum in rank order")
+            collective = ("push all-reduce over peer memory: the down kernel's epilogue stores into the peers' windows "
+                          "(batch <= 2) and lux_peer_allreduce_push waits and sums; larger batches push from that kernel; "
+                          "f16 partials, f32 sum in rank order")
         else:
             collective = "NCCL all-reduce of f16 partials (torch.distributed)"
     note = f"[bench] rank {rank}/{world}: batch {M}, collective = {collective}"
@@ -475,13 +481,9 @@ def bench_tp(args, peaks):
         return mlps[i % copies].forward(M)
 
     def agree(ok):
-        """True only if `ok` holds on every rank (the capture-or-eager choice must be collective:
-        ranks replaying graphs next to ranks launching eagerly would issue different sequences)."""
-        if world == 1:
-            return bool(ok)
-        f = torch.tensor([1 if ok else 0], device="cuda")
-        dist.all_reduce(f, op=dist.ReduceOp.MIN)
-        return int(f.item()) == 1
+        # the capture-or-eager choice is collective: ranks replaying graphs next to ranks launching
+        # eagerly would issue different sequences of collectives and barriers
+        return tp.all_ranks_agree(ok, device="cuda")
 
     def eager_time(fn):
         with torch.cuda.stream(rig.stream):
@@ -490,6 +492,7 @@ def bench_tp(args, peaks):
             torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda._sleep(200_000)
+            fn(copies - 1)                      # untimed: its collective aligns the ranks
             e0.record(rig.stream)
             for i in range(args.steps):
                 fn(i)
@@ -505,7 +508,7 @@ def bench_tp(args, peaks):
     sampler.start()
     sec = sec_compute = None
     try:
-        sec, _ = rig.time_graph(step, copies, args.steps, args.warmup)
+        sec, _ = rig.time_graph(step, copies, args.steps, args.warmup, align=(lambda: step(copies - 1)) if world > 1 else None)
         captured = True
     except Exception as exc:   # noqa: BLE001
         captured = False
@@ -602,7 +605,6 @@ def bench_tp(args, peaks):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_sec = float(t[0])
 
-    fused = peer is not None and M <= 2
     per_gpu_alg = shard_bytes + M * d["K"] * 2 + 2 * M * (d["I"] // world) * 2 + M * d["H"] * 2
     line = None
     if rank == 0:
@@ -623,7 +625,7 @@ def bench_tp(args, peaks):
                          "us_compute_only": sec_compute * 1e6, "us_with_allreduce": sec * 1e6},
             "e2e": {"value": total_wbytes / e2e_sec / 1e9, "unit": "GB/s", "h2d_bytes_per_step": int(x.nbytes),
                     "d2h_bytes_per_step": int(M * d["H"] * 2), "us_per_step": e2e_sec * 1e6, "path": e2e_path},
-            "gpu_launches": (2 if (fused or world == 1) else 3) * args.steps, "clocks": clocks,
+            "gpu_launches": (2 if world == 1 else 3) * args.steps, "clocks": clocks,
             "parity_rel_l2": parity, "parity_rows": parity_rows, "ranks_identical": ranks_identical,
             "tp1_us_same_box": tp1["us"], "ffn70b_cfg5_tp1": tp1,
             "strong_scaling_efficiency": tp1["us"] / (world * sec * 1e6),

@@ -132,10 +132,12 @@ def test_two_ranks_with_the_peer_played_by_the_host(ctx, backend, count):
         ctx.peer_comm_destroy(comm)
 
 
+@pytest.mark.parametrize("mode,launches", [(0, 3), (1, 2)])
 @pytest.mark.parametrize("M", [1, 2])
-def test_fused_down_plus_allreduce_with_the_peer_played_by_the_host(ctx, backend, M):
-    """lux_cuda_qmlp_tp at batch 1 and 2: the down projection's kernel pushes its outputs, waits
-    for the peer's words and writes the sum itself (two launches per FFN, no all-reduce kernel).
+def test_fused_down_plus_allreduce_with_the_peer_played_by_the_host(ctx, backend, M, mode, launches):
+    """lux_cuda_qmlp_tp at batch 1 and 2.  Default (mode 0): the down projection's kernel pushes its
+    outputs from its epilogue and a reduce-only kernel waits and sums (three launches per FFN).
+    Mode 1: the down kernel also waits for the peer's words and writes the sum (two launches).
     Rank 1's partial output is written into rank 0's window by the host beforehand; the result
     must be f16(f32(f16 partial of rank 0) + f32(partial of rank 1)) within the 16-bit tolerance
     of the oracle, on two calls in a row (two epochs)."""
@@ -146,6 +148,7 @@ def test_fused_down_plus_allreduce_with_the_peer_played_by_the_host(ctx, backend
     comm, _ = ctx.peer_comm_create(0, 2, nbytes)
     fake = ctx.upload(np.zeros(int(backend.lib.lux_cuda_peer_comm_window_bytes(comm)), np.uint8))
     rng = np.random.default_rng(61)
+    backend.tune("tp_fused_push", mode)
     try:
         win = ctx.peer_comm_window(comm)
         ctx.peer_comm_connect_ptrs(comm, [win, fake.device_ptr])
@@ -156,11 +159,12 @@ def test_fused_down_plus_allreduce_with_the_peer_played_by_the_host(ctx, backend
             xb, hb, yb = ctx.upload(x), ctx.alloc(M * I * 2), ctx.alloc(M * H * 2)
             before = backend.launch_count()
             ctx.qmlp_tp(xb, G, D, hb, yb, M, B.F16, comm)
-            assert backend.launch_count() - before == 2, "the all-reduce was not fused into the down kernel"
-            assert backend.last_kernel_name() == "lux_qgemv_i4_g128_units_fx"
+            assert backend.launch_count() - before == launches, "the push was not fused into the down kernel"
+            assert backend.last_kernel_name() == ("lux_qgemv_i4_g128_units_fx" if mode == 1 else "lux_peer_allreduce_push")
             y = yb.to_host(np.float16, (M, H))
             part = orc.mlp(x, gate_up.triple, down.triple, fused=True)
             want = (part.astype(np.float32) + other.astype(np.float32)).astype(np.float16)
             assert orc.rel_l2(y, want) < 5e-3, epoch
     finally:
+        backend.tune("tp_fused_push", 0)
         ctx.peer_comm_destroy(comm)

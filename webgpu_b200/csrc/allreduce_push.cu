@@ -19,7 +19,7 @@
 //             issued before any is tested, L1 bypassed) until every epoch field matches, sums the
 //             source ranks in rank order in f32 and writes the piece of the local tensor, so all
 //             ranks hold bit-identical results.
-// The wait is bounded by a deadline on the GPU's nanosecond timer for the whole call (1 s by
+// The wait is bounded by a deadline on the SM's cycle counter for the whole call (about 1 s by
 // default).  If it passes, the kernel sets the context's status word (the host then reports
 // DEVICE_LOST) and marks the communicator FAILED in device memory: pieces whose words never came
 // keep their old contents, and every later call on that communicator returns at once with the same
@@ -111,7 +111,8 @@ __device__ __forceinline__ uint4 load_words(const uint4* src) {
 }
 
 // count is a multiple of 8 (16-byte pieces of the tensor); buf is 16-byte aligned
-template <bool BF16>
+// PUSH = false: the producer kernel's epilogue has already stored this rank's words (same epoch)
+template <bool BF16, bool PUSH>
 __global__ void __launch_bounds__(AR_THREADS) lux_peer_allreduce_push(const PushParams p) {
     __shared__ int s_failed;
     const int tid = threadIdx.x;
@@ -134,7 +135,7 @@ __global__ void __launch_bounds__(AR_THREADS) lux_peer_allreduce_push(const Push
     const unsigned long long t0 = peer_timer_ns();
 
     // 1. push: piece i becomes four words = two 16-byte stores, into my slot of every window
-    for (size_t i = first; i < pieces; i += stride) {
+    for (size_t i = first; PUSH && i < pieces; i += stride) {
         const uint4 v = src[i];
         const uint4 lo = make_uint4(v.x, epoch, v.y, epoch), hi = make_uint4(v.z, epoch, v.w, epoch);
 #pragma unroll
@@ -196,7 +197,7 @@ PeerComm* as_comm(LuxPeerComm* c) { return reinterpret_cast<PeerComm*>(c); }
 
 }  // namespace
 
-const void* kernel_addr_peer_allreduce_push() { return (const void*)lux_peer_allreduce_push<false>; }
+const void* kernel_addr_peer_allreduce_push() { return (const void*)lux_peer_allreduce_push<false, true>; }
 
 unsigned long long peer_wait_ns() {
     // peer_wait_limit is given in microseconds; the default bounds a whole call to one second
@@ -213,11 +214,12 @@ bool peer_comm_push_target(LuxPeerComm* comm, size_t count, int device, PushTarg
     out->max_bytes = c->max_bytes;
     out->rank = c->rank;
     out->world = c->world;
+    out->reduce_here = 1;
     return true;
 }
 
 LuxBackendError peer_allreduce_launch(Context* ctx, LuxPeerComm* comm, void* buf, size_t buf_bytes, size_t count,
-                                      int dtype) {
+                                      int dtype, bool push) {
     PeerComm* c = reinterpret_cast<PeerComm*>(comm);
     if (!ctx || !c || !buf || count == 0) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
     if (dtype != LUX_QDTYPE_F16 && dtype != LUX_QDTYPE_BF16) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
@@ -239,9 +241,10 @@ LuxBackendError peer_allreduce_launch(Context* ctx, LuxPeerComm* comm, void* buf
     const size_t pieces = count / 8;
     const unsigned grid = (unsigned)std::min<size_t>((size_t)ctx->sm_count, (pieces + AR_THREADS - 1) / AR_THREADS);
     const bool pdl = g_tune.pdl != 2;          // reads no weight operand: the pending-writer mark does not concern it
-    const cudaError_t le = dtype == LUX_QDTYPE_BF16
-        ? launch_pdl(pdl, lux_peer_allreduce_push<true>, dim3(grid), dim3(AR_THREADS), 0, ctx->stream, 1, p)
-        : launch_pdl(pdl, lux_peer_allreduce_push<false>, dim3(grid), dim3(AR_THREADS), 0, ctx->stream, 1, p);
+    const bool bf16 = dtype == LUX_QDTYPE_BF16;
+    auto kfn = push ? (bf16 ? lux_peer_allreduce_push<true, true> : lux_peer_allreduce_push<false, true>)
+                    : (bf16 ? lux_peer_allreduce_push<true, false> : lux_peer_allreduce_push<false, false>);
+    const cudaError_t le = launch_pdl(pdl, kfn, dim3(grid), dim3(AR_THREADS), 0, ctx->stream, 1, p);
     if (le != cudaSuccess) return map_cuda(le, "lux_peer_allreduce_push");
     count_launch("lux_peer_allreduce_push");
     return map_cuda(cudaGetLastError(), "lux_peer_allreduce_push");
@@ -350,7 +353,7 @@ LuxBackendError lux_cuda_peer_allreduce(LuxBackendContext* context, LuxPeerComm*
     if (!ctx || !comm || !b || !b->ptr) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
     cudaSetDevice(ctx->device);
     std::lock_guard<std::mutex> lock(ctx->mu);
-    LuxBackendError e = peer_allreduce_launch(ctx, comm, b->ptr, b->size, count, (int)dtype);
+    LuxBackendError e = peer_allreduce_launch(ctx, comm, b->ptr, b->size, count, (int)dtype, true);
     if (e != LUX_BACKEND_OK) return e;
     return finish_op(ctx, (flags & LUX_QMATMUL_FLAG_NO_SYNC) != 0, "lux_cuda_peer_allreduce");
 }

@@ -91,8 +91,9 @@ struct Tunables {
     int gemv_i4_warps = 0;       // warps per CTA of the int4 skinny kernel
     int gemv_i4_row_tiles = 0;   // 16-row tiles per CTA
     int gemv_i8_warps = 0;
-    int tp_fused_push = 0;       // lux_cuda_qmlp_tp: 0/1 push from the down kernel's epilogue when possible, 2 never
-    int peer_wait_limit = 0;     // push all-reduce: polls (40 ns apart) before a wait gives up (default 2^22)
+    int tp_fused_push = 0;       // lux_cuda_qmlp_tp at batch <= 2: 0 the down kernel pushes and a reduce-only kernel follows;
+                                 // 1 the down kernel pushes, waits and sums itself; 2 separate all-reduce kernel
+    int peer_wait_limit = 0;     // push all-reduce: microseconds before a call's wait for its peers gives up (default 10^6)
     int gemv_i8_kernel = 0;      // 0 auto, 1 lux_qgemv_i8_g32_f32, 2 lux_qgemv_i8_g32_units_fx
     int gemv_i4_kernel = 0;      // 0 auto, 1 lux_qskinny_i4_g128, 2 lux_qgemv_i4_g128_stream, 3 lux_qgemv_i4_g128_units
     int gemv_stream_cg = 0;      // stream kernel: groups per stage / 8 (1, 2 or 4)
@@ -174,6 +175,8 @@ struct PushTarget {
     unsigned long long max_bytes;
     unsigned long long wait_ns;     // deadline of a wait for the peers' words
     int rank, world;
+    int reduce_here;                // 1: the producer kernel also waits for the peers and writes the sum;
+                                    // 0: it only pushes, and a reduce-only all-reduce kernel follows
 };
 // control words of a push communicator
 enum { PEER_CTL_EPOCH = 0,          // number of completed reductions
@@ -187,11 +190,11 @@ __device__ __forceinline__ uint32_t peer_ctl_load(const uint32_t* p) {
     asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ unsigned long long peer_timer_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
+// The waits are bounded on the SM's own cycle counter: a register read, unlike the global
+// nanosecond timer, whose reads from tens of thousands of threads at once queue up for microseconds.
+// The bound is given in nanoseconds and counted at 2 cycles per nanosecond (the SM clock runs at
+// 1.3-2 GHz, so "one second" is 1 to 1.5 s: it is a safety limit, not a measurement).
+__device__ __forceinline__ unsigned long long peer_timer_ns() { return (unsigned long long)clock64() >> 1; }
 // One thread per CTA, after the CTA's part of a reduction: records a failure, and the last CTA of
 // the grid to arrive advances the epoch (only while the communicator is intact) and re-arms the count.
 __device__ __forceinline__ void peer_ctl_finish(uint32_t* ctl, int done_word, unsigned ctas, uint32_t epoch, bool failed,
@@ -236,7 +239,7 @@ inline bool pdl_allowed(Context* ctx, bool weights_volatile) {
 // 16-bit elements), and the all-reduce launch with or without its own push phase
 bool peer_comm_push_target(LuxPeerComm* comm, size_t count, int device, PushTarget* out);
 LuxBackendError peer_allreduce_launch(Context* ctx, LuxPeerComm* comm, void* buf, size_t buf_bytes, size_t count,
-                                      int dtype);
+                                      int dtype, bool push);
 
 LuxBackendError launch_qgemv_i8(Context* ctx, const QArgs& a);
 LuxBackendError launch_qgemv_i8_units(Context* ctx, const QArgs& a);    // NOT_SUPPORTED if the shape does not fit

@@ -859,6 +859,7 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
                     asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(pk), "r"(epoch) : "memory");
                 }
             }
+            if (!p.push.reduce_here) continue;                    // a reduce-only all-reduce kernel follows
             uint32_t got[8];
             for (uint32_t it = 1;; ++it) {
                 bool all = true;
@@ -887,7 +888,7 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
             *reinterpret_cast<__half2*>(p.y + (size_t)m * p.Nout + col) = __floats2half2_rn(a0, a1);
         }
         const int any_failed = __syncthreads_or(failed ? 1 : 0);
-        if (tid == 0) peer_ctl_finish(p.push.ctl, PEER_CTL_DONE_FUSED, gridDim.x, epoch, any_failed != 0, p.status);
+        if (tid == 0 && p.push.reduce_here) peer_ctl_finish(p.push.ctl, PEER_CTL_DONE_FUSED, gridDim.x, epoch, any_failed != 0, p.status);
         return;
     }
     const int nout = ntiles * 16 * MM;

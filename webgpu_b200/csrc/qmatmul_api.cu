@@ -272,9 +272,13 @@ LuxBackendError lux_cuda_qunpack(LuxBackendContext* context, const LuxQMatmulDes
 
 // The tensor-parallel FFN of one rank: gate_up + SwiGLU, down, and the all-reduce of the partial
 // outputs through the push communicator.  When the down projection runs in the warp-autonomous
-// fixed-point kernel (batch <= 2), that kernel is the all-reduce too: its final reduction stores
-// the outputs straight into every rank's window, waits for the peers' and writes the sum (two
-// launches per FFN); otherwise down writes y and the all-reduce kernel follows.
+// fixed-point kernel (batch <= 2), its final reduction stores the outputs straight into every
+// rank's window (fused compute + push) and the all-reduce kernel that follows only waits and sums:
+// its CTAs are resident before `down` ends (programmatic launch), and while they wait for the
+// peers' words the NEXT matmul's CTAs already take the SMs `down` has left and request their
+// weights.  (tp_fused_push = 1 makes the down kernel wait and sum itself, two launches per FFN:
+// measured 1 us slower per step on two GPUs, because the waiting CTAs keep the SMs from the next
+// kernel's prefetch.)  Otherwise down writes y and the all-reduce kernel pushes it.
 LuxBackendError lux_cuda_qmlp_tp(LuxBackendContext* context, const LuxQMlpDesc* d, LuxBackendBuffer* x,
                                  LuxBackendBuffer* w_gate_up, LuxBackendBuffer* s_gate_up, LuxBackendBuffer* z_gate_up,
                                  LuxBackendBuffer* w_down, LuxBackendBuffer* s_down, LuxBackendBuffer* z_down,
@@ -308,6 +312,7 @@ LuxBackendError lux_cuda_qmlp_tp(LuxBackendContext* context, const LuxQMlpDesc* 
             aligned16(by->ptr) && bh->size >= (size_t)d->M * d->I * 2 && by->size >= count * 2) {
             c.a.x = bh->ptr;
             c.a.y = by->ptr;
+            target.reduce_here = g_tune.tp_fused_push == 1 ? 1 : 0;
             c.a.push = &target;
             cudaSetDevice(ctx->device);
             e = launch_qgemv_i4_units(ctx, c.a);
@@ -319,9 +324,9 @@ LuxBackendError lux_cuda_qmlp_tp(LuxBackendContext* context, const LuxQMlpDesc* 
         e = lux_cuda_qmatmul(context, &dn, h_scratch, w_down, s_down, z_down, y);
         if (e != LUX_BACKEND_OK) return e;
     }
-    if (!fused) {
+    if (!fused || !target.reduce_here) {
         cudaSetDevice(ctx->device);
-        e = peer_allreduce_launch(ctx, comm, by->ptr, by->size, count, (int)d->act_dtype);
+        e = peer_allreduce_launch(ctx, comm, by->ptr, by->size, count, (int)d->act_dtype, !fused);
         if (e != LUX_BACKEND_OK) return e;
     }
     return finish_op(ctx, (d->flags & LUX_QMATMUL_FLAG_NO_SYNC) != 0, "lux_cuda_qmlp_tp");

@@ -142,6 +142,21 @@ class TPMlp:
         return out
 
 
+def all_ranks_agree(ok: bool, device=None, group=None) -> bool:
+    """True only if `ok` holds on EVERY rank.  A choice that changes the sequence of collectives a
+    rank issues (replay a captured graph or launch eagerly, use one collective or another) must be
+    made with this, never per rank: ranks that issue different sequences wait for each other
+    forever.  Call it on every rank, outside any try block."""
+    import torch
+    import torch.distributed as dist
+
+    if not dist.is_available() or not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return bool(ok)
+    f = torch.tensor([1 if ok else 0], device=device)
+    dist.all_reduce(f, op=dist.ReduceOp.MIN, group=group)
+    return int(f.item()) == 1
+
+
 def all_reduce_partials(partial: np.ndarray, group=None) -> np.ndarray:
     """Host-side stand-in used by the CPU (gloo) tests of the sharding logic: sums f32
     partials across ranks with torch.distributed."""
