@@ -65,7 +65,10 @@ enum {
      * stream (programmatic dependent launch); with it the launch is ordered after all
      * earlier work like any other.  The library sets it by itself after its own writer
      * calls; a caller whose own stream work produces these operands must set it. */
-    LUX_QMATMUL_FLAG_WEIGHTS_VOLATILE = 1u << 2
+    LUX_QMATMUL_FLAG_WEIGHTS_VOLATILE = 1u << 2,
+    /* lux_cuda_qquantize, asymmetric int4 only: store clamp(round(v / scale) + zp, 0, 15).  NOT the
+     * reference's arithmetic: its shader stores clamp(round(v / scale), 0, 15) (see there). */
+    LUX_QQUANT_FLAG_SHIFTED = 1u << 3
 };
 
 typedef struct LuxQMatmulDesc {
@@ -126,6 +129,26 @@ LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_qdequant(
 LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_qunpack(
     LuxBackendContext* ctx, const LuxQMatmulDesc* desc,
     LuxBackendBuffer* w, LuxBackendBuffer* zeros, LuxBackendBuffer* out_i8);
+
+/* The quantize side: x[N, K] (f32, or f16 / bf16 widened exactly; desc->x_dtype) becomes packed
+ * weights, a scale table and a zero-point table in the layout above, ready for lux_cuda_qmatmul.
+ * Replaces compute_group_scales + quantize_nax_int4_sym / quantize_nax_int4_asym /
+ * quantize_nax_int8_group (kernels/wgsl/gpu/quantized_nax.wgsl:157-232, 236-259, 288-310, 336-362)
+ * in one pass, bit for bit: IEEE division, round-half-to-even, saturating conversion, min / max
+ * seeded with +-1e30, "scale == 0 -> 1", zero-point = clamp(round(-min / scale), 0, 15).
+ *   bits=4 group=128: zeros_out given -> asymmetric, NULL -> symmetric (stored nibble = q + 8);
+ *                     desc->scale_dtype f32 (the reference's GroupScale.scale) or f16 (the scale is
+ *                     rounded to f16 first and the values are quantized with the rounded number)
+ *   bits=8 group=32 : symmetric, f32 scales, zeros_out NULL
+ * The reference's asymmetric int4 shader never shifts by the zero-point before clamping (:303 with
+ * :118): it stores clamp(round(v / scale), 0, 15), so negative inputs become 0 and a round trip
+ * through lux_cuda_qdequant is offset by -zp * scale.  That behaviour is reproduced;
+ * LUX_QQUANT_FLAG_SHIFTED asks for clamp(round(v / scale) + zp, 0, 15) instead.
+ * desc->M and y_dtype are ignored.  The next matmul on this context is ordered behind this call
+ * even with LUX_QMATMUL_FLAG_NO_SYNC (see LUX_QMATMUL_FLAG_WEIGHTS_VOLATILE). */
+LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_qquantize(
+    LuxBackendContext* ctx, const LuxQMatmulDesc* desc, LuxBackendBuffer* x,
+    LuxBackendBuffer* w_out, LuxBackendBuffer* scales_out, LuxBackendBuffer* zeros_out);
 
 /* Llama-style FFN on one GPU or one tensor-parallel shard:
  *   h[M, I] = silu(x.gate^T) * (x.up^T)    W_gate_up [2*I, K]  (gate rows, then up rows)

@@ -60,6 +60,8 @@ def lib() -> C.CDLL:
         L.orc_qmatmul.argtypes = [i32, i32, i32, i32, i32, vp, i32, vp, vp, i32, vp, vp, i32, i32, i32, i32]
         L.orc_swiglu.argtypes = [i32, i32, vp, i32, vp, i32]
         L.orc_num_procs.restype = i32
+        L.orc_compute_group_scales.argtypes = [vp, C.c_size_t, i32, i32, vp]
+        L.orc_quantize.argtypes = [vp, C.c_size_t, i32, i32, vp, vp]
         _lib = L
     return _lib
 
@@ -229,6 +231,70 @@ def tp_mlp(x, shards, group: int = 128, fused: bool = True, w_round: int = F32) 
     if code == BF16:
         return f32_to_bf16(total)
     return total
+
+
+# -- quantize side ---------------------------------------------------------------------
+
+NAX_INT4_SYM, NAX_INT4_ASYM, NAX_INT8_SYM = 0, 1, 2          # quantized_nax.wgsl:31-33
+EXT_INT4_ASYM_SHIFTED = 101                                   # not a reference format (see orc_quantize)
+GROUP_SCALE = np.dtype([("scale", np.float32), ("zero_point", np.int32), ("group_min", np.float32),
+                        ("group_max", np.float32)])          # GroupScale, quantized_nax.wgsl:49-54
+
+
+def group_scales(x: np.ndarray, group: int, fmt: int) -> np.ndarray:
+    """compute_group_scales over the flat array: one GroupScale record per `group` elements."""
+    flat = np.ascontiguousarray(x, np.float32).ravel()
+    out = np.zeros((flat.size + group - 1) // group, GROUP_SCALE)
+    rc = lib().orc_compute_group_scales(_ptr(flat), flat.size, group, fmt, _ptr(out))
+    assert rc == 0, rc
+    return out
+
+
+def quantize_packed(x: np.ndarray, group: int, fmt: int, gs: np.ndarray) -> np.ndarray:
+    """quantize_nax_int4_sym / _asym / quantize_nax_int8_group: the packed u32 words."""
+    flat = np.ascontiguousarray(x, np.float32).ravel()
+    per = 4 if fmt == NAX_INT8_SYM else 8
+    out = np.zeros(flat.size // per, np.uint32)
+    rc = lib().orc_quantize(_ptr(flat), flat.size, group, fmt, _ptr(np.ascontiguousarray(gs)), _ptr(out))
+    assert rc == 0, rc
+    return out
+
+
+def quantize(x: np.ndarray, bits: int, group: int, symmetric: bool, scale_code: int = F32, shifted: bool = False):
+    """The reference's two quantize passes on a row-major [N, K] f32 matrix (K % group == 0), mapped
+    onto the compact layout the matmul kernels read: (w, scales, zeros) with w uint8 [N, K/2] (int4,
+    low nibble first) or int8 [N, K], scales [N, K/group], zeros packed two per byte or None.
+
+    `shifted` selects the non-reference asymmetric variant clamp(round(v / scale) + zp, 0, 15).
+    scale_code F32 is the reference's arithmetic exactly.  F16 (the benchmark configurations' int4
+    scale tables) is an extension: the scale is rounded to f16 first and the values are quantized
+    with the rounded scale, so that quantize and dequantize use the same number."""
+    x = np.ascontiguousarray(x, np.float32)
+    N, K = x.shape
+    assert K % group == 0
+    fmt = NAX_INT8_SYM if bits == 8 else (NAX_INT4_SYM if symmetric else NAX_INT4_ASYM)
+    gs = group_scales(x, group, fmt)
+    if scale_code == F16:
+        s16 = gs["scale"].astype(np.float16)
+        gs = gs.copy()
+        gs["scale"] = s16.astype(np.float32)
+        scales = s16.reshape(N, K // group)
+    else:
+        scales = gs["scale"].reshape(N, K // group).copy()
+    with np.errstate(divide="ignore", invalid="ignore"):
+        words = quantize_packed(x, group, EXT_INT4_ASYM_SHIFTED if (shifted and fmt == NAX_INT4_ASYM) else fmt, gs)
+    if bits == 4:
+        w = words.view(np.uint8).reshape(N, K // 2)
+    else:
+        w = words.view(np.int8).reshape(N, K)
+    zeros = None
+    if fmt == NAX_INT4_ASYM:
+        zp = gs["zero_point"].reshape(N, K // group).astype(np.uint8)
+        G = K // group
+        if G % 2:
+            zp = np.concatenate([zp, np.zeros((N, 1), np.uint8)], axis=1)
+        zeros = (zp[:, 0::2] | (zp[:, 1::2] << 4)).astype(np.uint8)
+    return w, scales, zeros
 
 
 def rel_l2(a: np.ndarray, ref: np.ndarray) -> float:

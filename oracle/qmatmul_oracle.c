@@ -364,3 +364,102 @@ int orc_num_procs(void) {
     return 1;
 #endif
 }
+
+/* ------------------------------------------------------------------------------------
+ * Quantize side: f32 matrix -> group statistics -> packed integers
+ * ---------------------------------------------------------------------------------- */
+
+#define ORC_NAX_INT4_SYM  0     /* quantized_nax.wgsl:31-34 */
+#define ORC_NAX_INT4_ASYM 1
+#define ORC_NAX_INT8_SYM  2
+/* NOT a reference format: asymmetric int4 with the zero-point applied before the clamp,
+ * clamp(round(v / scale) + zp, 0, 15) -- the library's LUX_QQUANT_FLAG_SHIFTED extension. */
+#define ORC_EXT_INT4_ASYM_SHIFTED 101
+
+/* GroupScale, quantized_nax.wgsl:49-54 */
+typedef struct { float scale; int32_t zero_point; float group_min; float group_max; } OrcGroupScale;
+
+/* WGSL i32(f32): truncation toward zero, out-of-range values clamp to the i32 range.  The
+ * result for NaN is indeterminate in WGSL; 0 is used here (UNPINNED choice, reached only by a
+ * group of zeros in the asymmetric format: -0/0). */
+static int32_t wgsl_i32(float v) {
+    if (v != v) return 0;
+    if (v >= 2147483648.0f) return INT32_MAX;
+    if (v <= -2147483648.0f) return INT32_MIN;
+    return (int32_t)v;
+}
+static int32_t clampi(int32_t v, int32_t lo, int32_t hi) { return v < lo ? lo : (v > hi ? hi : v); }
+
+/* compute_group_scales, quantized_nax.wgsl:157-232.  Groups are runs of group_size consecutive
+ * elements of the flat array (:165-166); with a row-major [N, K] matrix and K % group_size == 0
+ * they lie along K inside a row.  min / max start from +-1e30 (:169-170).  round() is
+ * round-half-to-even.  The zero-point is computed BEFORE the "scale == 0 -> 1" guard (:217-218
+ * vs :227), so a constant group divides by zero there; IEEE results are used. */
+int orc_compute_group_scales(const float* in, size_t size, int group_size, int format, OrcGroupScale* out) {
+    if (group_size <= 0 || format < 0 || format > 2) return -1;
+    const size_t groups = (size + (size_t)group_size - 1) / (size_t)group_size;
+    #pragma omp parallel for schedule(static)
+    for (size_t g = 0; g < groups; g++) {
+        const size_t b = g * (size_t)group_size;
+        const size_t e = b + (size_t)group_size < size ? b + (size_t)group_size : size;
+        float mx = -1e30f, mn = 1e30f;
+        for (size_t i = b; i < e; i++) {
+            const float v = in[i];
+            mx = mx > v ? mx : v;       /* max(local_max, val) */
+            mn = mn < v ? mn : v;
+        }
+        float scale;
+        int32_t zp;
+        if (format == ORC_NAX_INT4_SYM || format == ORC_NAX_INT8_SYM) {
+            const float amax = fabsf(mx) > fabsf(mn) ? fabsf(mx) : fabsf(mn);
+            scale = format == ORC_NAX_INT4_SYM ? amax / 7.0f : amax / 127.0f;
+            zp = 0;
+        } else {
+            const float range = mx - mn;
+            scale = range / 15.0f;
+            zp = clampi(wgsl_i32(rintf(-mn / scale)), 0, 15);
+        }
+        if (scale == 0.0f) scale = 1.0f;
+        out[g].scale = scale; out[g].zero_point = zp; out[g].group_min = mn; out[g].group_max = mx;
+    }
+    return 0;
+}
+
+/* quantize_nax_int4_sym (:236-259), quantize_nax_int4_asym (:288-310) with
+ * pack_nax_int4_asym_x8 (:115-122), quantize_nax_int8_group symmetric branch (:336-362) with
+ * pack_nax_int8_x4 (:135-140).  `size` must be a multiple of 8 (int4) or 4 (int8).
+ *
+ * The asymmetric int4 shader is restated AS WRITTEN: q = clamp(i32(round(val / scale)), 0, 15)
+ * - zp (:303), and the pack adds zp back and clamps again (:118), so the stored nibble is
+ * clamp(round(val / scale), 0, 15).  The zero-point never shifts the value before the clamp:
+ * negative inputs are stored as 0 and the round trip through dequantize (nibble - zp) * scale
+ * is offset by -zp * scale.  See tests/test_oracle_quantize.py for the characterisation. */
+int orc_quantize(const float* in, size_t size, int group_size, int format, const OrcGroupScale* gs, uint32_t* out_packed) {
+    if (group_size <= 0 || format < 0 || (format > 2 && format != ORC_EXT_INT4_ASYM_SHIFTED)) return -1;
+    const int per = format == ORC_NAX_INT8_SYM ? 4 : 8;
+    if (size % (size_t)per) return -1;
+    #pragma omp parallel for schedule(static)
+    for (size_t w = 0; w < size / (size_t)per; w++) {
+        const size_t e0 = w * (size_t)per;
+        const OrcGroupScale g = gs[e0 / (size_t)group_size];
+        uint32_t word = 0;
+        for (int i = 0; i < per; i++) {
+            const float scaled = rintf(in[e0 + (size_t)i] / g.scale);
+            if (format == ORC_NAX_INT4_SYM) {
+                const int32_t q = clampi(wgsl_i32(scaled), -8, 7);
+                word |= ((uint32_t)(q + 8) & 0xFu) << (4 * i);
+            } else if (format == ORC_EXT_INT4_ASYM_SHIFTED) {
+                const int32_t q = clampi(clampi(wgsl_i32(scaled), -32, 32) + g.zero_point, 0, 15);
+                word |= ((uint32_t)q & 0xFu) << (4 * i);
+            } else if (format == ORC_NAX_INT4_ASYM) {
+                const int32_t q = clampi(wgsl_i32(scaled), 0, 15) - g.zero_point;
+                word |= ((uint32_t)clampi(q + g.zero_point, 0, 15) & 0xFu) << (4 * i);
+            } else {
+                const int32_t q = clampi(wgsl_i32(scaled), -128, 127);
+                word |= ((uint32_t)q & 0xFFu) << (8 * i);
+            }
+        }
+        out_packed[w] = word;
+    }
+    return 0;
+}

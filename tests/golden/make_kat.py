@@ -113,6 +113,73 @@ def bf16_rne_bits(val):
     return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16) & 0xFFFF
 
 
+def wgsl_i32(v):
+    """i32(f32): toward zero, clamped to the i32 range; NaN -> 0 (indeterminate in WGSL)."""
+    if v != v:
+        return 0
+    if v >= 2147483648.0:
+        return 2147483647
+    if v <= -2147483648.0:
+        return -2147483648
+    return int(v)
+
+
+def f32_div(a, b):
+    """IEEE f32 division with the f32 results for a zero divisor."""
+    if b == 0.0:
+        if a == 0.0 or a != a:
+            return float("nan")
+        return float("inf") if (a > 0) == (str(b)[0] != "-") else float("-inf")
+    return f32(a / b)
+
+
+def clamp(v, lo, hi):
+    return max(lo, min(hi, v))
+
+
+# kernels/wgsl/gpu/quantized_nax.wgsl:157-232 (format 0 = int4 sym, 1 = int4 asym, 2 = int8 sym)
+def compute_group_scales(vals, group, fmt):
+    out = []
+    for b in range(0, len(vals), group):
+        mx, mn = f32(-1e30), f32(1e30)
+        for v in vals[b:b + group]:
+            mx = max(mx, v)
+            mn = min(mn, v)
+        if fmt in (0, 2):
+            amax = max(abs(mx), abs(mn))
+            scale = f32_div(amax, 7.0 if fmt == 0 else 127.0)
+            zp = 0
+        else:
+            scale = f32_div(f32(mx - mn), 15.0)
+            r = f32_div(-mn, scale)
+            zp = clamp(wgsl_i32(float(round(r)) if r == r and abs(r) != float("inf") else r), 0, 15)
+        if scale == 0.0:
+            scale = 1.0
+        out.append((scale, zp, mn, mx))
+    return out
+
+
+# kernels/wgsl/gpu/quantized_nax.wgsl:236-259, 288-310 (+ :115-122), 336-362 (+ :135-140)
+def quantize_words(vals, group, fmt, gs):
+    per = 4 if fmt == 2 else 8
+    words = []
+    for w in range(len(vals) // per):
+        scale, zp, _, _ = gs[(w * per) // group]
+        word = 0
+        for i in range(per):
+            r = f32_div(vals[w * per + i], scale)
+            scaled = float(round(r)) if r == r and abs(r) != float("inf") else r
+            if fmt == 0:
+                word |= ((clamp(wgsl_i32(scaled), -8, 7) + 8) & 0xF) << (4 * i)
+            elif fmt == 1:
+                q = clamp(wgsl_i32(scaled), 0, 15) - zp
+                word |= (clamp(q + zp, 0, 15) & 0xF) << (4 * i)
+            else:
+                word |= (clamp(wgsl_i32(scaled), -128, 127) & 0xFF) << (8 * i)
+        words.append(word)
+    return words
+
+
 def main():
     rnd = random.Random(20240607)
     kat = {"unpack_int4_asym": [], "unpack_int4_sym": [], "unpack_int8": [], "pack_int4_asym": [],
@@ -191,6 +258,29 @@ def main():
             "dequant_bf16_bits": [[bf16_rne_bits(v) for v in r] for r in wdq],
             "y_f32_bits": y,
         })
+
+    # quantize side: group statistics and packed words.  A literal case first (checked by hand):
+    # eight values 0..7 in one int4-asym group of 8: max 7, min 0, scale 7/15, zp 0, and
+    # round(v / (7/15)) = 0, 2, 4, 6, 9, 11, 13, 15.
+    kat["quantize"] = []
+    lit = [float(i) for i in range(8)]
+    gs = compute_group_scales(lit, 8, 1)
+    assert quantize_words(lit, 8, 1, gs) == [0xFDB96420] and gs[0][1] == 0
+    cases = [(lit, 8, 1)]
+    for fmt, group in ((0, 128), (1, 128), (2, 32)):
+        n = 2 * group
+        cases.append(([f32(rnd.gauss(0, 1)) for _ in range(n)], group, fmt))
+        cases.append(([f32(rnd.gauss(0.5, 0.1)) for _ in range(n)], group, fmt))          # all positive
+        cases.append(([f32(-abs(rnd.gauss(0, 3))) for _ in range(n)], group, fmt))         # all negative
+        cases.append(([0.0] * group + [f32(rnd.uniform(-1, 1)) for _ in range(group)], group, fmt))   # a group of zeros
+        cases.append(([f32(2.5)] * group + [f32(-1.25)] * group, group, fmt))               # constant groups
+    for vals, group, fmt in cases:
+        gs = compute_group_scales(vals, group, fmt)
+        kat["quantize"].append({
+            "format": fmt, "group": group, "x_bits": [f32_bits(v) for v in vals],
+            "scale_bits": [f32_bits(g[0]) for g in gs], "zero_points": [g[1] for g in gs],
+            "min_bits": [f32_bits(g[2]) for g in gs], "max_bits": [f32_bits(g[3]) for g in gs],
+            "words": quantize_words(vals, group, fmt, gs)})
 
     out = os.path.join(os.path.dirname(os.path.abspath(__file__)), "wgsl_kat.json")
     with open(out, "w") as f:

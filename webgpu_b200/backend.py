@@ -38,7 +38,7 @@ CAP_TENSOR_OPS, CAP_MATMUL, CAP_CUSTOM_KERNELS = 1 << 0, 1 << 1, 1 << 4
 
 F32, F16, BF16 = 0, 1, 2
 NOALLOC_MAX_BYTES = 1 << 20          # LUX_QMLP_NOALLOC_MAX_BYTES
-FLAG_NO_SYNC, FLAG_SWIGLU = 1, 2
+FLAG_NO_SYNC, FLAG_SWIGLU, FLAG_WEIGHTS_VOLATILE, FLAG_QUANT_SHIFTED = 1, 2, 4, 8
 ROUTE_NONE, ROUTE_GEMV_I8, ROUTE_SKINNY_I4, ROUTE_GEMM_I4_TC = range(4)
 
 VTBL_FIELDS = [
@@ -103,7 +103,7 @@ class KernelAttributes(C.Structure):
 EXPORTED_SYMBOLS = [
     "lux_gpu_backend_init",
     "lux_cuda_qmatmul", "lux_cuda_qmatmul_host", "lux_cuda_qmatmul_route", "lux_cuda_qdequant",
-    "lux_cuda_qunpack", "lux_cuda_qmlp", "lux_cuda_qmlp_noalloc", "lux_cuda_context_set_stream", "lux_cuda_context_get_stream",
+    "lux_cuda_qunpack", "lux_cuda_qquantize", "lux_cuda_qmlp", "lux_cuda_qmlp_noalloc", "lux_cuda_context_set_stream", "lux_cuda_context_get_stream",
     "lux_cuda_buffer_wrap", "lux_cuda_buffer_device_ptr", "lux_cuda_buffer_size",
     "lux_cuda_launch_count", "lux_cuda_last_kernel_name", "lux_cuda_tune_set", "lux_cuda_last_device_status",
     "lux_cuda_kernel_get", "lux_cuda_kernel_destroy", "lux_cuda_kernel_entry_point",
@@ -198,6 +198,7 @@ class Backend:
         L.lux_cuda_qmatmul_route.argtypes = [C.POINTER(QMatmulDesc), _int, C.POINTER(_int)]
         L.lux_cuda_qdequant.argtypes = [_vp, C.POINTER(QMatmulDesc), _vp, _vp, _vp, _vp]
         L.lux_cuda_qunpack.argtypes = [_vp, C.POINTER(QMatmulDesc), _vp, _vp, _vp]
+        L.lux_cuda_qquantize.argtypes = [_vp, C.POINTER(QMatmulDesc), _vp, _vp, _vp, _vp]
         L.lux_cuda_qmlp.argtypes = [_vp, C.POINTER(QMlpDesc)] + [_vp] * 9
         L.lux_cuda_qmlp_noalloc.argtypes = [_vp, C.POINTER(QMlpDesc)] + [_vp] * 8
         L.lux_cuda_peer_comm_create.restype = C.c_int
@@ -457,6 +458,25 @@ class Context:
         res = out.to_host(np.int8, (L.N, L.K))
         out.free()
         return res
+
+    def qquantize(self, x: np.ndarray, bits: int, symmetric: bool = False, scale_dtype: int | None = None,
+                  flags: int = 0) -> DeviceQLayer:
+        """Quantizes a host matrix [N, K] (f32 / f16 / bf16 bit patterns) ON THE DEVICE into a layer the
+        matmul entry points take (lux_cuda_qquantize)."""
+        x = np.ascontiguousarray(x)
+        N, K = x.shape
+        group = 128 if bits == 4 else 32
+        if scale_dtype is None:
+            scale_dtype = F16 if bits == 4 else F32
+        G = K // group
+        xb = self.upload(x)
+        w = self.alloc(N * K * bits // 8)
+        sc = self.alloc(N * G * (4 if scale_dtype == F32 else 2))
+        z = self.alloc(N * ((G + 1) // 2)) if (bits == 4 and not symmetric) else None
+        d = make_desc(0, N, K, bits, group, np_dtype_code(x), scale_dtype, F32, flags)
+        _check(self.backend.lib.lux_cuda_qquantize(self.handle, C.byref(d), xb.handle, w.handle, sc.handle,
+                                                   z.handle if z else None), "lux_cuda_qquantize")
+        return DeviceQLayer(bits, group, N, K, w, sc, z, scale_dtype)
 
     def qmlp(self, x: Buffer, gate_up: DeviceQLayer, down: DeviceQLayer, h: Buffer, y: Buffer, M: int,
              act_dtype: int, flags: int = 0) -> None:
