@@ -275,7 +275,8 @@ def quantize(x: np.ndarray, bits: int, group: int, symmetric: bool, scale_code: 
     fmt = NAX_INT8_SYM if bits == 8 else (NAX_INT4_SYM if symmetric else NAX_INT4_ASYM)
     gs = group_scales(x, group, fmt)
     if scale_code == F16:
-        s16 = gs["scale"].astype(np.float16)
+        with np.errstate(over="ignore"):
+            s16 = gs["scale"].astype(np.float16)
         gs = gs.copy()
         gs["scale"] = s16.astype(np.float32)
         scales = s16.reshape(N, K // group)

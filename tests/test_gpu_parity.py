@@ -50,7 +50,7 @@ def _units_supported(M, K, n_out=16, swiglu=False, sms=148, f16_variant=False):
     tmax = (min(M, 8) + 1) // 2
     zs = (G + 1) // 2
     meta = rows * G * 2 + ((rows * zs + 15) & ~15) + cap * 16
-    if M <= 2 and not f16_variant:      # block-fixed-point variant: three byte planes of x
+    if M <= 2 and not f16_variant:      # block-fixed-point variant: at least three byte planes of x
         fixed = G * 3 * M * 128 + G * 64 + meta + cap * 16 * M * 4 + 16 * 8 * 8 + 16 + 1024   # + barriers, slack
     else:
         fixed = M * (2 * K + 64) + G * 8 * mt * 8 + meta + cap * mt * 8 * tmax * 16
@@ -317,6 +317,35 @@ def test_int4_units_geometries(ctx, backend, cg, ks, stages, pre, M, fx):
     assert ctx.last_device_status() == 0
 
 
+@pytest.mark.parametrize("warps", [8, 16])
+@pytest.mark.parametrize("M", [1, 2])
+def test_units_fixed_point_both_cta_geometries(ctx, backend, M, warps):
+    """The fixed-point kernels in their half-SM (8 warps, two CTAs per SM) and whole-SM (16 warps)
+    geometries: plain int4, int4 with the SwiGLU epilogue, and int8, each against the oracle."""
+    backend.tune("gemv_units_warps", warps)
+    try:
+        x = synth.activations(M, 2048, "f16", 31, "geo.x")
+        layer = synth.int4_layer(1200, 2048, 31, "geo")
+        with _kernel(backend, 3):
+            y = _run(ctx, x, layer)
+            assert backend.last_kernel_name() == "lux_qgemv_i4_g128_units_fx"
+        assert orc.rel_l2(y, orc.qmatmul(x, *layer.triple, bits=4, group=128)) < 1e-3
+        gate_up, _ = synth.mlp_layers(2048, 592, 128, 31, "geo.mlp")
+        with _kernel(backend, 3):
+            h = _run(ctx, x, gate_up, flags=B.FLAG_SWIGLU)
+        gu = orc.qmatmul(x, *gate_up.triple, bits=4, group=128, y_code=orc.F32)
+        assert orc.rel_l2(h, orc.swiglu(gu, h_code=orc.F16)) < TOL_16
+        x8 = synth.activations(M, 2048, "f32", 31, "geo.x8")
+        l8 = synth.int8_layer(1200, 2048, 31, "geo8")
+        with _kernel8(backend, 2):
+            y8 = _run(ctx, x8, l8)
+            assert backend.last_kernel_name() == "lux_qgemv_i8_g32_units_fx"
+        assert orc.rel_l2(y8, orc.qmatmul(x8, *l8.triple, bits=8, group=32)) < 1e-5
+    finally:
+        backend.tune("gemv_units_warps", 0)
+    assert ctx.last_device_status() == 0
+
+
 @pytest.mark.parametrize("M", [1, 2])
 def test_int4_units_fixed_point_ranges(ctx, backend, M):
     """Block fixed point per group of 128 activations: groups of all zeros, of f16 denormals,
@@ -345,6 +374,63 @@ def test_int4_units_fixed_point_ranges(ctx, backend, M):
     with _kernel(backend, 3):
         y2 = _run(ctx, x2, layer)
     assert orc.rel_l2(y2, ref2) < TOL_16
+
+
+@pytest.mark.parametrize("warps", [8, 16])
+@pytest.mark.parametrize("k_out", [130, 131])
+@pytest.mark.parametrize("M", [1, 2])
+def test_int4_units_fixed_point_outlier_group(ctx, backend, M, k_out, warps):
+    """The "massive activation" case: one activation 2^15 times larger than everything else in its
+    group, sitting on a weight whose (q - zp) is 0 in every row, at an even and at an odd k.  The
+    outlier sets the group's block exponent and contributes nothing, so the outputs are made of
+    the SMALL elements alone: with four byte planes (30 bits below the block exponent for even
+    k, 26 for odd k) every f16 within 2^15 of the outlier is still exact, and the result must
+    meet the 16-bit tolerance with room to spare, in both CTA geometries."""
+    K, N = 1024, 512
+    rng = np.random.default_rng(91)
+    x = (rng.standard_normal((M, K)) * 0.5).astype(np.float32)
+    x[:, k_out] = 0.9 * 32768.0 * np.sign(x[:, k_out])
+    x = x.astype(np.float16)
+    layer = synth.int4_layer(N, K, 91, "outl")
+    zp = synth.unpack_nibbles(layer.zeros, K // 128)[:, k_out // 128]
+    byte = layer.w[:, k_out // 2]
+    layer.w[:, k_out // 2] = (byte & 0xF0) | zp if k_out % 2 == 0 else (byte & 0x0F) | (zp << 4)
+    ref = orc.qmatmul(x, *layer.triple, bits=4, group=128)
+    x0 = x.copy()
+    x0[:, k_out] = 0
+    assert orc.rel_l2(orc.qmatmul(x0, *layer.triple, bits=4, group=128), ref) < 1e-6     # the outlier is inert
+    backend.tune("gemv_units_warps", warps)
+    try:
+        with _kernel(backend, 3):
+            y = _run(ctx, x, layer)
+        assert backend.last_kernel_name() == "lux_qgemv_i4_g128_units_fx"
+        # rows too long for four planes keep three (22 / 18 bits): the same case then carries the
+        # rounding of the small odd-k elements, 2^-19 of the outlier each, and stays within 3e-2
+        backend.tune("gemv_units_planes", 3)
+        with _kernel(backend, 3):
+            y3 = _run(ctx, x, layer)
+    finally:
+        backend.tune("gemv_units_warps", 0)
+        backend.tune("gemv_units_planes", 0)
+    assert orc.rel_l2(y, ref) < 1e-3, orc.rel_l2(y, ref)
+    assert orc.rel_l2(y3, ref) < 3e-2, orc.rel_l2(y3, ref)
+
+
+@pytest.mark.parametrize("M", [1, 2])
+def test_int8_units_fixed_point_outlier_group(ctx, backend, M):
+    """The same for the int8 kernel (groups of 32, f32 activations, 30 bits below the block
+    exponent): an activation 2^15 times the rest on weights that are 0."""
+    K, N = 1024, 512
+    rng = np.random.default_rng(92)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    x[:, 77] = 32768.0 * 1.7
+    layer = synth.int8_layer(N, K, 92, "outl8")
+    layer.w[:, 77] = 0
+    ref = orc.qmatmul(x, *layer.triple, bits=8, group=32)
+    with _kernel8(backend, 2):
+        y = _run(ctx, x, layer)
+        assert backend.last_kernel_name() == "lux_qgemv_i8_g32_units_fx"
+    assert orc.rel_l2(y, ref) < 1e-5, orc.rel_l2(y, ref)
 
 
 def test_int4_units_fixed_point_nonfinite(ctx, backend):

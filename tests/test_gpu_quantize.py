@@ -24,8 +24,9 @@ def _matrix(N, K, seed, kind="normal"):
         x[2, :g] = -1.25                        # a constant negative group (+inf)
         x[3] = np.abs(x[3])                     # one sign only
         x[4] = -np.abs(x[4])
-        x[5, 7] = 3.0e38                        # near the f32 limit
-        x[6, :32] *= 1e-30                      # tiny values: scale far below f16's range
+        if N > 6:
+            x[5, 7] = 3.0e38                    # near the f32 limit
+            x[6, :32] *= 1e-30                  # tiny values: scale far below f16's range
     return x
 
 

@@ -104,6 +104,8 @@ struct Tunables {
     int gemv_units_cg = 0;       // units kernel: groups per chunk (2 or 4)
     int gemv_units_pre = 0;      // units kernel: chunks requested per warp before its loop starts (default 1)
     int gemv_units_fx = 0;       // units kernel, batch <= 2: 0/1 block-fixed-point int8 variant, 2 f16 variant
+    int gemv_units_warps = 0;    // fixed-point units kernels: 8 half-SM CTAs (where the plan fits), 0/16 whole-SM CTAs
+    int gemv_units_planes = 0;   // fixed-point units kernels: byte planes of the activations, 3 or 4 (0 = 4 where it costs no FIFO depth)
     int gemm_tc_bn = 0;          // N tile of the tcgen05 GEMM
     int gemm_tc_stages = 0;
     int gemm_tc_splitk = 0;      // weights-in-TMEM GEMM: K splits over a CTA cluster, 1, 2 or 4 (0 = choose)

@@ -5,13 +5,16 @@
 //
 // The weights ARE signed bytes: they feed mma.sync.m16n8k32.s8.s8 straight from shared memory
 // with no unpacking at all (one mma per 16 rows x one quantization group).  The activations are
-// converted once per CTA to block fixed point per group of 32: X = rint(x * 2^(22-E)) with 2^E
-// just above the group's largest |x| (absolute error at most 2^(E-23); groups whose largest
-// magnitude is below 2^-96 count as zero), split into three signed bytes
-// X = d0 + 256 d1 + 65536 d2 that ride in three of the eight B columns (six for batch 2).  The
-// int32 accumulators are exact and start at the bit pattern of 1.5 * 2^23, so they read as
-// floats without a conversion; the group sum is scaled by 2^(E-22) 256^plane and the group's
-// f32 scale, and the planes are added once per unit.
+// converted once per CTA to block fixed point per group of 32: X = rint(x * 2^(30-E)) with 2^E
+// just above the group's largest |x|.  An f32 has 24 significant bits, so every value down to 2^-6
+// of the group's largest magnitude is represented exactly and a smaller one is rounded with an
+// absolute error of at most 2^(E-31), i.e. 2^-31 of the group's largest magnitude (the reference's
+// f32 products round at 2^-24 relative, kernels/wgsl/gpu/quantized_nax.wgsl:615-618); groups whose
+// largest magnitude is below 2^-96 count as zero.  X is split into four signed bytes
+// X = d0 + 256 d1 + 65536 d2 + 2^24 d3 that ride in four of the eight B columns (all eight for
+// batch 2).  The int32 accumulators are exact and start at the bit pattern of 1.5 * 2^23, so they
+// read as floats without a conversion; the group sum is scaled by 2^(E-30) 256^plane and the
+// group's f32 scale, and the planes are added once per unit.
 //
 // Structure as in the int4 kernel: one persistent CTA per SM owns a contiguous range of 16-row
 // tiles; a tile is cut along K into units of KS groups and every (tile, unit) belongs to ONE
@@ -109,23 +112,25 @@ struct I8UnitsParams {
     int units_cap;          // partial-sum slots per CTA
     int rows_cap;           // weight rows whose scales are staged per CTA
     uint32_t inv_U;         // ceil(2^32 / U) (0 when U == 1): division-free unit table
+    int planes;             // signed byte planes of the activations, 4 or 3
 };
 
 // Shared memory: [FIFOs: UW x S x 4 KB, 1024-byte aligned]
-// [xq: G x (3 planes x MM) x 32 signed bytes in K order]
-// [xmeta: G x 8 columns x coefficient 2^(E-22) 256^plane; column = plane (MM = 1) or 2 plane + m]
+// [xq: G x (4 planes x MM) x 32 signed bytes in K order]
+// [xmeta: G x 8 columns x coefficient 2^(E-30) 256^plane; column = plane (MM = 1) or 2 plane + m]
 // [scales: rows_cap x G f32][partials: units_cap x 16 rows x MM float][unit table][barriers][flag]
 //
 // mma operand order inside a group: lane (g, t) supplies k = 8t .. 8t+7 of its two rows (a0 / a1 =
 // bytes 8t..8t+3 of rows g / g+8, a2 / a3 = bytes 8t+4..8t+7) and, for the B operand, the same
 // eight k of column g: both are plain contiguous 8-byte reads.
-template <int MM>
-__global__ void __launch_bounds__(UW * 32, 1)
+template <int MM, int UWT>
+__global__ void __launch_bounds__(UWT * 32, UWT == 8 ? 2 : 1)
 lux_qgemv_i8_g32_units_fx(const __grid_constant__ CUtensorMap map_w, const I8UnitsParams p) {
     extern __shared__ unsigned char smem_raw[];
     // 1024-byte alignment by OFFSET from the __shared__ symbol (keeps 32-bit shared addressing)
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    constexpr int XG = 3 * MM * 32;                     // bytes of xq per group
+    constexpr int UW = UWT;                             // warps per CTA (shadows the file-wide 16)
+    const int XG = p.planes * MM * 32;                  // bytes of xq per group
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
 
@@ -206,7 +211,7 @@ lux_qgemv_i8_g32_units_fx(const __grid_constant__ CUtensorMap map_w, const I8Uni
     // Everything above read static model state only; x may come from the previous kernel.
     pdl_wait();
 
-    // ---- x -> block fixed point, three signed byte planes in K order -----------------------------
+    // ---- x -> block fixed point, four signed byte planes in K order -----------------------------
     for (int c = tid; c < npieces; c += UW * 32) {
         xa = __ldg(reinterpret_cast<const uint4*>(p.x) + 2 * c);
         xb = __ldg(reinterpret_cast<const uint4*>(p.x) + 2 * c + 1);
@@ -222,45 +227,51 @@ lux_qgemv_i8_g32_units_fx(const __grid_constant__ CUtensorMap map_w, const I8Uni
         mb = max(mb, __shfl_xor_sync(0xffffffffu, mb, 1));
         mb = max(mb, __shfl_xor_sync(0xffffffffu, mb, 2));
         const bool bad = mb >= 0x7f800000u;
-        // amax = f * 2^E with f in [0.5, 1): biased exponent eb = E + 126.  x * 2^(22-E) is exact
+        // amax = f * 2^E with f in [0.5, 1): biased exponent eb = E + 126.  x * 2^(30-E) is exact
         // up to the final rounding to an integer.
         const uint32_t eb = mb >> 23;
         const bool live = eb >= 30u && !bad;             // below 2^-96: the group counts as zero
-        const float up = live ? __uint_as_float((275u - eb) << 23) : 0.0f;     // 2^(22-E)
-        float down = live ? __uint_as_float((eb - 21u) << 23) : 0.0f;          // 2^(E-22)
+        // four planes: 30 bits below the block exponent; three (rows too long for four): 22
+        const uint32_t sh = p.planes == 4 ? 30u : 22u;
+        const float up = live ? __uint_as_float((253u + sh - eb) << 23) : 0.0f;     // 2^(sh-E)
+        float down = live ? __uint_as_float((eb + 1u - sh) << 23) : 0.0f;           // 2^(E-sh)
         if (bad) down = __uint_as_float(0x7FC00000u);    // inf / NaN in the group: the outputs are NaN
-        // I + 0x808080 has bytes d0+128, d1+128, d2+128 (I = d0 + 256 d1 + 65536 d2, digits in
-        // [-128, 127]); flipping the top bit of each turns them into the digits as signed bytes.
+        // I + 0x80808080 has bytes d0+128 .. d3+128 (I = d0 + 256 d1 + 65536 d2 + 2^24 d3, digits in
+        // [-128, 127]; |I| <= 2^30 fits); flipping the top bit of each turns them into the digits as
+        // signed bytes.
         uint32_t e[8];
 #pragma unroll
         for (int i = 0; i < 8; i++)
-            e[i] = (uint32_t)(__float2int_rn(__uint_as_float(bits[i]) * up) + 0x808080) ^ 0x808080u;
+            e[i] = ((uint32_t)__float2int_rn(__uint_as_float(bits[i]) * up) + 0x80808080u) ^ 0x80808080u;
         // byte transpose: word h of plane pl holds the digits of k = 4h .. 4h+3
-        uint32_t pw[3][2];
+        uint32_t pw[4][2];
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             const uint32_t a01 = prmt(e[4 * h], e[4 * h + 1], 0x5140), a23 = prmt(e[4 * h + 2], e[4 * h + 3], 0x5140);
-            const uint32_t c01 = prmt(e[4 * h], e[4 * h + 1], 0x0062), c23 = prmt(e[4 * h + 2], e[4 * h + 3], 0x0062);
+            const uint32_t c01 = prmt(e[4 * h], e[4 * h + 1], 0x7362), c23 = prmt(e[4 * h + 2], e[4 * h + 3], 0x7362);
             pw[0][h] = prmt(a01, a23, 0x5410);
             pw[1][h] = prmt(a01, a23, 0x7632);
             pw[2][h] = prmt(c01, c23, 0x5410);
+            pw[3][h] = prmt(c01, c23, 0x7632);
         }
 #pragma unroll
-        for (int pl = 0; pl < 3; pl++)
+        for (int pl = 0; pl < 4; pl++) {
+            if (pl == 3 && p.planes == 3) break;             // the fourth digit of a 23-bit number is 0
             *reinterpret_cast<uint2*>(xq + (size_t)grp * XG + (pl * MM + m) * 32 + l4 * 8) = make_uint2(pw[pl][0], pw[pl][1]);
+        }
         if (l4 == 0) {
             // Lane t of a consumer reads {coefficient of column 2t, of column 2t+1}.  Every float of
             // the group's eight is written exactly once; columns without a plane behind them get 0
             // (their accumulators hold garbage).
             float* xm = xmeta + grp * 8;
             if (MM == 1) {
-                *reinterpret_cast<float4*>(xm) = make_float4(down, down * 256.0f, down * 65536.0f, 0.f);
+                *reinterpret_cast<float4*>(xm) = make_float4(down, down * 256.0f, down * 65536.0f, p.planes == 4 ? down * 16777216.0f : 0.f);
                 *reinterpret_cast<float4*>(xm + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
             } else {
                 xm[m] = down;
                 xm[2 + m] = down * 256.0f;
                 xm[4 + m] = down * 65536.0f;
-                xm[6 + m] = 0.f;
+                xm[6 + m] = p.planes == 4 ? down * 16777216.0f : 0.f;
             }
         }
     }
@@ -270,8 +281,8 @@ lux_qgemv_i8_g32_units_fx(const __grid_constant__ CUtensorMap map_w, const I8Uni
     asm volatile("cp.async.wait_group 0;" ::: "memory");   // the scales have landed
     __syncthreads();
 
-    // lanes of column g >= 3*MM multiply garbage that nobody reads: point them at a valid column
-    const int col = min(g, 3 * MM - 1);
+    // lanes of column g >= 4*MM multiply garbage that nobody reads: point them at a valid column
+    const int col = min(g, p.planes * MM - 1);
     const int xcol_off = col * 32 + t * 8;
     const int rg = row_of(g);                            // tile row behind fragment row g
     float res[2][2];                                     // [row half][column 2t / 2t+1 of the lane]
@@ -374,9 +385,9 @@ lux_qgemv_i8_g32_units_fx(const __grid_constant__ CUtensorMap map_w, const I8Uni
     }
 }
 
-template <int MM>
+template <int MM, int UWT>
 cudaError_t launch_inst(bool pdl, const CUtensorMap& map, const I8UnitsParams& p, int grid, size_t smem, cudaStream_t st) {
-    auto kfn = lux_qgemv_i8_g32_units_fx<MM>;
+    auto kfn = lux_qgemv_i8_g32_units_fx<MM, UWT>;
     static std::atomic<size_t> configured[64];
     int dev = 0;
     cudaGetDevice(&dev);
@@ -385,7 +396,7 @@ cudaError_t launch_inst(bool pdl, const CUtensorMap& map, const I8UnitsParams& p
         if (e != cudaSuccess) return e;
         configured[dev & 63].store(smem, std::memory_order_relaxed);
     }
-    return launch_pdl(pdl, kfn, dim3((unsigned)grid), dim3(UW * 32), smem, st, 1, map, p);
+    return launch_pdl(pdl, kfn, dim3((unsigned)grid), dim3(UWT * 32), smem, st, 1, map, p);
 }
 
 }  // namespace
@@ -402,50 +413,71 @@ LuxBackendError launch_qgemv_i8_units(Context* ctx, const QArgs& a) {
     const int tiles = a.N / 16;
     const int grid = std::min(ctx->sm_count, tiles);
     const int tiles_per_cta = (tiles + grid - 1) / grid;
-    // Unit size KS (a multiple of the 8-group chunk, dividing G): the one that spreads the busiest
-    // CTA's groups most evenly over its 16 warps, each unit costing about one group of overhead.
-    int KS = 0;
-    double best = 1e30;
-    for (int ks = CGRP; ks <= std::min(a.G, 256); ks += CGRP) {
-        if (a.G % ks) continue;
-        const int units = tiles_per_cta * (a.G / ks);
-        const double cost = (double)((units + UW - 1) / UW) * (ks + 1.0);
-        if (cost < best - 1e-9) { best = cost; KS = ks; }
-    }
-    if (g_tune.gemv_units_ks > 0 && a.G % g_tune.gemv_units_ks == 0 && g_tune.gemv_units_ks % CGRP == 0) KS = g_tune.gemv_units_ks;
-    if (KS == 0) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
-    const int U = a.G / KS;
 
-    I8UnitsParams p{};
-    p.x = (const float*)a.x;
-    p.w = (const int8_t*)a.w;
-    p.scales = (const float*)a.scales;
-    p.y = (float*)a.y;
-    p.status = ctx->d_status;
-    p.M = a.M;
-    p.N = a.N;
-    p.K = a.K;
-    p.G = a.G;
-    p.U = U;
-    p.KS = KS;
-    p.tiles_base = tiles / grid;
-    p.tiles_rem = tiles % grid;
-    p.units_cap = tiles_per_cta * U;
-    p.rows_cap = tiles_per_cta * 16;
-    p.inv_U = U > 1 ? (uint32_t)((((uint64_t)1 << 32) + (uint32_t)U - 1) / (uint32_t)U) : 0u;
-
-    const size_t fixed = (size_t)a.G * 3 * a.M * 32 + (size_t)a.G * 8 * sizeof(float) + (size_t)p.rows_cap * a.G * sizeof(float) +
-                         (size_t)p.units_cap * 16 * a.M * sizeof(float) + (size_t)p.units_cap * sizeof(int2) +
-                         (size_t)UW * MAX_STAGES * 8 + 16 + 1024;
-    const size_t budget = 227 * 1024;
-    if (fixed + (size_t)UW * CHUNK > budget) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
-    const int max_chunks = (p.units_cap + UW - 1) / UW * (KS / CGRP);      // per warp
-    int S = (int)std::min<size_t>((budget - fixed) / ((size_t)UW * CHUNK), MAX_STAGES);
-    S = std::min(S, std::max(max_chunks, 1));
-    if (g_tune.gemv_units_stages > 0) S = std::min(S, g_tune.gemv_units_stages);
-    else S = std::min(S, 2);
-    p.S = std::max(S, 1);
-    const size_t smem = fixed + (size_t)p.S * UW * CHUNK;
+    // Geometry as in the int4 kernel: the whole SM with 16 warps; gemv_units_warps = 8 selects half an
+    // SM (8 warps, at most 113 KB), measured slower there.
+    struct Plan { int uw, S; size_t smem; I8UnitsParams p; };
+    auto make_plan = [&](int uw, size_t budget, int min_stages, int planes, Plan& pl) -> bool {
+        // Unit size KS (a multiple of the 8-group chunk, dividing G): the one that spreads the busiest
+        // CTA's groups most evenly over its warps, each unit costing about one group of overhead.
+        int KS = 0;
+        double best = 1e30;
+        for (int ks = CGRP; ks <= std::min(a.G, 256); ks += CGRP) {
+            if (a.G % ks) continue;
+            const int units = tiles_per_cta * (a.G / ks);
+            const double cost = (double)((units + uw - 1) / uw) * (ks + 1.0);
+            if (cost < best - 1e-9) { best = cost; KS = ks; }
+        }
+        if (g_tune.gemv_units_ks > 0 && a.G % g_tune.gemv_units_ks == 0 && g_tune.gemv_units_ks % CGRP == 0) KS = g_tune.gemv_units_ks;
+        if (KS == 0) return false;
+        const int U = a.G / KS;
+        I8UnitsParams& p = pl.p;
+        p = I8UnitsParams{};
+        p.x = (const float*)a.x;
+        p.w = (const int8_t*)a.w;
+        p.scales = (const float*)a.scales;
+        p.y = (float*)a.y;
+        p.status = ctx->d_status;
+        p.M = a.M;
+        p.N = a.N;
+        p.K = a.K;
+        p.G = a.G;
+        p.U = U;
+        p.KS = KS;
+        p.tiles_base = tiles / grid;
+        p.tiles_rem = tiles % grid;
+        p.units_cap = tiles_per_cta * U;
+        p.rows_cap = tiles_per_cta * 16;
+        p.inv_U = U > 1 ? (uint32_t)((((uint64_t)1 << 32) + (uint32_t)U - 1) / (uint32_t)U) : 0u;
+        p.planes = planes;
+        const size_t fixed = (size_t)a.G * planes * a.M * 32 + (size_t)a.G * 8 * sizeof(float) + (size_t)p.rows_cap * a.G * sizeof(float) +
+                             (size_t)p.units_cap * 16 * a.M * sizeof(float) + (size_t)p.units_cap * sizeof(int2) +
+                             (size_t)uw * MAX_STAGES * 8 + 16 + 1024;
+        if (fixed + (size_t)min_stages * uw * CHUNK > budget) return false;
+        const int max_chunks = (p.units_cap + uw - 1) / uw * (KS / CGRP);      // per warp
+        int S = (int)std::min<size_t>((budget - fixed) / ((size_t)uw * CHUNK), MAX_STAGES);
+        S = std::min(S, std::max(max_chunks, 1));
+        if (g_tune.gemv_units_stages > 0) S = std::min(S, g_tune.gemv_units_stages);
+        else S = std::min(S, uw == 8 ? 3 : 2);
+        pl.uw = uw;
+        pl.S = p.S = std::max(S, 1);
+        pl.smem = fixed + (size_t)p.S * uw * CHUNK;
+        return true;
+    };
+    Plan pl;
+    bool planned = false;
+    // four byte planes of the activations wherever they cost no FIFO depth, else three
+    auto plan_planes = [&](int uw, size_t budget, int min_stages) -> bool {
+        Plan p3, p4;
+        const bool ok3 = g_tune.gemv_units_planes != 4 && make_plan(uw, budget, min_stages, 3, p3);
+        const bool ok4 = g_tune.gemv_units_planes != 3 && make_plan(uw, budget, min_stages, 4, p4);
+        if (ok4 && (!ok3 || p4.S >= p3.S)) { pl = p4; return true; }
+        if (ok3) { pl = p3; return true; }
+        return false;
+    };
+    if (g_tune.gemv_units_warps == 8) planned = plan_planes(8, (size_t)113 * 1024, 2);
+    if (!planned && g_tune.gemv_units_warps != 8) planned = plan_planes(UW, (size_t)227 * 1024, 1);
+    if (!planned) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
 
     // int8 weights as a 3-D tensor {128 bytes, N rows, K/128 lines}; a chunk is one box {128, 16, 2},
     // 128-byte swizzle keyed by the row
@@ -455,12 +487,17 @@ LuxBackendError launch_qgemv_i8_units(Context* ctx, const QArgs& a) {
     const uint32_t box[3] = {128, 16, 2};
     if (!encode_tensor_map_u8(&map, 3, a.w, dims, strides, box, true)) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
     const bool pdl = pdl_allowed(ctx, a.weights_volatile);
-    const cudaError_t e = a.M == 1 ? launch_inst<1>(pdl, map, p, grid, smem, ctx->stream)
-                                   : launch_inst<2>(pdl, map, p, grid, smem, ctx->stream);
+    cudaError_t e;
+    if (pl.uw == 8)
+        e = a.M == 1 ? launch_inst<1, 8>(pdl, map, pl.p, grid, pl.smem, ctx->stream)
+                     : launch_inst<2, 8>(pdl, map, pl.p, grid, pl.smem, ctx->stream);
+    else
+        e = a.M == 1 ? launch_inst<1, 16>(pdl, map, pl.p, grid, pl.smem, ctx->stream)
+                     : launch_inst<2, 16>(pdl, map, pl.p, grid, pl.smem, ctx->stream);
     count_launch("lux_qgemv_i8_g32_units_fx");
     return map_cuda(e, "lux_qgemv_i8_g32_units_fx");
 }
 
-const void* kernel_addr_qgemv_i8_units_fx() { return (const void*)lux_qgemv_i8_g32_units_fx<1>; }
+const void* kernel_addr_qgemv_i8_units_fx() { return (const void*)lux_qgemv_i8_g32_units_fx<1, 16>; }
 
 }  // namespace luxcuda

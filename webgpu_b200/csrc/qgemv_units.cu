@@ -36,13 +36,16 @@
 //       valid u8 operands of mma.m16n8k32.u8.s8 (half as many mma as f16), and
 //       lo Xe + hi Xo = R Xe + H (Zo - Xe) when the odd-k activation is held as Xo = 16 Zo.
 //       The activations are converted once per CTA to block fixed point: per group of 128,
-//       X = rint(x 2^(22-E)) for even k and 16 rint(x 2^(18-E)) for odd k, with 2^E just above
-//       the group's largest |x| (an f16 within 2^-11, resp. 2^-7, of that magnitude is
-//       represented exactly; the absolute error is at most 2^(E-23), resp. 2^(E-19)).  Xe and
-//       W = Zo - Xe are split into three signed bytes I = d0 + 256 d1 + 65536 d2 that ride in
-//       three of the eight B columns.  The int32 accumulators are exact; sum (n - zp) X is
-//       completed exactly in f32, scaled by 2^(E-22) 256^plane and the group's f16 scale, and
-//       the three planes are added at the end of a unit.
+//       X = rint(x 2^(30-E)) for even k and 16 rint(x 2^(26-E)) for odd k, with 2^E just above
+//       the group's largest |x|.  An f16 has 11 significant bits, so every value down to 2^-19
+//       (even k) resp. 2^-15 (odd k) of the group's largest magnitude is represented EXACTLY; a
+//       smaller one is rounded with an absolute error of at most 2^(E-31) resp. 2^(E-27), i.e.
+//       2^-27 of the group's largest magnitude -- below the 2^-24 relative rounding of the f32
+//       products the reference forms (kernels/wgsl/gpu/quantized_nax.wgsl:615-618).  Xe and
+//       W = Zo - Xe are split into four signed bytes I = d0 + 256 d1 + 65536 d2 + 2^24 d3 that
+//       ride in four of the eight B columns (all eight at batch 2).  The int32 accumulators are
+//       exact; sum (n - zp) X is completed exactly in f32 per plane, scaled by 2^(E-30) 256^plane
+//       and the group's f16 scale, and the planes are added at the end of a unit.
 //
 // Both compute matmul_nax_grouped (luxcpp/webgpu kernels/wgsl/gpu/quantized_nax.wgsl:568-626)
 // in a different summation order.
@@ -124,6 +127,7 @@ struct UnitsParams {
     int rows_cap;           // weight rows (gate + up) whose scales / zero-points are staged per CTA
     uint32_t* status;       // device status word for a wait that gave up (may be null)
     uint32_t inv_upt, inv_U; // ceil(2^32 / (units per tile)), ceil(2^32 / U): division-free unit table
+    int planes;             // fixed-point variant: signed byte planes of the activations, 4 or 3
     PushTarget push;        // world > 1: the outputs go to the peers' all-reduce windows instead of y
 };
 
@@ -431,7 +435,7 @@ __global__ void __launch_bounds__(UW * 32, 1) lux_qgemv_i4_g128_units(const Unit
 // gives up sets a flag, every warp leaves its loop, and the status word reports it.
 //
 // Shared memory: [FIFOs: UW x S x CG KB, 1024-byte aligned]
-// [xq: G x (3 planes x MM) x 128 signed bytes, each 128 in B-fragment order]
+// [xq: G x (4 planes x MM) x 128 signed bytes, each 128 in B-fragment order]
 // [xmeta: G x 8 columns x {coef, digit sum}; column = plane (MM = 1) or 2 plane + m (MM = 2)]
 // [scales][zero-points][partials: units_cap x 16 rows x MM float][unit table][barriers][flag]
 //
@@ -481,15 +485,16 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
 }
 __device__ __forceinline__ int rho(int g) { return (g >> 1) | ((g & 1) << 2); }
 
-template <int MM, bool SWIGLU, int CG>
-__global__ void __launch_bounds__(UW * 32, 1)
+template <int MM, bool SWIGLU, int CG, int UWT>
+__global__ void __launch_bounds__(UWT * 32, UWT == 8 ? 2 : 1)
 lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const UnitsParams p) {
     extern __shared__ unsigned char smem_raw[];
     // 1024-byte alignment by OFFSET from the __shared__ symbol (keeps 32-bit shared addressing)
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     constexpr int NACC = SWIGLU ? 2 : 1;
     constexpr int CHUNK = CG * 1024;
-    constexpr int XG = 3 * MM * 128;                    // bytes of xq per group
+    constexpr int UW = UWT;                             // warps per CTA (shadows the file-wide 16)
+    const int XG = p.planes * MM * 128;                 // bytes of xq per group
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
 
@@ -587,7 +592,7 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
     // Everything above read static model state only; x may come from the previous kernel.
     pdl_wait();
 
-    // ---- x -> block fixed point, three signed byte planes in B-fragment order -----------------
+    // ---- x -> block fixed point, four signed byte planes in B-fragment order -----------------
     for (int c = tid; c < npieces; c += UW * 32) {
         const uint4 s4 = __ldg(reinterpret_cast<const uint4*>(p.x) + c);
         const int m = (MM == 2 && c >= p.G * 16) ? 1 : 0, cg16 = c - m * p.G * 16;
@@ -609,82 +614,89 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
         for (int o = 8; o > 0; o >>= 1) mb = max(mb, __shfl_xor_sync(0xffffffffu, mb, o));
         const bool bad = mb >= 0x7C00u;
         const float amax = __half2float(__ushort_as_half((unsigned short)mb));
-        // amax = f * 2^E with f in [0.5, 1): biased exponent eb = E + 126.  x * 2^(22-E) is exact.
+        // amax = f * 2^E with f in [0.5, 1): biased exponent eb = E + 126.  x * 2^(30-E) is exact.
         const unsigned eb = __float_as_uint(amax) >> 23;
-        const float up = (mb != 0u && !bad) ? __uint_as_float((275u - eb) << 23) : 0.0f;    // 2^(22-E)
-        float down = mb != 0u ? __uint_as_float((eb - 21u) << 23) : 0.0f;                  // 2^(E-22)
+        // four planes: 30 bits below the block exponent; three (rows too long for four): 22
+        const unsigned sh = p.planes == 4 ? 30u : 22u;
+        const float up = (mb != 0u && !bad) ? __uint_as_float((253u + sh - eb) << 23) : 0.0f;   // 2^(sh-E)
+        float down = mb != 0u ? __uint_as_float((eb + 1u - sh) << 23) : 0.0f;                  // 2^(E-sh)
         if (bad) down = __uint_as_float(0x7FC00000u);    // inf / NaN in the group: the outputs are NaN
-        // Even k: X = rint(x 2^(22-E)).  Odd k: Z = rint(x 2^(18-E)) and X = 16 Z, so that the
+        // Even k: X = rint(x 2^(30-E)).  Odd k: Z = rint(x 2^(26-E)) and X = 16 Z, so that the
         // high nibble's product n X equals (16 n) Z: the weights' bytes then need one mask, not two.
         // With R = lo + 16 hi the raw byte and H = 16 hi the masked one,
         //   lo Xe + hi Xo = R Xe + H (Zo - Xe),
         // so the B operand holds the digits of Xe against R and of W = Zo - Xe against H.
-        // I + 0x808080 has bytes d0+128, d1+128, d2+128 (I = d0 + 256 d1 + 65536 d2, digits in
-        // [-128, 127]); flipping the top bit of each turns them into the digits as signed bytes.
+        // I + 0x80808080 has bytes d0+128 .. d3+128 (I = d0 + 256 d1 + 65536 d2 + 2^24 d3, digits in
+        // [-128, 127]; |I| < 2^30 + 2^26 fits); flipping the top bit of each turns them into the
+        // digits as signed bytes.
         uint32_t e[8], xo[4];
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             const int xe = __float2int_rn(v[2 * i] * up);
             const int zo = __float2int_rn(v[2 * i + 1] * (up * 0.0625f));
-            e[2 * i] = (uint32_t)(xe + 0x808080) ^ 0x808080u;
-            e[2 * i + 1] = (uint32_t)(zo - xe + 0x808080) ^ 0x808080u;
-            xo[i] = (uint32_t)(16 * zo + 0x808080) ^ 0x808080u;    // digits of the odd k's true X, for the sums
+            e[2 * i] = ((uint32_t)xe + 0x80808080u) ^ 0x80808080u;
+            e[2 * i + 1] = ((uint32_t)(zo - xe) + 0x80808080u) ^ 0x80808080u;
+            xo[i] = ((uint32_t)(16 * zo) + 0x80808080u) ^ 0x80808080u;   // digits of the odd k's true X, for the sums
         }
         // byte transpose: word h of plane pl holds, for i = 0..3, the digit of Xe (h = 0) or W (h = 1)
         // of the byte with nibbles k = 2i, 2i+1
-        uint32_t pw[3][2], po[3];
+        uint32_t pw[4][2], po[4];
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             const uint32_t a01 = prmt(e[h], e[2 + h], 0x5140), a23 = prmt(e[4 + h], e[6 + h], 0x5140);
-            const uint32_t c01 = prmt(e[h], e[2 + h], 0x0062), c23 = prmt(e[4 + h], e[6 + h], 0x0062);
+            const uint32_t c01 = prmt(e[h], e[2 + h], 0x7362), c23 = prmt(e[4 + h], e[6 + h], 0x7362);
             pw[0][h] = prmt(a01, a23, 0x5410);
             pw[1][h] = prmt(a01, a23, 0x7632);
             pw[2][h] = prmt(c01, c23, 0x5410);
+            pw[3][h] = prmt(c01, c23, 0x7632);
         }
         {
             const uint32_t a01 = prmt(xo[0], xo[1], 0x5140), a23 = prmt(xo[2], xo[3], 0x5140);
-            const uint32_t c01 = prmt(xo[0], xo[1], 0x0062), c23 = prmt(xo[2], xo[3], 0x0062);
+            const uint32_t c01 = prmt(xo[0], xo[1], 0x7362), c23 = prmt(xo[2], xo[3], 0x7362);
             po[0] = prmt(a01, a23, 0x5410);
             po[1] = prmt(a01, a23, 0x7632);
             po[2] = prmt(c01, c23, 0x5410);
+            po[3] = prmt(c01, c23, 0x7632);
         }
         // this thread's 8 k are 32t' + 16jp + 8b + (2i + h)
         const int tq = l16 >> 2, jp = (l16 >> 1) & 1, bb = l16 & 1;
 #pragma unroll
-        for (int pl = 0; pl < 3; pl++) {
+        for (int pl = 0; pl < 4; pl++) {
+            if (pl == 3 && p.planes == 3) break;             // the fourth digit of a 23-bit number is 0
             unsigned char* dst = xq + (size_t)grp * XG + (pl * MM + m) * 128 + tq * 32;
             *reinterpret_cast<uint32_t*>(dst + ((0 * 2 + jp) * 2 + bb) * 4) = pw[pl][0];
             *reinterpret_cast<uint32_t*>(dst + ((1 * 2 + jp) * 2 + bb) * 4) = pw[pl][1];
         }
-        // sums over the group of the true X's digits per plane (for the zero-point term); planes
-        // 0 and 1 share one register through the reduction (|sum| <= 128 * 128 fits 16 bits)
-        int ds[3];
+        // sums over the group of the true X's digits per plane (for the zero-point term); two planes
+        // share one register through the reduction (|sum| <= 128 * 128 fits 16 bits)
+        int ds[4];
 #pragma unroll
-        for (int pl = 0; pl < 3; pl++)
+        for (int pl = 0; pl < 4; pl++)
             ds[pl] = __dp4a((int)pw[pl][0], 0x01010101, __dp4a((int)po[pl], 0x01010101, 0));
-        int d01 = ds[0] + ds[1] * 65536, d2 = ds[2];
+        int d01 = ds[0] + ds[1] * 65536, d23 = ds[2] + ds[3] * 65536;
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) {
             d01 += __shfl_xor_sync(0xffffffffu, d01, o);
-            d2 += __shfl_xor_sync(0xffffffffu, d2, o);
+            d23 += __shfl_xor_sync(0xffffffffu, d23, o);
         }
         if (l16 == 0) {
             const int s0 = (int)(short)(d01 & 0xffff), s1 = (d01 - s0) >> 16;
+            const int s2 = (int)(short)(d23 & 0xffff), s3 = (d23 - s2) >> 16;
             // Lane t of a consumer reads one float4 = {coef, digit sum} of its columns 2t and 2t+1.
             // Every float of the group's four entries is written here exactly once; columns
             // without a plane behind them get coefficient 0 (their accumulators hold garbage).
             float4* xm = xmeta + grp * 4;
             if (MM == 1) {
                 xm[0] = make_float4(down, (float)s0, down * 256.0f, (float)s1);
-                xm[1] = make_float4(down * 65536.0f, (float)d2, 0.f, 0.f);
+                xm[1] = make_float4(down * 65536.0f, (float)s2, p.planes == 4 ? down * 16777216.0f : 0.f, (float)s3);
                 xm[2] = make_float4(0.f, 0.f, 0.f, 0.f);
                 xm[3] = make_float4(0.f, 0.f, 0.f, 0.f);
             } else {
                 float2* x2 = reinterpret_cast<float2*>(xm) + m;          // .xy for m = 0, .zw for m = 1
                 x2[0] = make_float2(down, (float)s0);
                 x2[2] = make_float2(down * 256.0f, (float)s1);
-                x2[4] = make_float2(down * 65536.0f, (float)d2);
-                x2[6] = make_float2(0.f, 0.f);
+                x2[4] = make_float2(down * 65536.0f, (float)s2);
+                x2[6] = make_float2(p.planes == 4 ? down * 16777216.0f : 0.f, (float)s3);
             }
         }
     }
@@ -695,8 +707,8 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
     cp_async_wait(0);                                    // the scales and zero-points have landed
     __syncthreads();
 
-    // lanes of column g >= 3*MM multiply garbage that nobody reads: point them at a valid column
-    const int col = min(g, 3 * MM - 1);
+    // lanes of column g >= 4*MM multiply garbage that nobody reads: point them at a valid column
+    const int col = min(g, p.planes * MM - 1);
     const int xcol_off = col * 128 + t * 32;
     const int rg = rho(g);                               // tile row behind fragment row g
     float res[2][2];                                     // [row half][column 2t / 2t+1 of the lane]
@@ -922,9 +934,9 @@ cudaError_t launch_units_inst(const UnitsParams& p, int grid, size_t smem, cudaS
     return cudaGetLastError();
 }
 
-template <int MM, bool SW, int CG>
+template <int MM, bool SW, int CG, int UWT>
 cudaError_t launch_units_fx_inst(bool pdl, const CUtensorMap& map, const UnitsParams& p, int grid, size_t smem, cudaStream_t st) {
-    auto kfn = lux_qgemv_i4_g128_units_fx<MM, SW, CG>;
+    auto kfn = lux_qgemv_i4_g128_units_fx<MM, SW, CG, UWT>;
     static std::atomic<size_t> configured[64];
     int dev = 0;
     cudaGetDevice(&dev);
@@ -933,13 +945,17 @@ cudaError_t launch_units_fx_inst(bool pdl, const CUtensorMap& map, const UnitsPa
         if (e != cudaSuccess) return e;
         configured[dev & 63].store(smem, std::memory_order_relaxed);
     }
-    return launch_pdl(pdl, kfn, dim3((unsigned)grid), dim3(UW * 32), smem, st, 1, map, p);
+    return launch_pdl(pdl, kfn, dim3((unsigned)grid), dim3(UWT * 32), smem, st, 1, map, p);
 }
 
 template <int MM, bool SW>
-cudaError_t launch_units_fx_cg(bool pdl, int cg, const CUtensorMap& map, const UnitsParams& p, int grid, size_t smem, cudaStream_t st) {
-    return cg == 4 ? launch_units_fx_inst<MM, SW, 4>(pdl, map, p, grid, smem, st)
-                   : launch_units_fx_inst<MM, SW, 2>(pdl, map, p, grid, smem, st);
+cudaError_t launch_units_fx_cg(bool pdl, int cg, int uw, const CUtensorMap& map, const UnitsParams& p, int grid, size_t smem,
+                               cudaStream_t st) {
+    if (uw == 8)
+        return cg == 4 ? launch_units_fx_inst<MM, SW, 4, 8>(pdl, map, p, grid, smem, st)
+                       : launch_units_fx_inst<MM, SW, 2, 8>(pdl, map, p, grid, smem, st);
+    return cg == 4 ? launch_units_fx_inst<MM, SW, 4, 16>(pdl, map, p, grid, smem, st)
+                   : launch_units_fx_inst<MM, SW, 2, 16>(pdl, map, p, grid, smem, st);
 }
 
 template <int MT, bool SW, bool M1>
@@ -961,49 +977,6 @@ LuxBackendError launch_qgemv_i4_units(Context* ctx, const QArgs& a) {
     const int MT = a.M <= 8 ? 1 : 2;
     const int nacc = a.swiglu ? 2 : 1;
     const int tiles = nout / 16;
-    const int grid = std::min(ctx->sm_count, tiles);
-    const int tiles_per_cta = (tiles + grid - 1) / grid;
-
-    // Chunk size: 4 groups when the group count allows, else 2.  Unit size KS (a multiple of
-    // the chunk, dividing G): the one that spreads the busiest CTA's groups most evenly over
-    // its 16 warps, each unit costing about a quarter of a group of overhead.
-    int cg = g_tune.gemv_units_cg == 2 || g_tune.gemv_units_cg == 4 ? g_tune.gemv_units_cg : ((a.G & 3) ? 2 : 4);
-    if (a.G % cg) cg = 2;
-    int KS = 0;
-    if (g_tune.gemv_units_ks > 0 && a.G % g_tune.gemv_units_ks == 0 && g_tune.gemv_units_ks % cg == 0) {
-        KS = g_tune.gemv_units_ks;
-    } else {
-        double best = 1e30;
-        for (int ks = cg; ks <= std::min(a.G, 32); ks += cg) {
-            if (a.G % ks) continue;
-            const int units = tiles_per_cta * nacc * (a.G / ks);
-            const double cost = (double)((units + UW - 1) / UW) * (ks + 0.25);
-            if (cost < best - 1e-9) { best = cost; KS = ks; }
-        }
-    }
-    if (KS == 0) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
-    const int U = a.G / KS;
-
-    UnitsParams p{};
-    p.x = (const __half*)a.x;
-    p.w = a.w;
-    p.scales = (const __half*)a.scales;
-    p.zeros = a.zeros;
-    p.y = (__half*)a.y;
-    p.M = a.M;
-    p.K = a.K;
-    p.G = a.G;
-    p.ZS = (a.G + 1) / 2;
-    p.Nout = nout;
-    p.up_row_offset = a.swiglu ? nout : 0;
-    p.U = U;
-    p.KS = KS;
-    p.xstride = a.G * 256 + 64;
-    p.tmax = (std::min(a.M, 8) + 1) / 2;
-    p.tiles_base = tiles / grid;
-    p.tiles_rem = tiles % grid;
-    p.units_cap = tiles_per_cta * nacc * U;
-    p.rows_cap = tiles_per_cta * 16 * nacc;
     // the staged tables are copied in 16-byte pieces per (CTA, gate/up half): 16 rows of scales
     // are 32*G bytes (always whole pieces); 16 rows of zero-points are 16*ZS bytes (always whole);
     // the sources must be 16-byte aligned
@@ -1011,30 +984,106 @@ LuxBackendError launch_qgemv_i4_units(Context* ctx, const QArgs& a) {
         (reinterpret_cast<uintptr_t>(a.w) & 15) || (reinterpret_cast<uintptr_t>(a.x) & 15))
         return LUX_BACKEND_ERROR_NOT_SUPPORTED;
     if (a.swiglu && (((size_t)nout * a.G * 2) & 15)) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
-
     // batch 1 and 2 use the block-fixed-point variant unless the tunable says otherwise
     const bool fx = a.M <= 2 && g_tune.gemv_units_fx != 2;
-    const size_t x_bytes = fx ? (size_t)a.G * 3 * a.M * 128 + (size_t)a.G * 4 * sizeof(float4)
-                              : (size_t)a.M * p.xstride + (size_t)a.G * 8 * MT * sizeof(float2);
-    const size_t meta_bytes = (size_t)p.rows_cap * a.G * 2 + (((size_t)p.rows_cap * p.ZS + 15) & ~(size_t)15);
-    const size_t part_bytes = fx ? (size_t)p.units_cap * 16 * a.M * sizeof(float)
-                                 : (size_t)p.units_cap * MT * 8 * p.tmax * sizeof(float4);
-    // the fixed-point variant also holds its barriers and flag, and 1024 bytes of alignment slack
-    const size_t fixed = x_bytes + meta_bytes + part_bytes + (size_t)p.units_cap * sizeof(int4) +
-                         (fx ? (size_t)UW * MAX_STAGES * 8 + 16 + 1024 : 0);
-    const size_t budget = 227 * 1024;
+
+    // Chunk size: 4 groups when the group count allows, else 2.
+    int cg = g_tune.gemv_units_cg == 2 || g_tune.gemv_units_cg == 4 ? g_tune.gemv_units_cg : ((a.G & 3) ? 2 : 4);
+    if (a.G % cg) cg = 2;
     const size_t chunk = (size_t)cg * 1024;
-    // room for at least one chunk of FIFO per warp (two for the cp.async variant)
-    if (fixed + (fx ? 1 : 2) * UW * chunk > budget) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
-    const int max_chunks = (p.units_cap + UW - 1) / UW * (KS / cg);       // per warp
-    int S = (int)std::min<size_t>((budget - fixed) / (UW * chunk), MAX_STAGES);
-    S = std::min(S, std::max(max_chunks, 1));
-    // measured on B200: the fixed-point variant is fastest two chunks deep (deeper FIFOs only delay
-    // the first chunk and the tables at start-up; large layers do not care)
-    if (g_tune.gemv_units_stages > 0) S = std::min(S, g_tune.gemv_units_stages);
-    else if (fx) S = std::min(S, 2);
-    p.S = std::max(S, 1);
-    p.S0 = std::min(p.S, g_tune.gemv_units_pre > 0 ? g_tune.gemv_units_pre : 1);
+
+    // A geometry: `uw` warps per CTA, one CTA per SM.  The default is the whole SM with 16 warps.
+    // gemv_units_warps = 8 selects HALF an SM (8 warps, at most 113 KB of shared memory, registers
+    // for two CTAs), so that the next kernel of the stream, launched programmatically, becomes
+    // resident beside this one and fills its FIFOs while this one still streams.  Measured on B200
+    // (config 2): 8.5 us per GEMV against 6.9 us with 16 warps -- eight warps per SM cannot keep up
+    // with the SM's share of HBM, and the overlap does not make up for it.
+    struct Plan { int uw, grid, tiles_per_cta, KS, U, S; size_t fixed, smem; UnitsParams p; };
+    auto make_plan = [&](int uw, size_t budget, int min_stages, int planes, Plan& pl) -> bool {
+        pl.uw = uw;
+        pl.grid = std::min(ctx->sm_count, tiles);
+        pl.tiles_per_cta = (tiles + pl.grid - 1) / pl.grid;
+        // Unit size KS (a multiple of the chunk, dividing G): the one that spreads the busiest CTA's
+        // groups most evenly over its warps, each unit costing about a quarter of a group of overhead.
+        int KS = 0;
+        if (g_tune.gemv_units_ks > 0 && a.G % g_tune.gemv_units_ks == 0 && g_tune.gemv_units_ks % cg == 0) {
+            KS = g_tune.gemv_units_ks;
+        } else {
+            double best = 1e30;
+            for (int ks = cg; ks <= std::min(a.G, 32); ks += cg) {
+                if (a.G % ks) continue;
+                const int units = pl.tiles_per_cta * nacc * (a.G / ks);
+                const double cost = (double)((units + uw - 1) / uw) * (ks + 0.25);
+                if (cost < best - 1e-9) { best = cost; KS = ks; }
+            }
+        }
+        if (KS == 0) return false;
+        pl.KS = KS;
+        pl.U = a.G / KS;
+        UnitsParams& p = pl.p;
+        p = UnitsParams{};
+        p.x = (const __half*)a.x;
+        p.w = a.w;
+        p.scales = (const __half*)a.scales;
+        p.zeros = a.zeros;
+        p.y = (__half*)a.y;
+        p.M = a.M;
+        p.K = a.K;
+        p.G = a.G;
+        p.ZS = (a.G + 1) / 2;
+        p.Nout = nout;
+        p.up_row_offset = a.swiglu ? nout : 0;
+        p.U = pl.U;
+        p.KS = KS;
+        p.xstride = a.G * 256 + 64;
+        p.tmax = (std::min(a.M, 8) + 1) / 2;
+        p.tiles_base = tiles / pl.grid;
+        p.tiles_rem = tiles % pl.grid;
+        p.units_cap = pl.tiles_per_cta * nacc * pl.U;
+        p.rows_cap = pl.tiles_per_cta * 16 * nacc;
+        p.planes = planes;
+        const size_t x_bytes = fx ? (size_t)a.G * planes * a.M * 128 + (size_t)a.G * 4 * sizeof(float4)
+                                  : (size_t)a.M * p.xstride + (size_t)a.G * 8 * MT * sizeof(float2);
+        const size_t meta_bytes = (size_t)p.rows_cap * a.G * 2 + (((size_t)p.rows_cap * p.ZS + 15) & ~(size_t)15);
+        const size_t part_bytes = fx ? (size_t)p.units_cap * 16 * a.M * sizeof(float)
+                                     : (size_t)p.units_cap * MT * 8 * p.tmax * sizeof(float4);
+        // the fixed-point variant also holds its barriers and flag, and 1024 bytes of alignment slack
+        pl.fixed = x_bytes + meta_bytes + part_bytes + (size_t)p.units_cap * sizeof(int4) +
+                   (fx ? (size_t)uw * MAX_STAGES * 8 + 16 + 1024 : 0);
+        if (pl.fixed + (size_t)min_stages * uw * chunk > budget) return false;
+        const int max_chunks = (p.units_cap + uw - 1) / uw * (KS / cg);       // per warp
+        int S = (int)std::min<size_t>((budget - pl.fixed) / ((size_t)uw * chunk), MAX_STAGES);
+        S = std::min(S, std::max(max_chunks, 1));
+        // measured on B200: the fixed-point variant is fastest two or three chunks deep (deeper FIFOs
+        // only delay the first chunk and the tables at start-up; large layers do not care)
+        if (g_tune.gemv_units_stages > 0) S = std::min(S, g_tune.gemv_units_stages);
+        else if (fx) S = std::min(S, uw == 8 ? 3 : 2);
+        pl.S = p.S = std::max(S, 1);
+        p.S0 = std::min(p.S, g_tune.gemv_units_pre > 0 ? g_tune.gemv_units_pre : 1);
+        pl.smem = pl.fixed + (size_t)p.S * uw * chunk;
+        return true;
+    };
+    Plan pl;
+    bool planned = false;
+    // two CTAs per SM: 2 x (dynamic + 1 KB reserved) must fit the SM's 228 KB
+    // Four byte planes of the activations wherever they cost no FIFO depth; rows so long that the
+    // fourth plane would (28672 elements at batch 1: 114 KB of planes) keep three, i.e. 22 / 18 bits
+    // below the block exponent instead of 30 / 26.  gemv_units_planes forces either.
+    auto plan_planes = [&](int uw, size_t budget, int min_stages) -> bool {
+        if (!fx) return make_plan(uw, budget, min_stages, 4, pl);
+        Plan p3, p4;
+        const bool ok3 = g_tune.gemv_units_planes != 4 && make_plan(uw, budget, min_stages, 3, p3);
+        const bool ok4 = g_tune.gemv_units_planes != 3 && make_plan(uw, budget, min_stages, 4, p4);
+        if (ok4 && (!ok3 || p4.S >= p3.S)) { pl = p4; return true; }
+        if (ok3) { pl = p3; return true; }
+        return false;
+    };
+    if (fx && g_tune.gemv_units_warps == 8) planned = plan_planes(8, (size_t)113 * 1024, 2);
+    if (!planned && (!fx || g_tune.gemv_units_warps != 8)) planned = plan_planes(UW, (size_t)227 * 1024, fx ? 1 : 2);
+    if (!planned) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+    UnitsParams& p = pl.p;
+    const int grid = pl.grid;
+    const size_t smem = pl.smem;
     p.status = ctx->d_status;
     p.push = PushTarget{};
     if (a.push) {
@@ -1043,11 +1092,10 @@ LuxBackendError launch_qgemv_i4_units(Context* ctx, const QArgs& a) {
         p.push = *a.push;
     }
     {
-        const uint32_t upt = (uint32_t)(nacc * U);
+        const uint32_t upt = (uint32_t)(nacc * pl.U);
         p.inv_upt = upt > 1 ? (uint32_t)((((uint64_t)1 << 32) + upt - 1) / upt) : 0u;
-        p.inv_U = U > 1 ? (uint32_t)((((uint64_t)1 << 32) + (uint32_t)U - 1) / (uint32_t)U) : 0u;
+        p.inv_U = pl.U > 1 ? (uint32_t)((((uint64_t)1 << 32) + (uint32_t)pl.U - 1) / (uint32_t)pl.U) : 0u;
     }
-    const size_t smem = fixed + (size_t)p.S * UW * chunk;
 
     cudaError_t e;
     if (fx) {
@@ -1060,11 +1108,11 @@ LuxBackendError launch_qgemv_i4_units(Context* ctx, const QArgs& a) {
         if (!encode_tensor_map_u8(&map, 3, a.w, dims, strides, box, true)) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
         const bool pdl = pdl_allowed(ctx, a.weights_volatile);
         if (a.M == 1)
-            e = a.swiglu ? launch_units_fx_cg<1, true>(pdl, cg, map, p, grid, smem, ctx->stream)
-                         : launch_units_fx_cg<1, false>(pdl, cg, map, p, grid, smem, ctx->stream);
+            e = a.swiglu ? launch_units_fx_cg<1, true>(pdl, cg, pl.uw, map, p, grid, smem, ctx->stream)
+                         : launch_units_fx_cg<1, false>(pdl, cg, pl.uw, map, p, grid, smem, ctx->stream);
         else
-            e = a.swiglu ? launch_units_fx_cg<2, true>(pdl, cg, map, p, grid, smem, ctx->stream)
-                         : launch_units_fx_cg<2, false>(pdl, cg, map, p, grid, smem, ctx->stream);
+            e = a.swiglu ? launch_units_fx_cg<2, true>(pdl, cg, pl.uw, map, p, grid, smem, ctx->stream)
+                         : launch_units_fx_cg<2, false>(pdl, cg, pl.uw, map, p, grid, smem, ctx->stream);
     } else if (a.M == 1) {
         e = a.swiglu ? launch_units_cg<1, true, true>(cg, p, grid, smem, ctx->stream)
                      : launch_units_cg<1, false, true>(cg, p, grid, smem, ctx->stream);
@@ -1079,10 +1127,9 @@ LuxBackendError launch_qgemv_i4_units(Context* ctx, const QArgs& a) {
     return map_cuda(e, "lux_qgemv_i4_g128_units");
 }
 
-
 const void* kernel_addr_qgemv_i4_units() { return (const void*)lux_qgemv_i4_g128_units<1, false, false, 4>; }
-const void* kernel_addr_qgemv_i4_units_fx() { return (const void*)lux_qgemv_i4_g128_units_fx<1, false, 4>; }
-const void* kernel_addr_qgemv_i4_units_fx_swiglu() { return (const void*)lux_qgemv_i4_g128_units_fx<1, true, 4>; }
-const void* kernel_addr_qgemv_i4_units_fx_batch2() { return (const void*)lux_qgemv_i4_g128_units_fx<2, false, 4>; }
+const void* kernel_addr_qgemv_i4_units_fx() { return (const void*)lux_qgemv_i4_g128_units_fx<1, false, 4, 16>; }
+const void* kernel_addr_qgemv_i4_units_fx_swiglu() { return (const void*)lux_qgemv_i4_g128_units_fx<1, true, 4, 16>; }
+const void* kernel_addr_qgemv_i4_units_fx_batch2() { return (const void*)lux_qgemv_i4_g128_units_fx<2, false, 4, 16>; }
 
 }  // namespace luxcuda

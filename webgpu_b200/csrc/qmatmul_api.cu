@@ -363,7 +363,7 @@ LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_tune_set(const char* key, int val
         {"gemv_i8_warps", &g_tune.gemv_i8_warps},   {"gemv_i8_kernel", &g_tune.gemv_i8_kernel}, {"peer_wait_limit", &g_tune.peer_wait_limit}, {"tp_fused_push", &g_tune.tp_fused_push},   {"gemm_tc_bn", &g_tune.gemm_tc_bn},
         {"gemv_i4_kernel", &g_tune.gemv_i4_kernel}, {"gemv_stream_cg", &g_tune.gemv_stream_cg},
         {"gemv_stream_stages", &g_tune.gemv_stream_stages}, {"gemv_stream_warps", &g_tune.gemv_stream_warps},
-        {"gemv_units_ks", &g_tune.gemv_units_ks}, {"gemv_units_stages", &g_tune.gemv_units_stages}, {"gemv_units_cg", &g_tune.gemv_units_cg}, {"gemv_units_pre", &g_tune.gemv_units_pre}, {"gemv_units_fx", &g_tune.gemv_units_fx},
+        {"gemv_units_ks", &g_tune.gemv_units_ks}, {"gemv_units_stages", &g_tune.gemv_units_stages}, {"gemv_units_cg", &g_tune.gemv_units_cg}, {"gemv_units_pre", &g_tune.gemv_units_pre}, {"gemv_units_fx", &g_tune.gemv_units_fx}, {"gemv_units_warps", &g_tune.gemv_units_warps}, {"gemv_units_planes", &g_tune.gemv_units_planes},
         {"gemm_tc_stages", &g_tune.gemm_tc_stages}, {"gemm_tc_splitk", &g_tune.gemm_tc_splitk}, {"gemm_tc_ma", &g_tune.gemm_tc_ma}, {"gemm_tc_groups", &g_tune.gemm_tc_groups}, {"gemm_tc_kernel", &g_tune.gemm_tc_kernel}, {"gemm_min_m", &g_tune.gemm_min_m}, {"pdl", &g_tune.pdl},
     };
     for (auto& t : table)
