@@ -105,14 +105,24 @@ typedef struct lux_gpu_backend_vtbl {
     LuxBackendError   (*buffer_copy_from_host)(LuxBackendContext*, LuxBackendBuffer*, const void* src, size_t bytes);
     void*             (*buffer_get_host_ptr)(LuxBackendContext*, LuxBackendBuffer*);
 
-    /* f32 tensor ops (:1694-1771); unwired slots are nullptr in the plugin too */
+    /* f32 tensor ops.  add / sub / mul / matmul are wired in the plugin (:1694-1771) and their
+     * signatures are observed.  The other slots of this block are nullptr there (:4044-4072), so
+     * their parameter lists CANNOT be observed: the ones below are this reconstruction's choice,
+     * made to match the wired ops (buffers first, sizes last) and the parameter blocks of the
+     * shaders that would back them (unary.wgsl, copy.wgsl, softmax.wgsl, logsumexp.wgsl,
+     * layer_norm.wgsl, rms_norm.wgsl).  UNPINNED like the values at the top of this header: a
+     * maintainer with the real header either confirms them or builds this backend with
+     * -DLUX_CUDA_F32_SLOTS_NULL, which leaves these slots nullptr exactly as the WebGPU plugin does
+     * (the same functions stay reachable as lux_cuda_op_* symbols, qmatmul_ext.h).  The six
+     * reduction slots stay untyped and nullptr. */
     LuxBackendError (*op_add_f32)(LuxBackendContext*, LuxBackendBuffer* a, LuxBackendBuffer* b, LuxBackendBuffer* out, size_t n);
     LuxBackendError (*op_sub_f32)(LuxBackendContext*, LuxBackendBuffer* a, LuxBackendBuffer* b, LuxBackendBuffer* out, size_t n);
     LuxBackendError (*op_mul_f32)(LuxBackendContext*, LuxBackendBuffer* a, LuxBackendBuffer* b, LuxBackendBuffer* out, size_t n);
-    void* op_div_f32;
+    LuxBackendError (*op_div_f32)(LuxBackendContext*, LuxBackendBuffer* a, LuxBackendBuffer* b, LuxBackendBuffer* out, size_t n);
 
     LuxBackendError (*op_matmul_f32)(LuxBackendContext*, LuxBackendBuffer* a, LuxBackendBuffer* b, LuxBackendBuffer* out, int M, int K, int N);
-    void* op_transpose_f32;
+    /* out[cols, rows] = in[rows, cols]^T */
+    LuxBackendError (*op_transpose_f32)(LuxBackendContext*, LuxBackendBuffer* in, LuxBackendBuffer* out, int rows, int cols);
 
     void* op_reduce_sum_f32;
     void* op_reduce_max_f32;
@@ -121,23 +131,27 @@ typedef struct lux_gpu_backend_vtbl {
     void* op_reduce_sum_axis_f32;
     void* op_reduce_max_axis_f32;
 
-    void* op_softmax_f32;
-    void* op_log_softmax_f32;
+    /* over the last axis of [batch, dim] */
+    LuxBackendError (*op_softmax_f32)(LuxBackendContext*, LuxBackendBuffer* in, LuxBackendBuffer* out, size_t batch, size_t dim);
+    LuxBackendError (*op_log_softmax_f32)(LuxBackendContext*, LuxBackendBuffer* in, LuxBackendBuffer* out, size_t batch, size_t dim);
 
-    void* op_exp_f32;
-    void* op_log_f32;
-    void* op_sqrt_f32;
-    void* op_neg_f32;
-    void* op_abs_f32;
-    void* op_tanh_f32;
-    void* op_sigmoid_f32;
-    void* op_relu_f32;
-    void* op_gelu_f32;
+    LuxBackendError (*op_exp_f32)(LuxBackendContext*, LuxBackendBuffer* in, LuxBackendBuffer* out, size_t n);
+    LuxBackendError (*op_log_f32)(LuxBackendContext*, LuxBackendBuffer* in, LuxBackendBuffer* out, size_t n);
+    LuxBackendError (*op_sqrt_f32)(LuxBackendContext*, LuxBackendBuffer* in, LuxBackendBuffer* out, size_t n);
+    LuxBackendError (*op_neg_f32)(LuxBackendContext*, LuxBackendBuffer* in, LuxBackendBuffer* out, size_t n);
+    LuxBackendError (*op_abs_f32)(LuxBackendContext*, LuxBackendBuffer* in, LuxBackendBuffer* out, size_t n);
+    LuxBackendError (*op_tanh_f32)(LuxBackendContext*, LuxBackendBuffer* in, LuxBackendBuffer* out, size_t n);
+    LuxBackendError (*op_sigmoid_f32)(LuxBackendContext*, LuxBackendBuffer* in, LuxBackendBuffer* out, size_t n);
+    LuxBackendError (*op_relu_f32)(LuxBackendContext*, LuxBackendBuffer* in, LuxBackendBuffer* out, size_t n);
+    LuxBackendError (*op_gelu_f32)(LuxBackendContext*, LuxBackendBuffer* in, LuxBackendBuffer* out, size_t n);
 
-    void* op_copy_f32;
+    LuxBackendError (*op_copy_f32)(LuxBackendContext*, LuxBackendBuffer* src, LuxBackendBuffer* dst, size_t n);
 
-    void* op_layer_norm_f32;
-    void* op_rms_norm_f32;
+    /* over the last axis of [batch, dim]; gamma, beta, weight are [dim] */
+    LuxBackendError (*op_layer_norm_f32)(LuxBackendContext*, LuxBackendBuffer* in, LuxBackendBuffer* gamma, LuxBackendBuffer* beta,
+                                         LuxBackendBuffer* out, size_t batch, size_t dim, float eps);
+    LuxBackendError (*op_rms_norm_f32)(LuxBackendContext*, LuxBackendBuffer* in, LuxBackendBuffer* weight, LuxBackendBuffer* out,
+                                       size_t batch, size_t dim, float eps);
 
     /* NTT (:1773, 1918) */
     LuxBackendError (*op_ntt_forward)(LuxBackendContext*, uint64_t* data, size_t n, uint64_t modulus);

@@ -150,6 +150,38 @@ LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_qquantize(
     LuxBackendContext* ctx, const LuxQMatmulDesc* desc, LuxBackendBuffer* x,
     LuxBackendBuffer* w_out, LuxBackendBuffer* scales_out, LuxBackendBuffer* zeros_out);
 
+/* ---- the activation-quantized integer path (W8A8 / W4A8) ----------------------------------
+ * Exact integer arithmetic: results are bit-identical to the shaders.
+ *
+ * lux_cuda_dynamic_quantize: per-tensor symmetric quantization of n f32 activations
+ * (dynamic_quantize, kernels/wgsl/gpu/quantized_nax.wgsl:644-718): scale = max|x| / 127 (bits 8) or
+ * / 7 (bits 4), 1 if that is 0; q = clamp(round(x / scale)).  `out` receives n int8 bytes, or
+ * ceil(n / 2) bytes of int4 in the weight-only format's +8 offset (pack_nax_int4_sym_x8);
+ * `scale_out` one f32.
+ * lux_cuda_matmul_int8: C[M, N] (i32) = A[M, K] (int8) . B[K, N] (int8), both row-major
+ * (matmul_int8, kernels/wgsl/gpu/quantized.wgsl:497-555).
+ * lux_cuda_matmul_int4_int8: the same with A as packed int4, element 2j in the low nibble of byte
+ * j, nibbles in TWO'S COMPLEMENT (unpack_int4x8, quantized.wgsl:150-158 -- not the +8 offset of the
+ * weight-only format) (matmul_int4_int8, :590-647).
+ * lux_cuda_requantize_int32_to_int8: out[i] (i32) = clamp(i32(round(f32(in[i]) * input_scale /
+ * output_scale) + zero_point), -128, 127) (requantize_int32_to_int8, :573-588).
+ * Any shape; K % 16 == 0, N % 16 == 0 and 16-byte aligned buffers take the tensor-core kernel
+ * (mma.sync int8), everything else a plain one. */
+LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_dynamic_quantize(LuxBackendContext* ctx, LuxBackendBuffer* x, LuxBackendBuffer* out,
+                                                                LuxBackendBuffer* scale_out, size_t n, uint32_t bits);
+LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_matmul_int8(LuxBackendContext* ctx, LuxBackendBuffer* a, LuxBackendBuffer* b,
+                                                           LuxBackendBuffer* c, int M, int N, int K);
+LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_matmul_int4_int8(LuxBackendContext* ctx, LuxBackendBuffer* w4, LuxBackendBuffer* b,
+                                                                LuxBackendBuffer* c, int M, int N, int K);
+LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_requantize_int32_to_int8(LuxBackendContext* ctx, LuxBackendBuffer* in, LuxBackendBuffer* out,
+                                                                        size_t n, float input_scale, float output_scale,
+                                                                        int32_t output_zero_point);
+
+/* out = in / (1 + exp(-in)), element-wise f32 (silu, kernels/wgsl/gpu/unary.wgsl:375-381).  The
+ * backend vtable has slots for sigmoid, relu and gelu but none for SiLU, the activation of the
+ * Llama FFN, so it ships as a symbol beside the vtable like the quantized ops. */
+LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_op_silu_f32(LuxBackendContext* ctx, LuxBackendBuffer* in, LuxBackendBuffer* out, size_t n);
+
 /* Llama-style FFN on one GPU or one tensor-parallel shard:
  *   h[M, I] = silu(x.gate^T) * (x.up^T)    W_gate_up [2*I, K]  (gate rows, then up rows)
  *   y[M, H] = h . dequant(W_down)^T        W_down    [H, I]

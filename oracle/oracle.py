@@ -60,6 +60,14 @@ def lib() -> C.CDLL:
         L.orc_qmatmul.argtypes = [i32, i32, i32, i32, i32, vp, i32, vp, vp, i32, vp, vp, i32, i32, i32, i32]
         L.orc_swiglu.argtypes = [i32, i32, vp, i32, vp, i32]
         L.orc_num_procs.restype = i32
+        L.orc_unary_f32.argtypes = [i32, vp, vp, C.c_size_t]
+        L.orc_transpose_f32.argtypes = [vp, vp, i32, i32]
+        L.orc_softmax_f32.argtypes = [vp, vp, C.c_size_t, C.c_size_t, i32]
+        L.orc_layer_norm_f32.argtypes = [vp, vp, vp, vp, C.c_size_t, C.c_size_t, f32]
+        L.orc_rms_norm_f32.argtypes = [vp, vp, vp, C.c_size_t, C.c_size_t, f32]
+        L.orc_matmul_int.argtypes = [i32, i32, i32, i32, vp, vp, vp]
+        L.orc_requantize_int32_to_int8.argtypes = [vp, vp, C.c_size_t, f32, f32, i32]
+        L.orc_dynamic_quantize.argtypes = [vp, C.c_size_t, i32, vp, vp]
         L.orc_compute_group_scales.argtypes = [vp, C.c_size_t, i32, i32, vp]
         L.orc_quantize.argtypes = [vp, C.c_size_t, i32, i32, vp, vp]
         _lib = L
@@ -233,6 +241,48 @@ def tp_mlp(x, shards, group: int = 128, fused: bool = True, w_round: int = F32) 
     return total
 
 
+# -- f32 tensor ops (oracle/tensor_ops_oracle.c) ---------------------------------------
+
+UNARY_OPS = {"exp": 0, "log": 1, "sqrt": 2, "neg": 3, "abs": 4, "tanh": 5, "sigmoid": 6, "relu": 7, "gelu": 8,
+             "silu": 9, "copy": 10}
+
+
+def unary_f32(op: str, x: np.ndarray) -> np.ndarray:
+    x = np.ascontiguousarray(x, np.float32)
+    out = np.empty_like(x)
+    assert lib().orc_unary_f32(UNARY_OPS[op], _ptr(x), _ptr(out), x.size) == 0
+    return out
+
+
+def transpose_f32(x: np.ndarray) -> np.ndarray:
+    x = np.ascontiguousarray(x, np.float32)
+    out = np.empty((x.shape[1], x.shape[0]), np.float32)
+    lib().orc_transpose_f32(_ptr(x), _ptr(out), x.shape[0], x.shape[1])
+    return out
+
+
+def softmax_f32(x: np.ndarray, log: bool = False) -> np.ndarray:
+    x = np.ascontiguousarray(x, np.float32)
+    out = np.empty_like(x)
+    lib().orc_softmax_f32(_ptr(x), _ptr(out), x.shape[0], x.shape[1], int(log))
+    return out
+
+
+def layer_norm_f32(x, gamma, beta, eps: float) -> np.ndarray:
+    x = np.ascontiguousarray(x, np.float32)
+    out = np.empty_like(x)
+    lib().orc_layer_norm_f32(_ptr(x), _ptr(np.ascontiguousarray(gamma, np.float32)), _ptr(np.ascontiguousarray(beta, np.float32)),
+                             _ptr(out), x.shape[0], x.shape[1], eps)
+    return out
+
+
+def rms_norm_f32(x, weight, eps: float) -> np.ndarray:
+    x = np.ascontiguousarray(x, np.float32)
+    out = np.empty_like(x)
+    lib().orc_rms_norm_f32(_ptr(x), _ptr(np.ascontiguousarray(weight, np.float32)), _ptr(out), x.shape[0], x.shape[1], eps)
+    return out
+
+
 # -- quantize side ---------------------------------------------------------------------
 
 NAX_INT4_SYM, NAX_INT4_ASYM, NAX_INT8_SYM = 0, 1, 2          # quantized_nax.wgsl:31-33
@@ -296,6 +346,33 @@ def quantize(x: np.ndarray, bits: int, group: int, symmetric: bool, scale_code: 
             zp = np.concatenate([zp, np.zeros((N, 1), np.uint8)], axis=1)
         zeros = (zp[:, 0::2] | (zp[:, 1::2] << 4)).astype(np.uint8)
     return w, scales, zeros
+
+
+# -- activation-quantized integer path --------------------------------------------------
+
+def matmul_int(a: np.ndarray, b: np.ndarray, M: int, N: int, K: int, a_bits: int = 8) -> np.ndarray:
+    """C[M, N] i32 = A[M, K] . B[K, N]: A int8 (a_bits 8) or packed two's-complement int4 bytes (a_bits 4)."""
+    a = np.ascontiguousarray(a).view(np.uint8)
+    b = np.ascontiguousarray(b, np.int8)
+    c = np.empty((M, N), np.int32)
+    assert lib().orc_matmul_int(M, N, K, a_bits, _ptr(a), _ptr(b), _ptr(c)) == 0
+    return c
+
+
+def requantize_int32_to_int8(x: np.ndarray, input_scale: float, output_scale: float, zero_point: int) -> np.ndarray:
+    x = np.ascontiguousarray(x, np.int32)
+    out = np.empty_like(x)
+    lib().orc_requantize_int32_to_int8(_ptr(x), _ptr(out), x.size, input_scale, output_scale, zero_point)
+    return out
+
+
+def dynamic_quantize(x: np.ndarray, bits: int = 8):
+    """(packed bytes, scale): per-tensor symmetric quantization of activations."""
+    x = np.ascontiguousarray(x, np.float32).ravel()
+    out = np.empty(x.size if bits == 8 else (x.size + 1) // 2, np.uint8)
+    scale = np.zeros(1, np.float32)
+    assert lib().orc_dynamic_quantize(_ptr(x), x.size, bits, _ptr(out), _ptr(scale)) == 0
+    return out, float(scale[0])
 
 
 def rel_l2(a: np.ndarray, ref: np.ndarray) -> float:

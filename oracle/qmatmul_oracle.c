@@ -463,3 +463,76 @@ int orc_quantize(const float* in, size_t size, int group_size, int format, const
     }
     return 0;
 }
+
+/* ------------------------------------------------------------------------------------
+ * Activation-quantized integer path (gpu/quantized.wgsl, gpu/quantized_nax.wgsl)
+ * ---------------------------------------------------------------------------------- */
+
+/* unpack_int4x8, kernels/wgsl/gpu/quantized.wgsl:150-158: TWO'S COMPLEMENT nibbles ("if (val >= 8)
+ * val -= 16"), unlike the +8 offset of the weight-only format above. */
+void orc_unpack_int4x8_twos(uint32_t packed, int32_t out[8]) {
+    for (uint32_t i = 0; i < 8u; i++) {
+        int32_t val = (int32_t)((packed >> (i * 4u)) & 0xFu);
+        if (val >= 8) val -= 16;
+        out[i] = val;
+    }
+}
+
+/* matmul_int8 (quantized.wgsl:497-555) and matmul_int4_int8 (:590-647): C[M,N] (i32) = A[M,K] . B[K,N].
+ * A is read as element flat_idx = row*K + col of a flat packed array (four int8 or eight int4 per
+ * u32); B is int8, row-major [K, N].  a_bits = 8 or 4. */
+int orc_matmul_int(int M, int N, int K, int a_bits, const uint8_t* a, const int8_t* b, int32_t* c) {
+    if (M <= 0 || N <= 0 || K <= 0 || (a_bits != 4 && a_bits != 8)) return -1;
+    #pragma omp parallel for schedule(static)
+    for (int r = 0; r < M; r++)
+        for (int col = 0; col < N; col++) {
+            int32_t sum = 0;
+            for (int k = 0; k < K; k++) {
+                const size_t flat = (size_t)r * K + k;
+                int32_t av;
+                if (a_bits == 8) {
+                    av = (int32_t)((a[flat]) & 0xFFu);
+                    if (av >= 128) av -= 256;                    /* unpack_int8x4, :167-178 */
+                } else {
+                    av = (int32_t)((a[flat >> 1] >> ((flat & 1) * 4)) & 0xFu);
+                    if (av >= 8) av -= 16;
+                }
+                sum += av * (int32_t)b[(size_t)k * N + col];
+            }
+            c[(size_t)r * N + col] = sum;
+        }
+    return 0;
+}
+
+/* requantize_int32_to_int8, quantized.wgsl:573-588 (the output array holds i32 values in [-128, 127]) */
+int orc_requantize_int32_to_int8(const int32_t* in, int32_t* out, size_t n, float input_scale, float output_scale, int32_t zp) {
+    for (size_t i = 0; i < n; i++) {
+        const float v = (float)in[i] * input_scale;
+        const float r = rintf(v / output_scale) + (float)zp;
+        out[i] = clampi(wgsl_i32(r), -128, 127);
+    }
+    return 0;
+}
+
+/* dynamic_quantize, quantized_nax.wgsl:644-718: ONE scale for the whole tensor, max|x| / 127 (bits 8)
+ * or / 7 (bits 4), 1 if that is 0; q = clamp(i32(round(x / scale)), MIN, MAX); int8 packed four per
+ * word, int4 as pack_nax_int4_sym_x8 (stored nibble = q + 8, padding elements q = 0).  `out` holds
+ * n bytes (bits 8) or ceil(n / 2) bytes (bits 4). */
+int orc_dynamic_quantize(const float* x, size_t n, int bits, uint8_t* out, float* scale_out) {
+    if (bits != 4 && bits != 8) return -1;
+    float mx = 0.0f;
+    for (size_t i = 0; i < n; i++) { const float a = fabsf(x[i]); mx = mx > a ? mx : a; }
+    float scale = bits == 4 ? mx / 7.0f : mx / 127.0f;
+    if (scale == 0.0f) scale = 1.0f;
+    *scale_out = scale;
+    if (bits == 8) {
+        for (size_t i = 0; i < n; i++) out[i] = (uint8_t)(clampi(wgsl_i32(rintf(x[i] / scale)), -128, 127) & 0xFF);
+    } else {
+        for (size_t b = 0; b < (n + 1) / 2; b++) {
+            const int32_t lo = clampi(wgsl_i32(rintf(x[2 * b] / scale)), -8, 7);
+            const int32_t hi = 2 * b + 1 < n ? clampi(wgsl_i32(rintf(x[2 * b + 1] / scale)), -8, 7) : 0;
+            out[b] = (uint8_t)(((uint32_t)(lo + 8) & 0xFu) | (((uint32_t)(hi + 8) & 0xFu) << 4));
+        }
+    }
+    return 0;
+}

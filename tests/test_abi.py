@@ -12,13 +12,16 @@ from webgpu_b200 import backend as B
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
-# Slots the reference's own vtable leaves nullptr (src/webgpu_plugin.cpp:4044-4072).
+# Of the 22 slots the reference's own vtable leaves nullptr (src/webgpu_plugin.cpp:4044-4072) this
+# backend wires the sixteen either side of a linear layer; the six reductions stay nullptr.
 REFERENCE_NULL_SLOTS = {
-    "op_div_f32", "op_transpose_f32", "op_reduce_sum_f32", "op_reduce_max_f32", "op_reduce_min_f32",
-    "op_reduce_mean_f32", "op_reduce_sum_axis_f32", "op_reduce_max_axis_f32", "op_softmax_f32",
-    "op_log_softmax_f32", "op_exp_f32", "op_log_f32", "op_sqrt_f32", "op_neg_f32", "op_abs_f32",
-    "op_tanh_f32", "op_sigmoid_f32", "op_relu_f32", "op_gelu_f32", "op_copy_f32", "op_layer_norm_f32",
-    "op_rms_norm_f32",
+    "op_reduce_sum_f32", "op_reduce_max_f32", "op_reduce_min_f32",
+    "op_reduce_mean_f32", "op_reduce_sum_axis_f32", "op_reduce_max_axis_f32",
+}
+WIRED_F32_SLOTS = {
+    "op_div_f32", "op_transpose_f32", "op_softmax_f32", "op_log_softmax_f32", "op_exp_f32", "op_log_f32",
+    "op_sqrt_f32", "op_neg_f32", "op_abs_f32", "op_tanh_f32", "op_sigmoid_f32", "op_relu_f32", "op_gelu_f32",
+    "op_copy_f32", "op_layer_norm_f32", "op_rms_norm_f32",
 }
 
 
@@ -63,6 +66,11 @@ def test_vtable_slots(backend):
                   "buffer_copy_from_host", "buffer_get_host_ptr", "op_add_f32", "op_sub_f32", "op_mul_f32",
                   "op_matmul_f32", "op_ntt_forward", "op_msm", "op_kzg_verify", "op_ecrecover_batch"):
         assert getattr(raw, field), field
+    for field in WIRED_F32_SLOTS:
+        assert getattr(raw, field), field
+        assert backend.vt[field] is not None, field
+    assert backend.vt["op_exp_f32"](None, None, None, 4) == B.INVALID_ARGUMENT
+    assert backend.vt["op_rms_norm_f32"](None, None, None, None, 1, 8, 1e-6) == B.INVALID_ARGUMENT
     # the post-quantum / threshold / Schnorr batches are callable stubs in the reference
     # (src/webgpu_plugin.cpp:3973-4016, 4110-4122), so a loader may call them without a null check
     for field in B.VTBL_FIELDS[56:]:

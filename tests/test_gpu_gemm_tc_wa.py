@@ -76,6 +76,26 @@ def test_wa_groups_and_stages(ctx, backend, groups, stages):
     assert ctx.last_device_status() == 0
 
 
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+@pytest.mark.parametrize("splitk", [1, 2, 4])
+@pytest.mark.parametrize("narrow", [1, 2])
+@pytest.mark.parametrize("M,N,K", [(16, 256, 1024), (33, 128, 512), (64, 384, 512), (40, 128, 2048)])
+def test_wa_narrow_and_wide_tiles_for_small_batches(ctx, backend, dtype, splitk, narrow, M, N, K):
+    """Batches of up to 64 rows in both tile widths (narrow: 64 accumulator columns, 256 TMEM columns,
+    two CTAs per SM; wide: 256 columns, one CTA per SM), every K split, plain and SwiGLU."""
+    x = synth.activations(M, K, dtype, 47, f"wan.{M}.{K}")
+    layer = synth.int4_layer(N, K, 47, f"wan.{N}.{K}")
+    with _Tuned(backend, gemm_tc_kernel=2, gemm_tc_splitk=splitk, gemm_wa_narrow=narrow):
+        y = _run(ctx, x, layer)
+        assert backend.last_kernel_name().startswith("lux_qgemm_i4_tc_wa")
+        h = _run_swiglu(ctx, x, layer)
+    assert orc.rel_l2(y, _oracle(x, layer)) < TOL_16
+    code = orc.dtype_code(x)
+    gu = orc.qmatmul(x, *layer.triple, bits=4, group=128, y_code=orc.F32, w_round=code)
+    assert orc.rel_l2(h, orc.swiglu(gu, h_code=code)) < TOL_16
+    assert ctx.last_device_status() == 0
+
+
 def test_wa_symmetric_weights(ctx, backend):
     """No zero-point table: the symmetric special case (zero-point 8)."""
     x = synth.activations(256, 512, "f16", 43, "was.x")

@@ -103,7 +103,8 @@ class KernelAttributes(C.Structure):
 EXPORTED_SYMBOLS = [
     "lux_gpu_backend_init",
     "lux_cuda_qmatmul", "lux_cuda_qmatmul_host", "lux_cuda_qmatmul_route", "lux_cuda_qdequant",
-    "lux_cuda_qunpack", "lux_cuda_qquantize", "lux_cuda_qmlp", "lux_cuda_qmlp_noalloc", "lux_cuda_context_set_stream", "lux_cuda_context_get_stream",
+    "lux_cuda_qunpack", "lux_cuda_qquantize", "lux_cuda_op_silu_f32", "lux_cuda_dynamic_quantize",
+    "lux_cuda_matmul_int8", "lux_cuda_matmul_int4_int8", "lux_cuda_requantize_int32_to_int8", "lux_cuda_qmlp", "lux_cuda_qmlp_noalloc", "lux_cuda_context_set_stream", "lux_cuda_context_get_stream",
     "lux_cuda_buffer_wrap", "lux_cuda_buffer_device_ptr", "lux_cuda_buffer_size",
     "lux_cuda_launch_count", "lux_cuda_last_kernel_name", "lux_cuda_tune_set", "lux_cuda_last_device_status",
     "lux_cuda_kernel_get", "lux_cuda_kernel_destroy", "lux_cuda_kernel_entry_point",
@@ -144,6 +145,17 @@ _SIGS = {   # vtable slot -> (restype, argtypes); unwired slots are not callable
     "op_sub_f32": (_int, [_vp, _vp, _vp, _vp, _sz]),
     "op_mul_f32": (_int, [_vp, _vp, _vp, _vp, _sz]),
     "op_matmul_f32": (_int, [_vp, _vp, _vp, _vp, _int, _int, _int]),
+    "op_div_f32": (_int, [_vp, _vp, _vp, _vp, _sz]),
+    "op_transpose_f32": (_int, [_vp, _vp, _vp, _int, _int]),
+    "op_softmax_f32": (_int, [_vp, _vp, _vp, _sz, _sz]),
+    "op_log_softmax_f32": (_int, [_vp, _vp, _vp, _sz, _sz]),
+    "op_exp_f32": (_int, [_vp, _vp, _vp, _sz]), "op_log_f32": (_int, [_vp, _vp, _vp, _sz]),
+    "op_sqrt_f32": (_int, [_vp, _vp, _vp, _sz]), "op_neg_f32": (_int, [_vp, _vp, _vp, _sz]),
+    "op_abs_f32": (_int, [_vp, _vp, _vp, _sz]), "op_tanh_f32": (_int, [_vp, _vp, _vp, _sz]),
+    "op_sigmoid_f32": (_int, [_vp, _vp, _vp, _sz]), "op_relu_f32": (_int, [_vp, _vp, _vp, _sz]),
+    "op_gelu_f32": (_int, [_vp, _vp, _vp, _sz]), "op_copy_f32": (_int, [_vp, _vp, _vp, _sz]),
+    "op_layer_norm_f32": (_int, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, C.c_float]),
+    "op_rms_norm_f32": (_int, [_vp, _vp, _vp, _vp, _sz, _sz, C.c_float]),
     "op_ntt_forward": (_int, [_vp, _vp, _sz, C.c_uint64]),
     "op_msm": (_int, [_vp, _vp, _vp, _vp, _sz, _int]),
     "op_mldsa_verify_batch": (_int, [_vp, _vp, _vp, _vp, _vp, _sz]),
@@ -199,6 +211,11 @@ class Backend:
         L.lux_cuda_qdequant.argtypes = [_vp, C.POINTER(QMatmulDesc), _vp, _vp, _vp, _vp]
         L.lux_cuda_qunpack.argtypes = [_vp, C.POINTER(QMatmulDesc), _vp, _vp, _vp]
         L.lux_cuda_qquantize.argtypes = [_vp, C.POINTER(QMatmulDesc), _vp, _vp, _vp, _vp]
+        L.lux_cuda_op_silu_f32.argtypes = [_vp, _vp, _vp, _sz]
+        L.lux_cuda_dynamic_quantize.argtypes = [_vp, _vp, _vp, _vp, _sz, C.c_uint32]
+        L.lux_cuda_matmul_int8.argtypes = [_vp, _vp, _vp, _vp, _int, _int, _int]
+        L.lux_cuda_matmul_int4_int8.argtypes = [_vp, _vp, _vp, _vp, _int, _int, _int]
+        L.lux_cuda_requantize_int32_to_int8.argtypes = [_vp, _vp, _vp, _sz, C.c_float, C.c_float, C.c_int32]
         L.lux_cuda_qmlp.argtypes = [_vp, C.POINTER(QMlpDesc)] + [_vp] * 9
         L.lux_cuda_qmlp_noalloc.argtypes = [_vp, C.POINTER(QMlpDesc)] + [_vp] * 8
         L.lux_cuda_peer_comm_create.restype = C.c_int
@@ -359,6 +376,7 @@ class DeviceQLayer:
 class Context:
     def __init__(self, backend: Backend, handle: int):
         self.backend, self.handle = backend, handle
+        self._host_calls = {}
 
     # vtable wrappers
     def destroy(self) -> None:
@@ -407,6 +425,28 @@ class Context:
     def binary_f32(self, op: str, a: Buffer, b: Buffer, out: Buffer, n: int) -> None:
         _check(self.backend.vt[f"op_{op}_f32"](self.handle, a.handle, b.handle, out.handle, n), f"op_{op}_f32")
 
+    def unary_f32(self, op: str, x: Buffer, out: Buffer, n: int) -> None:
+        """exp, log, sqrt, neg, abs, tanh, sigmoid, relu, gelu, copy through the vtable; silu through its symbol."""
+        if op == "silu":
+            _check(self.backend.lib.lux_cuda_op_silu_f32(self.handle, x.handle, out.handle, n), "lux_cuda_op_silu_f32")
+        else:
+            _check(self.backend.vt[f"op_{op}_f32"](self.handle, x.handle, out.handle, n), f"op_{op}_f32")
+
+    def transpose_f32(self, x: Buffer, out: Buffer, rows: int, cols: int) -> None:
+        _check(self.backend.vt["op_transpose_f32"](self.handle, x.handle, out.handle, rows, cols), "op_transpose_f32")
+
+    def softmax_f32(self, x: Buffer, out: Buffer, batch: int, dim: int, log: bool = False) -> None:
+        name = "op_log_softmax_f32" if log else "op_softmax_f32"
+        _check(self.backend.vt[name](self.handle, x.handle, out.handle, batch, dim), name)
+
+    def layer_norm_f32(self, x: Buffer, gamma: Buffer, beta: Buffer, out: Buffer, batch: int, dim: int, eps: float) -> None:
+        _check(self.backend.vt["op_layer_norm_f32"](self.handle, x.handle, gamma.handle, beta.handle, out.handle, batch, dim, eps),
+               "op_layer_norm_f32")
+
+    def rms_norm_f32(self, x: Buffer, weight: Buffer, out: Buffer, batch: int, dim: int, eps: float) -> None:
+        _check(self.backend.vt["op_rms_norm_f32"](self.handle, x.handle, weight.handle, out.handle, batch, dim, eps),
+               "op_rms_norm_f32")
+
     def matmul_f32(self, a: Buffer, b: Buffer, out: Buffer, M: int, K: int, N: int) -> None:
         _check(self.backend.vt["op_matmul_f32"](self.handle, a.handle, b.handle, out.handle, M, K, N), "op_matmul_f32")
 
@@ -428,17 +468,27 @@ class Context:
 
     def qmatmul_host(self, x: np.ndarray, L: DeviceQLayer, y_dtype: int | None = None, flags: int = 0,
                      out: np.ndarray | None = None) -> np.ndarray:
-        x = np.ascontiguousarray(x)
+        if not x.flags.c_contiguous:
+            x = np.ascontiguousarray(x)
         M = x.shape[0]
         xd = np_dtype_code(x)
         yd = xd if y_dtype is None else y_dtype
-        n_out = L.N // 2 if flags & FLAG_SWIGLU else L.N
         if out is None:
-            out = np.empty((M, n_out), _NP_OF[yd])
-        d = self._desc(L, M, xd, yd, flags)
-        _check(self.backend.lib.lux_cuda_qmatmul_host(self.handle, C.byref(d), x.ctypes.data, L.w.handle,
-                                                      L.scales.handle, L.zeros.handle if L.zeros else None,
-                                                      out.ctypes.data), "lux_cuda_qmatmul_host")
+            out = np.empty((M, L.N // 2 if flags & FLAG_SWIGLU else L.N), _NP_OF[yd])
+        # the descriptor and the weight handles of a (layer, batch, types) combination never change:
+        # a decode loop pays for building them once
+        key = (id(L), M, xd, yd, flags)
+        hit = self._host_calls.get(key)
+        if hit is None:
+            d = self._desc(L, M, xd, yd, flags)
+            hit = (C.byref(d), d, L.w.handle, L.scales.handle, L.zeros.handle if L.zeros else None, L)
+            if len(self._host_calls) > 256:
+                self._host_calls.clear()
+            self._host_calls[key] = hit
+        code = self.backend.lib.lux_cuda_qmatmul_host(self.handle, hit[0], x.ctypes.data, hit[2], hit[3], hit[4],
+                                                      out.ctypes.data)
+        if code != OK:
+            raise BackendError(code, "lux_cuda_qmatmul_host")
         return out
 
     def qdequant(self, L: DeviceQLayer, out_dtype: int = F32) -> np.ndarray:
@@ -477,6 +527,19 @@ class Context:
         _check(self.backend.lib.lux_cuda_qquantize(self.handle, C.byref(d), xb.handle, w.handle, sc.handle,
                                                    z.handle if z else None), "lux_cuda_qquantize")
         return DeviceQLayer(bits, group, N, K, w, sc, z, scale_dtype)
+
+    # activation-quantized integer path
+    def dynamic_quantize(self, x: Buffer, out: Buffer, scale: Buffer, n: int, bits: int = 8) -> None:
+        _check(self.backend.lib.lux_cuda_dynamic_quantize(self.handle, x.handle, out.handle, scale.handle, n, bits),
+               "lux_cuda_dynamic_quantize")
+
+    def matmul_int8(self, a: Buffer, b: Buffer, c: Buffer, M: int, N: int, K: int, a_bits: int = 8) -> None:
+        fn = self.backend.lib.lux_cuda_matmul_int8 if a_bits == 8 else self.backend.lib.lux_cuda_matmul_int4_int8
+        _check(fn(self.handle, a.handle, b.handle, c.handle, M, N, K), "lux_cuda_matmul_int8")
+
+    def requantize(self, x: Buffer, out: Buffer, n: int, input_scale: float, output_scale: float, zero_point: int) -> None:
+        _check(self.backend.lib.lux_cuda_requantize_int32_to_int8(self.handle, x.handle, out.handle, n, input_scale,
+                                                                  output_scale, zero_point), "lux_cuda_requantize_int32_to_int8")
 
     def qmlp(self, x: Buffer, gate_up: DeviceQLayer, down: DeviceQLayer, h: Buffer, y: Buffer, M: int,
              act_dtype: int, flags: int = 0) -> None:

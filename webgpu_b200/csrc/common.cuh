@@ -39,10 +39,12 @@ struct Context {
     uint32_t*      d_status = nullptr;      // device status word (0 = ok)
     uint32_t*      h_status = nullptr;      // pinned mirror
     void*          h_stage = nullptr;       // pinned staging for host-pointer ops
+    void*          d_stage_y = nullptr;     // the same buffer as the device sees it (null: not mapped)
     size_t         h_stage_bytes = 0;
     void*          d_stage = nullptr;       // device staging for host-pointer ops
     size_t         d_stage_bytes = 0;
     uint32_t       last_status = 0;
+    uint32_t*      d_absmax = nullptr;      // device word for lux_cuda_dynamic_quantize's tensor-wide max (allocated with the context)
     void*          d_splitk = nullptr;      // split-K exchange of the weights-in-TMEM GEMM: 128 KB per CTA pair,
     size_t         d_splitk_bytes = 0;      // allocated with the context (no entry point allocates for it)
     std::mutex     mu;                      // guards the staging buffers
@@ -105,6 +107,7 @@ struct Tunables {
     int gemv_units_pre = 0;      // units kernel: chunks requested per warp before its loop starts (default 1)
     int gemv_units_fx = 0;       // units kernel, batch <= 2: 0/1 block-fixed-point int8 variant, 2 f16 variant
     int gemv_units_warps = 0;    // fixed-point units kernels: 8 half-SM CTAs (where the plan fits), 0/16 whole-SM CTAs
+    int host_pageable = 0;       // host-pointer entry point: 0/1 hand x_host to the copy as it is (<= 64 KB), 2 stage it in pinned memory
     int gemv_units_planes = 0;   // fixed-point units kernels: byte planes of the activations, 3 or 4 (0 = 4 where it costs no FIFO depth)
     int gemm_tc_bn = 0;          // N tile of the tcgen05 GEMM
     int gemm_tc_stages = 0;
@@ -113,6 +116,8 @@ struct Tunables {
     int pdl = 0;                 // programmatic dependent launch of the persistent kernels: 0/1 on, 2 off
     int gemm_min_m = 0;          // smallest batch the weights-in-TMEM GEMM takes from the streaming kernels (0 = built-in)
     int gemm_tc_kernel = 0;      // 0 auto, 1 lux_qgemm_i4_tc, 2 lux_qgemm_i4_tc_wa wherever it applies
+    int gemm_wa_narrow = 0;      // weights-in-TMEM GEMM, batch <= 64: 0 narrow tile (two CTAs per SM) when the launch has more CTAs
+                                 // than SMs, 1 always, 2 never
     int gemm_tc_ma = 0;          // GEMM: batch tiles (128 rows) per CTA, 1 or 2 (0 = choose)
 };
 extern Tunables g_tune;
@@ -251,6 +256,27 @@ LuxBackendError launch_qgemv_i4_units(Context* ctx, const QArgs& a);    // NOT_S
 LuxBackendError launch_qgemm_i4_tc(Context* ctx, const QArgs& a);
 LuxBackendError launch_qgemm_i4_tc_wa(Context* ctx, const QArgs& a);    // NOT_SUPPORTED if the shape does not fit
 LuxBackendError launch_qdequant(Context* ctx, const QArgs& a, int bits);
+
+// tensor_ops.cu: the f32 slots the reference's shader library backs but its plugin leaves unwired
+LuxBackendError op_div_f32(LuxBackendContext*, LuxBackendBuffer* a, LuxBackendBuffer* b, LuxBackendBuffer* out, size_t n);
+LuxBackendError op_transpose_f32(LuxBackendContext*, LuxBackendBuffer* in, LuxBackendBuffer* out, int rows, int cols);
+LuxBackendError op_softmax_f32(LuxBackendContext*, LuxBackendBuffer* in, LuxBackendBuffer* out, size_t batch, size_t dim);
+LuxBackendError op_log_softmax_f32(LuxBackendContext*, LuxBackendBuffer* in, LuxBackendBuffer* out, size_t batch, size_t dim);
+LuxBackendError op_exp_f32(LuxBackendContext*, LuxBackendBuffer* in, LuxBackendBuffer* out, size_t n);
+LuxBackendError op_log_f32(LuxBackendContext*, LuxBackendBuffer* in, LuxBackendBuffer* out, size_t n);
+LuxBackendError op_sqrt_f32(LuxBackendContext*, LuxBackendBuffer* in, LuxBackendBuffer* out, size_t n);
+LuxBackendError op_neg_f32(LuxBackendContext*, LuxBackendBuffer* in, LuxBackendBuffer* out, size_t n);
+LuxBackendError op_abs_f32(LuxBackendContext*, LuxBackendBuffer* in, LuxBackendBuffer* out, size_t n);
+LuxBackendError op_tanh_f32(LuxBackendContext*, LuxBackendBuffer* in, LuxBackendBuffer* out, size_t n);
+LuxBackendError op_sigmoid_f32(LuxBackendContext*, LuxBackendBuffer* in, LuxBackendBuffer* out, size_t n);
+LuxBackendError op_relu_f32(LuxBackendContext*, LuxBackendBuffer* in, LuxBackendBuffer* out, size_t n);
+LuxBackendError op_gelu_f32(LuxBackendContext*, LuxBackendBuffer* in, LuxBackendBuffer* out, size_t n);
+LuxBackendError op_copy_f32(LuxBackendContext*, LuxBackendBuffer* src, LuxBackendBuffer* dst, size_t n);
+LuxBackendError op_silu_f32(LuxBackendContext*, LuxBackendBuffer* in, LuxBackendBuffer* out, size_t n);
+LuxBackendError op_layer_norm_f32(LuxBackendContext*, LuxBackendBuffer* in, LuxBackendBuffer* gamma, LuxBackendBuffer* beta,
+                                  LuxBackendBuffer* out, size_t batch, size_t dim, float eps);
+LuxBackendError op_rms_norm_f32(LuxBackendContext*, LuxBackendBuffer* in, LuxBackendBuffer* weight, LuxBackendBuffer* out,
+                                size_t batch, size_t dim, float eps);
 LuxBackendError launch_qunpack(Context* ctx, const QArgs& a, int bits);
 
 // Encodes a tiled uint8 tensor map (CUtensorMap, 128 bytes, 64-byte aligned) through the

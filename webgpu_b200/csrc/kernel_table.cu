@@ -21,6 +21,8 @@ const void* kernel_addr_qgemv_i4_units_fx();
 const void* kernel_addr_peer_allreduce_push();
 const void* kernel_addr_qdequant_i4();
 const void* kernel_addr_qdequant_i8();
+const void* kernel_addr_matmul_int8();
+const void* kernel_addr_matmul_int4_int8();
 const void* kernel_addr_qquantize_i4();
 const void* kernel_addr_qquantize_i8();
 const void* kernel_addr_qgemm_i4_tc_bf16();
@@ -52,6 +54,8 @@ const Entry kTable[] = {
     {"lux_peer_allreduce_push",    luxcuda::kernel_addr_peer_allreduce_push, 1024, 1, 1},
     {"lux_qdequant_i4_g128",       luxcuda::kernel_addr_qdequant_i4,        256, 1, 1},
     {"lux_qdequant_i8_g32",        luxcuda::kernel_addr_qdequant_i8,        256, 1, 1},
+    {"lux_matmul_int8",            luxcuda::kernel_addr_matmul_int8,        256, 1, 1},
+    {"lux_matmul_int4_int8",       luxcuda::kernel_addr_matmul_int4_int8,   256, 1, 1},
     {"lux_qquantize_i4_g128",      luxcuda::kernel_addr_qquantize_i4,       256, 1, 1},
     {"lux_qquantize_i8_g32",       luxcuda::kernel_addr_qquantize_i8,       256, 1, 1},
     {"lux_qgemm_i4_tc_bf16",       luxcuda::kernel_addr_qgemm_i4_tc_bf16,   320, 1, 1},

@@ -103,6 +103,7 @@ static LuxBackendContext* cuda_create_context(int device_index) {
     // stream wait without another copy.
     ok = ok && cudaHostAlloc(&ctx->h_status, sizeof(uint32_t), cudaHostAllocMapped) == cudaSuccess;
     ok = ok && cudaHostGetDevicePointer((void**)&ctx->d_status, ctx->h_status, 0) == cudaSuccess;
+    ok = ok && cudaMalloc(&ctx->d_absmax, sizeof(uint32_t)) == cudaSuccess;
     // Split-K partial sums of the tensor-core GEMM: one 128 KB slot per CTA pair, at most one pair
     // per two SMs.  Allocated here so that no matmul entry point ever allocates device memory.
     if (ok) {
@@ -114,6 +115,7 @@ static LuxBackendContext* cuda_create_context(int device_index) {
     if (!ok) {
         cudaGetLastError();
         if (ctx->d_splitk) cudaFree(ctx->d_splitk);
+        if (ctx->d_absmax) cudaFree(ctx->d_absmax);
         if (ctx->h_status) cudaFreeHost(ctx->h_status);
         if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
         delete ctx;
@@ -134,6 +136,7 @@ static void cuda_destroy_context(LuxBackendContext* context) {
     if (ctx->h_stage) cudaFreeHost(ctx->h_stage);
     if (ctx->d_stage) cudaFree(ctx->d_stage);
     if (ctx->d_splitk) cudaFree(ctx->d_splitk);
+    if (ctx->d_absmax) cudaFree(ctx->d_absmax);
     if (ctx->h_status) cudaFreeHost(ctx->h_status);
     if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
     cudaGetLastError();
@@ -328,6 +331,13 @@ static LuxBackendError ns_cggmp21_sign(LuxBackendContext*, const uint8_t* const*
 // ---------------------------------------------------------------------------------
 // Vtable, in the reference's slot order (src/webgpu_plugin.cpp:4022-4123)
 // ---------------------------------------------------------------------------------
+// The f32 slots the WebGPU plugin leaves nullptr: wired here with this reconstruction's signatures
+// (see backend_plugin.h), or left nullptr like the reference with -DLUX_CUDA_F32_SLOTS_NULL.
+#ifdef LUX_CUDA_F32_SLOTS_NULL
+#define LUX_F32_SLOT(fn) nullptr
+#else
+#define LUX_F32_SLOT(fn) luxcuda::fn
+#endif
 static const lux_gpu_backend_vtbl cuda_vtbl = {
     .create_context  = cuda_create_context,
     .destroy_context = cuda_destroy_context,
@@ -346,10 +356,10 @@ static const lux_gpu_backend_vtbl cuda_vtbl = {
     .op_add_f32 = cuda_op_add_f32,
     .op_sub_f32 = cuda_op_sub_f32,
     .op_mul_f32 = cuda_op_mul_f32,
-    .op_div_f32 = nullptr,
+    .op_div_f32 = LUX_F32_SLOT(op_div_f32),
 
     .op_matmul_f32    = cuda_op_matmul_f32,
-    .op_transpose_f32 = nullptr,
+    .op_transpose_f32 = LUX_F32_SLOT(op_transpose_f32),
 
     .op_reduce_sum_f32      = nullptr,
     .op_reduce_max_f32      = nullptr,
@@ -358,23 +368,23 @@ static const lux_gpu_backend_vtbl cuda_vtbl = {
     .op_reduce_sum_axis_f32 = nullptr,
     .op_reduce_max_axis_f32 = nullptr,
 
-    .op_softmax_f32     = nullptr,
-    .op_log_softmax_f32 = nullptr,
+    .op_softmax_f32     = LUX_F32_SLOT(op_softmax_f32),
+    .op_log_softmax_f32 = LUX_F32_SLOT(op_log_softmax_f32),
 
-    .op_exp_f32     = nullptr,
-    .op_log_f32     = nullptr,
-    .op_sqrt_f32    = nullptr,
-    .op_neg_f32     = nullptr,
-    .op_abs_f32     = nullptr,
-    .op_tanh_f32    = nullptr,
-    .op_sigmoid_f32 = nullptr,
-    .op_relu_f32    = nullptr,
-    .op_gelu_f32    = nullptr,
+    .op_exp_f32     = LUX_F32_SLOT(op_exp_f32),
+    .op_log_f32     = LUX_F32_SLOT(op_log_f32),
+    .op_sqrt_f32    = LUX_F32_SLOT(op_sqrt_f32),
+    .op_neg_f32     = LUX_F32_SLOT(op_neg_f32),
+    .op_abs_f32     = LUX_F32_SLOT(op_abs_f32),
+    .op_tanh_f32    = LUX_F32_SLOT(op_tanh_f32),
+    .op_sigmoid_f32 = LUX_F32_SLOT(op_sigmoid_f32),
+    .op_relu_f32    = LUX_F32_SLOT(op_relu_f32),
+    .op_gelu_f32    = LUX_F32_SLOT(op_gelu_f32),
 
-    .op_copy_f32 = nullptr,
+    .op_copy_f32 = LUX_F32_SLOT(op_copy_f32),
 
-    .op_layer_norm_f32 = nullptr,
-    .op_rms_norm_f32   = nullptr,
+    .op_layer_norm_f32 = LUX_F32_SLOT(op_layer_norm_f32),
+    .op_rms_norm_f32   = LUX_F32_SLOT(op_rms_norm_f32),
 
     .op_ntt_forward = ns_ntt,
     .op_ntt_inverse = ns_ntt,

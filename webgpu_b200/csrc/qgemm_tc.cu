@@ -31,6 +31,8 @@
 #include <cudaTypedefs.h>
 
 #include <algorithm>
+#include <cstring>
+#include <mutex>
 #include <type_traits>
 
 namespace luxcuda {
@@ -359,16 +361,39 @@ bool encode_2d(CUtensorMap* map, CUtensorMapDataType dt, size_t esz, const void*
 bool encode_tensor_map_u8(void* map, int rank, const void* base, const uint64_t* dims, const uint64_t* strides_bytes,
                           const uint32_t* box, bool swizzle128) {
     auto fn = get_encode_fn();
-    if (!fn) return false;
+    if (!fn || rank < 1 || rank > 5) return false;
+    // A decode loop encodes the same few maps over and over (one per layer and operand): the encoded
+    // 128 bytes depend on nothing but these arguments, so the last 64 are kept.
+    struct Key { const void* base; uint64_t d[5], st[4]; uint32_t b[5]; int rank; bool sw; };
+    struct Slot { Key key; alignas(64) CUtensorMap map; bool used; };
+    static Slot cache[64];
+    static unsigned next_slot = 0;
+    static std::mutex mu;
+    Key k;
+    std::memset(&k, 0, sizeof k);                      // padding too: the keys are compared bytewise
+    k.base = base; k.rank = rank; k.sw = swizzle128;
+    for (int i = 0; i < rank; i++) { k.d[i] = dims[i]; k.b[i] = box[i]; }
+    for (int i = 0; i + 1 < rank; i++) k.st[i] = strides_bytes[i];
+    std::lock_guard<std::mutex> lock(mu);
+    for (const Slot& sl : cache)
+        if (sl.used && std::memcmp(&sl.key, &k, sizeof k) == 0) {
+            std::memcpy(map, &sl.map, sizeof(CUtensorMap));
+            return true;
+        }
     cuuint64_t d[5], st[4];
     cuuint32_t b[5], es[5];
     for (int i = 0; i < rank; i++) { d[i] = dims[i]; b[i] = box[i]; es[i] = 1; }
     for (int i = 0; i + 1 < rank; i++) st[i] = strides_bytes[i];
-    CUresult r = fn(reinterpret_cast<CUtensorMap*>(map), CU_TENSOR_MAP_DATA_TYPE_UINT8, (cuuint32_t)rank,
+    Slot& sl = cache[next_slot++ % 64];
+    CUresult r = fn(&sl.map, CU_TENSOR_MAP_DATA_TYPE_UINT8, (cuuint32_t)rank,
                     const_cast<void*>(base), d, st, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS;
+    sl.used = r == CUDA_SUCCESS;
+    if (!sl.used) return false;
+    std::memcpy(&sl.key, &k, sizeof k);
+    std::memcpy(map, &sl.map, sizeof(CUtensorMap));
+    return true;
 }
 
 namespace {

@@ -44,18 +44,22 @@ namespace {
 
 using namespace tcptx;
 
-constexpr int WA_BN = 256;                 // batch rows per CTA = UMMA N = accumulator columns
-constexpr int WA_X_BYTES = WA_BN * 128;    // x tile of a stage: 256 rows x 64 K x 2 bytes
+// Two tile widths.  BN = 256 batch rows per CTA (= UMMA N = accumulator columns): one CTA per SM,
+// all 512 TMEM columns, 3 x 64 KB of x.  BN = 64 for batches of up to 64 rows: 256 TMEM columns
+// (accumulator [0, 64) + A units [64, 256)) and 3 x 16 KB of x, so that TWO CTAs share an SM.  Below
+// ~128 batch rows the kernel is bound by its one MMA-issuing thread (wait + eight MMAs + commit per
+// 128 K whatever N is); a second CTA per SM is a second issuing thread per SM.
+constexpr int WA_BN = 256;                 // the wide tile (batch tiling of large batches uses it)
+constexpr int WA_BN_SMALL = 64;
 constexpr int WA_A_COLS = BK / 2;          // TMEM columns of a converted 64-K block (2 K per column)
 constexpr int WA_UNIT_K = 128;             // K per ring slot: one quantization group = two 64-K blocks
-constexpr int WA_UNIT_X_BYTES = 2 * WA_X_BYTES;
 constexpr int WA_UNIT_A_COLS = 2 * WA_A_COLS;
-constexpr int WA_MAX_UNITS = 3;            // ring depth: 3 x 64 KB of x in shared memory, 3 x 64 columns of A in TMEM
+constexpr int WA_MAX_UNITS = 3;            // ring depth: 3 units of x in shared memory, 3 x 64 columns of A in TMEM
 constexpr int WA_MAX_GROUPS = 3;           // converter groups <= ring depth
 constexpr int WA_MAX_THREADS = (2 + 4 * WA_MAX_GROUPS) * 32;
-constexpr uint32_t WA_TMEM_COLS = 512;     // accumulator [0, 256) + A units [256, 448)
-constexpr int WA_HALF_SLOT = 128 * BM * 4;  // split-K exchange: the 128 columns x 128 rows x f32 one CTA leaves for its peer
-constexpr int WA_QUARTER_SLOT = 64 * BM * 4;   // four K splits: 64 columns per block, twelve blocks per tile
+constexpr int WA_SMALL_THREADS = (2 + 4 * 2) * 32;   // the narrow tile always runs two converter groups
+// split-K exchange: the (BN / KS columns) x 128 rows x f32 block one CTA leaves for a peer
+__host__ __device__ constexpr int wa_slot_bytes(int bn, int ks) { return (bn / ks) * BM * 4; }
 constexpr int WA_STAGE_PITCH = 320;        // bytes per batch row of the staged output tile: 256 + 64, so that the
                                            // even and the odd lanes of a staging store use different banks
 
@@ -91,14 +95,34 @@ __device__ __forceinline__ void group_consts(__half sh, uint32_t zp, uint32_t& z
     }
 }
 
-template <bool BF16, int KS, bool SW>
-__global__ void __launch_bounds__(WA_MAX_THREADS, 1)
+template <int CW> __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[CW]);
+template <> __device__ __forceinline__ void tmem_ld_cols<32>(uint32_t taddr, uint32_t (&r)[32]) { tmem_ld32(taddr, r); }
+template <> __device__ __forceinline__ void tmem_ld_cols<16>(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+template <> __device__ __forceinline__ void tmem_ld_cols<8>(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+        : "r"(taddr) : "memory");
+}
+
+template <bool BF16, int KS, bool SW, int BN>
+__global__ void __launch_bounds__(BN == WA_BN_SMALL ? WA_SMALL_THREADS : WA_MAX_THREADS, BN == WA_BN_SMALL ? 2 : 1)
 lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) {
+    constexpr int X_BYTES = BN * 128;                 // x tile of a stage: BN rows x 64 K x 2 bytes
+    constexpr int UNIT_X_BYTES = 2 * X_BYTES;         // a ring slot: 128 K
+    constexpr uint32_t TMEM_COLS = BN == WA_BN_SMALL ? 256u : 512u;   // accumulator [0, BN) + A units [BN, BN + 192)
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const int P = p.stages;                          // ring depth in units of 128 K
     unsigned char* x_ring = smem;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(x_ring + (size_t)P * WA_UNIT_X_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(x_ring + (size_t)P * UNIT_X_BYTES);
     // bars[0..P) full, [P..2P) empty, [2P] acc_full
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * P + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
@@ -107,7 +131,7 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     constexpr int OUT_W = SW ? BM / 2 : BM;         // outputs per tile: with SwiGLU lanes 0..63 hold gate rows, 64..127 up rows
     const int n0 = blockIdx.x * OUT_W;              // first output (= first gate / weight row) of the tile
-    const int m0 = blockIdx.y * WA_BN;              // first batch row of the tile
+    const int m0 = blockIdx.y * BN;                 // first batch row of the tile
     const int ksplit = KS == 1 ? 0 : (int)blockIdx.z;
     const int k_len = p.K / KS;
     const int k_base = ksplit * k_len;
@@ -122,10 +146,10 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
     auto load_x_unit = [&](int u, int s) {
         mbar_expect_tx(full(s), (uint32_t)(2 * p.ncols * 128));
         // byte coordinates: the map describes x as [M][2K bytes]; two 64-K boxes per unit
-        const uint32_t dst = smem_u32(x_ring + (size_t)s * WA_UNIT_X_BYTES);
+        const uint32_t dst = smem_u32(x_ring + (size_t)s * UNIT_X_BYTES);
         const int kbyte = (k_base + u * WA_UNIT_K) * 2;
         tma_load_2d(dst, &map_x, kbyte, m0, full(s));
-        tma_load_2d(dst + WA_X_BYTES, &map_x, kbyte + 128, m0, full(s));
+        tma_load_2d(dst + X_BYTES, &map_x, kbyte + 128, m0, full(s));
     };
 
     // Converter state, set up before the CTA-wide barrier so that the first weight bytes are
@@ -172,14 +196,14 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
         for (int u = 0; u < P && u < U; u++) load_x_unit(u, u);
     }
     if (warp == 1) {
-        tmem_alloc(smem_u32(tmem_slot), WA_TMEM_COLS);
+        tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
         tmem_relinquish();
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_a0 = tmem_base + (uint32_t)WA_BN;      // first A unit
+    const uint32_t tmem_a0 = tmem_base + (uint32_t)BN;         // first A unit
 
     bool ok = true;
     if (warp == 0) {
@@ -205,13 +229,13 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
                 ok = mbar_wait(full(s), ph, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
-                const uint64_t b_desc = make_kmajor_sw128_desc(smem_u32(x_ring + (size_t)s * WA_UNIT_X_BYTES));
+                const uint64_t b_desc = make_kmajor_sw128_desc(smem_u32(x_ring + (size_t)s * UNIT_X_BYTES));
                 const uint32_t a_tmem = tmem_a0 + (uint32_t)(s * WA_UNIT_A_COLS);
 #pragma unroll
                 for (int k = 0; k < WA_UNIT_K / 16; k++) {
                     // 16 K = 8 TMEM columns of A; in x: +32 bytes inside the 128-byte swizzle row
-                    // (+2 in the 16-byte address field), the second 64-K box 32 KB (+2048) further on
-                    const uint64_t b_off = (uint64_t)((k >> 2) * (WA_X_BYTES >> 4) + 2 * (k & 3));
+                    // (+2 in the 16-byte address field), the second 64-K box X_BYTES further on
+                    const uint64_t b_off = (uint64_t)((k >> 2) * (X_BYTES >> 4) + 2 * (k & 3));
                     umma_f16_ts(tmem_base, a_tmem + (uint32_t)(k * 8), b_desc + b_off, idesc, (u | k) != 0 ? 1u : 0u);
                 }
                 umma_commit(empty(s));        // x unit and A unit reusable once these MMAs have read them
@@ -272,39 +296,39 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
     const bool ep_warp = warp >= 2 && warp < 10;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
     const int my_row = quad * 32 + lane;
-    constexpr int KEEP = WA_BN / KS;                            // columns this CTA writes
+    constexpr int KEEP = BN / KS;                               // columns this CTA writes
     const int keep0 = ksplit * KEEP;                            // the first of them
     constexpr int PER_WARP = KEEP / 2;                          // per epilogue warp
-    // a half slot: 16 bytes (4 columns) per weight row, rows consecutive, [32 column quads][128 rows]:
+    constexpr int CW = PER_WARP < 32 ? PER_WARP : 32;           // columns per TMEM read (32, 16 or 8)
+    constexpr int NCH = PER_WARP / CW;                          // reads per warp
+    constexpr int SLOT = wa_slot_bytes(BN, KS);                 // split-K: KEEP columns x 128 rows x f32
+    // an exchange block: 16 bytes (4 columns) per weight row, rows consecutive, [column quads][128 rows]:
     // a warp's store or load is one contiguous 512-byte piece
-    unsigned char* slot = KS == 2 ? p.splitk + (size_t)(blockIdx.x + gridDim.x * blockIdx.y) * (2 * WA_HALF_SLOT) : nullptr;   // KS == 4: see below
     unsigned char* stage = x_ring;                                           // [column][WA_STAGE_PITCH bytes]
     const bool odd = lane & 1;
     // lanes pair up: the even lane stages (row, row + 1) of the even columns, the odd lane of the odd ones
     unsigned char* srow = stage + (quad * 32 + (lane & ~1)) * 2;
 
-    // 32 accumulator columns of the peer's half -> the peer's half slot `dst`, column quad q0 onwards
-    // (chunks that lie entirely beyond the batch's columns are skipped, by sender and receiver alike)
+    // CW accumulator columns of a peer's share -> the peer's block `dst`, column quad q0 onwards
+    // (reads that lie entirely beyond the batch's columns are skipped, by sender and receiver alike)
     auto send_chunk = [&](int col, unsigned char* dst, int q0) {
         if (col >= p.ncols) return;
-        uint32_t acc[32];
-        tmem_ld32(lane_addr + (uint32_t)col, acc);
+        uint32_t acc[CW];
+        tmem_ld_cols<CW>(lane_addr + (uint32_t)col, acc);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; i += 4)
+        for (int i = 0; i < CW; i += 4)
             __stcg(reinterpret_cast<uint4*>(dst + ((q0 + (i >> 2)) * BM + my_row) * 16), make_uint4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]));
     };
-    // 32 columns c0.. of this CTA's own half: add what the peer sent (column quad q0 onwards of
-    // `rsrc`), narrow once, stage
-    // what the peer left for 32 of this CTA's columns (requested for both chunks before either is used)
-    auto load_peer = [&](float4 (&r)[8], int c0, const unsigned char* rsrc, int q0) {
+    // what a peer left for CW of this CTA's columns (requested for every read of the warp before any is used)
+    auto load_peer = [&](float4 (&r)[CW / 4], int c0, const unsigned char* rsrc, int q0) {
         if (keep0 + c0 >= p.ncols) return;
 #pragma unroll
-        for (int i = 0; i < 8; i++) r[i] = __ldcg(reinterpret_cast<const float4*>(rsrc + ((q0 + i) * BM + my_row) * 16));
+        for (int i = 0; i < CW / 4; i++) r[i] = __ldcg(reinterpret_cast<const float4*>(rsrc + ((q0 + i) * BM + my_row) * 16));
     };
-    auto acc_add = [&](uint32_t (&acc)[32], const float4 (&r4)[8]) {
+    auto acc_add = [&](uint32_t (&acc)[CW], const float4 (&r4)[CW / 4]) {
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
+        for (int i = 0; i < CW / 4; i++) {
             const float4 r = r4[i];
             acc[4 * i + 0] = __float_as_uint(__uint_as_float(acc[4 * i + 0]) + r.x);
             acc[4 * i + 1] = __float_as_uint(__uint_as_float(acc[4 * i + 1]) + r.y);
@@ -312,18 +336,18 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
             acc[4 * i + 3] = __float_as_uint(__uint_as_float(acc[4 * i + 3]) + r.w);
         }
     };
-    // the accumulator columns keep0 + c0 .. + 32 of this thread's row, plus up to three peers' sums
-    auto finalize_chunk = [&](int c0, const float4 (&peer)[8], const unsigned char* more = nullptr, int q0 = 0) {
+    // the accumulator columns keep0 + c0 .. + CW of this thread's row, plus up to three peers' sums
+    auto finalize_chunk = [&](int c0, const float4 (&peer)[CW / 4], const unsigned char* more = nullptr, int q0 = 0) {
         if (keep0 + c0 >= p.ncols) return;
-        uint32_t acc[32];
-        tmem_ld32(lane_addr + (uint32_t)(keep0 + c0), acc);
+        uint32_t acc[CW];
+        tmem_ld_cols<CW>(lane_addr + (uint32_t)(keep0 + c0), acc);
         tmem_ld_wait();
         if (KS >= 2) acc_add(acc, peer);
         if (KS == 4) {
             // sources 1 and 2 of this CTA's slot row (source 0 came in `peer`)
-            float4 r1[8], r2[8];
+            float4 r1[CW / 4], r2[CW / 4];
             load_peer(r1, c0, more, q0);
-            load_peer(r2, c0, more + WA_QUARTER_SLOT, q0);
+            load_peer(r2, c0, more + SLOT, q0);
             acc_add(acc, r1);
             acc_add(acc, r2);
         }
@@ -332,10 +356,10 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
             // shared memory as f32, [column][128 rows], and are combined in the write-out pass
             float* fcol = reinterpret_cast<float*>(stage) + my_row;
 #pragma unroll
-            for (int i = 0; i < 32; i++) fcol[(c0 + i) * BM] = __uint_as_float(acc[i]);
+            for (int i = 0; i < CW; i++) fcol[(c0 + i) * BM] = __uint_as_float(acc[i]);
         } else {
 #pragma unroll
-            for (int i = 0; i < 32; i += 2) {
+            for (int i = 0; i < CW; i += 2) {
                 const float mine = __uint_as_float(odd ? acc[i + 1] : acc[i]);
                 const float give = __uint_as_float(odd ? acc[i] : acc[i + 1]);
                 const float got = __shfl_xor_sync(0xffffffffu, give, 1);
@@ -346,43 +370,47 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
     };
 
     if (KS == 4) {
-        // four CTAs, four quarters of K: CTA r finishes columns [64 r, 64 r + 64); block (d, s) of the
-        // tile's slot holds what the s-th CTA after d (cyclically) leaves for d
-        unsigned char* slot4 = p.splitk + (size_t)(blockIdx.x + gridDim.x * blockIdx.y) * (12 * WA_QUARTER_SLOT);
+        // four CTAs, four quarters of K: CTA r finishes columns [KEEP r, KEEP r + KEEP); block (d, s) of
+        // the tile's slot holds what the s-th CTA after d (cyclically) leaves for d.  One read per warp.
+        static_assert(KS != 4 || NCH == 1, "four K splits: one TMEM read per epilogue warp");
+        unsigned char* slot4 = p.splitk + (size_t)(blockIdx.x + gridDim.x * blockIdx.y) * (12 * SLOT);
         if (ep_warp && ok) {
 #pragma unroll 1
             for (int dd = 1; dd < 4; dd++) {
                 const int d = (ksplit + dd) & 3;                    // destination; this CTA is its source 3 - dd
-                send_chunk(d * KEEP + eh * PER_WARP, slot4 + (size_t)(d * 3 + 3 - dd) * WA_QUARTER_SLOT, eh * 8);
+                send_chunk(d * KEEP + eh * PER_WARP, slot4 + (size_t)(d * 3 + 3 - dd) * SLOT, eh * (PER_WARP / 4));
             }
         }
         cluster_sync_all();          // release / acquire at cluster scope: every block is published
         if (ep_warp && ok) {
-            const unsigned char* row = slot4 + (size_t)(ksplit * 3) * WA_QUARTER_SLOT;
-            float4 r0[8];
-            load_peer(r0, eh * PER_WARP, row, eh * 8);
-            finalize_chunk(eh * PER_WARP, r0, row + WA_QUARTER_SLOT, eh * 8);
+            const unsigned char* row = slot4 + (size_t)(ksplit * 3) * SLOT;
+            float4 r0[CW / 4];
+            load_peer(r0, eh * PER_WARP, row, eh * (PER_WARP / 4));
+            finalize_chunk(eh * PER_WARP, r0, row + SLOT, eh * (PER_WARP / 4));
         }
     } else if (KS == 2) {
-        const int send0 = (1 - ksplit) * (WA_BN / 2);
-        unsigned char* theirs = slot + (size_t)(1 - ksplit) * WA_HALF_SLOT;
-        const unsigned char* mine = slot + (size_t)ksplit * WA_HALF_SLOT;
+        // each CTA leaves the KEEP columns the other one finishes in the pair's slot
+        unsigned char* slot = p.splitk + (size_t)(blockIdx.x + gridDim.x * blockIdx.y) * (2 * SLOT);
+        const int send0 = (1 - ksplit) * KEEP;
+        unsigned char* theirs = slot + (size_t)(1 - ksplit) * SLOT;
+        const unsigned char* mine = slot + (size_t)ksplit * SLOT;
         if (ep_warp && ok) {
-            send_chunk(send0 + eh * PER_WARP, theirs, eh * 16);
-            send_chunk(send0 + eh * PER_WARP + 32, theirs, eh * 16 + 8);
+#pragma unroll
+            for (int ch = 0; ch < NCH; ch++)
+                send_chunk(send0 + eh * PER_WARP + ch * CW, theirs, (eh * PER_WARP + ch * CW) / 4);
         }
         cluster_sync_all();          // release / acquire at cluster scope: both halves are published
         if (ep_warp && ok) {
-            float4 ra[8], rb[8];
-            load_peer(ra, eh * PER_WARP, mine, eh * 16);
-            load_peer(rb, eh * PER_WARP + 32, mine, eh * 16 + 8);
-            finalize_chunk(eh * PER_WARP, ra);
-            finalize_chunk(eh * PER_WARP + 32, rb);
+            float4 rr[NCH][CW / 4];
+#pragma unroll
+            for (int ch = 0; ch < NCH; ch++) load_peer(rr[ch], eh * PER_WARP + ch * CW, mine, (eh * PER_WARP + ch * CW) / 4);
+#pragma unroll
+            for (int ch = 0; ch < NCH; ch++) finalize_chunk(eh * PER_WARP + ch * CW, rr[ch]);
         }
     } else if (ep_warp && ok) {
 #pragma unroll 1
-        for (int c0 = eh * PER_WARP; c0 < (eh + 1) * PER_WARP; c0 += 32) {
-            const float4 none[8] = {};
+        for (int c0 = eh * PER_WARP; c0 < (eh + 1) * PER_WARP; c0 += CW) {
+            const float4 none[CW / 4] = {};
             finalize_chunk(c0, none);
         }
     }
@@ -431,13 +459,13 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
     }
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, WA_TMEM_COLS);
+        tmem_dealloc(tmem_base, TMEM_COLS);
     }
 }
 
-template <bool BF16, int KS, bool SW>
+template <bool BF16, int KS, bool SW, int BN>
 cudaError_t launch_wa(bool pdl, const CUtensorMap& mx, const WaParams& p, dim3 grid, int threads, size_t smem, cudaStream_t st) {
-    auto kfn = lux_qgemm_i4_tc_wa<BF16, KS, SW>;
+    auto kfn = lux_qgemm_i4_tc_wa<BF16, KS, SW, BN>;
     static std::atomic<size_t> configured[64];
     int dev = 0;
     cudaGetDevice(&dev);
@@ -465,22 +493,40 @@ LuxBackendError launch_qgemm_i4_tc_wa(Context* ctx, const QArgs& a) {
     if ((reinterpret_cast<uintptr_t>(a.x) & 15u) || (reinterpret_cast<uintptr_t>(a.y) & 15u)) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
     const bool bf16 = a.x_dtype == LUX_QDTYPE_BF16;
 
-    // Split K over a pair of CTAs when whole tiles alone would leave most SMs idle.
-    const int tiles = (nout / out_w) * ((a.M + WA_BN - 1) / WA_BN);
-    const bool can_split = a.K % 256 == 0 && (size_t)tiles * (2 * WA_HALF_SLOT) <= ctx->d_splitk_bytes;
-    const bool can_split4 = a.K % 512 == 0 && (size_t)tiles * (12 * WA_QUARTER_SLOT) <= ctx->d_splitk_bytes;
-    int ks = (tiles * 4 <= ctx->sm_count && can_split4) ? 4 : (tiles * 2 <= ctx->sm_count && can_split) ? 2 : 1;
-    if (g_tune.gemm_tc_splitk == 1 || (g_tune.gemm_tc_splitk == 2 && can_split) || (g_tune.gemm_tc_splitk == 4 && can_split4))
-        ks = g_tune.gemm_tc_splitk;
+    // Split K over a cluster of two or four CTAs when whole tiles alone would leave most slots idle
+    // (`slots` = CTAs resident at once).
+    auto plan = [&](int bn, int slots, int& ks_out) {
+        const int tiles = (nout / out_w) * ((a.M + bn - 1) / bn);
+        const bool can_split = a.K % 256 == 0 && (size_t)tiles * (2 * wa_slot_bytes(bn, 2)) <= ctx->d_splitk_bytes;
+        const bool can_split4 = a.K % 512 == 0 && (size_t)tiles * (12 * wa_slot_bytes(bn, 4)) <= ctx->d_splitk_bytes;
+        int ks = (tiles * 4 <= slots && can_split4) ? 4 : (tiles * 2 <= slots && can_split) ? 2 : 1;
+        if (g_tune.gemm_tc_splitk == 1 || (g_tune.gemm_tc_splitk == 2 && can_split) || (g_tune.gemm_tc_splitk == 4 && can_split4))
+            ks = g_tune.gemm_tc_splitk;
+        ks_out = ks;
+        return tiles * ks;                                      // CTAs of the launch
+    };
+    // Batches of up to 64 rows may take the narrow tile, two CTAs per SM: worth it when the launch has
+    // more CTAs than SMs (measured, config 4 at 16..64 rows: gate_up 41 -> 27 us, qkv 12.9 -> 11.0 us;
+    // with 128 CTAs or fewer, `o` and `down`, the narrow tile only packs them onto half the SMs:
+    // 9.2 -> 10.4 us and 19.9 -> 24.8 us).  gemm_wa_narrow = 1 / 2 forces the narrow / wide tile.
+    int ks = 1, ks_narrow = 1;
+    plan(WA_BN, ctx->sm_count, ks);
+    bool narrow = false;
+    if (a.M <= WA_BN_SMALL && g_tune.gemm_wa_narrow != 2) {
+        const int ctas = plan(WA_BN_SMALL, 2 * ctx->sm_count, ks_narrow);
+        narrow = ctas > ctx->sm_count || g_tune.gemm_wa_narrow == 1;
+    }
+    if (narrow) ks = ks_narrow;
+    const int bn = narrow ? WA_BN_SMALL : WA_BN;
     const int stages = g_tune.gemm_tc_stages >= 2 && g_tune.gemm_tc_stages <= WA_MAX_UNITS ? g_tune.gemm_tc_stages : WA_MAX_UNITS;
     int groups = g_tune.gemm_tc_groups >= 2 && g_tune.gemm_tc_groups <= WA_MAX_GROUPS ? g_tune.gemm_tc_groups : 2;
-    groups = std::min(groups, stages);
-    const size_t smem = 1024 + (size_t)stages * WA_UNIT_X_BYTES + 512;
+    groups = narrow ? 2 : std::min(groups, stages);
+    const size_t smem = 1024 + (size_t)stages * (2 * bn * 128) + 512;
 
     CUtensorMap mx;
     const uint64_t dims[2] = {(uint64_t)a.K * 2, (uint64_t)a.M};
     const uint64_t strides[1] = {(uint64_t)a.K * 2};
-    const int ncols = a.M >= WA_BN ? WA_BN : (a.M + 15) / 16 * 16;
+    const int ncols = a.M >= bn ? bn : (a.M + 15) / 16 * 16;
     const uint32_t box[2] = {128, (uint32_t)ncols};
     if (!encode_tensor_map_u8(&mx, 2, a.x, dims, strides, box, true)) return LUX_BACKEND_ERROR_INTERNAL;
 
@@ -497,27 +543,32 @@ LuxBackendError launch_qgemm_i4_tc_wa(Context* ctx, const QArgs& a) {
     p.groups = groups;
     p.ncols = ncols;
 
-    dim3 grid(nout / out_w, (a.M + WA_BN - 1) / WA_BN, ks);
+    dim3 grid(nout / out_w, (a.M + bn - 1) / bn, ks);
     const int threads = (2 + 4 * groups) * 32;                  // groups >= 2: the epilogue needs warps 2..9
     const bool pdl = pdl_allowed(ctx, a.weights_volatile);
-    auto go = [&](auto bf_tag, auto sw_tag) {
+    auto go = [&](auto bf_tag, auto sw_tag, auto bn_tag) {
         constexpr bool BF_ = decltype(bf_tag)::value;
         constexpr bool SW_ = decltype(sw_tag)::value;
-        return ks == 4 ? launch_wa<BF_, 4, SW_>(pdl, mx, p, grid, threads, smem, ctx->stream)
-             : ks == 2 ? launch_wa<BF_, 2, SW_>(pdl, mx, p, grid, threads, smem, ctx->stream)
-                       : launch_wa<BF_, 1, SW_>(pdl, mx, p, grid, threads, smem, ctx->stream);
+        constexpr int BN_ = decltype(bn_tag)::value;
+        return ks == 4 ? launch_wa<BF_, 4, SW_, BN_>(pdl, mx, p, grid, threads, smem, ctx->stream)
+             : ks == 2 ? launch_wa<BF_, 2, SW_, BN_>(pdl, mx, p, grid, threads, smem, ctx->stream)
+                       : launch_wa<BF_, 1, SW_, BN_>(pdl, mx, p, grid, threads, smem, ctx->stream);
+    };
+    auto go_bn = [&](auto bf_tag, auto sw_tag) {
+        return narrow ? go(bf_tag, sw_tag, std::integral_constant<int, WA_BN_SMALL>{})
+                      : go(bf_tag, sw_tag, std::integral_constant<int, WA_BN>{});
     };
     cudaError_t e;
-    if (a.swiglu) e = bf16 ? go(std::true_type{}, std::true_type{}) : go(std::false_type{}, std::true_type{});
-    else          e = bf16 ? go(std::true_type{}, std::false_type{}) : go(std::false_type{}, std::false_type{});
+    if (a.swiglu) e = bf16 ? go_bn(std::true_type{}, std::true_type{}) : go_bn(std::false_type{}, std::true_type{});
+    else          e = bf16 ? go_bn(std::true_type{}, std::false_type{}) : go_bn(std::false_type{}, std::false_type{});
     count_launch(bf16 ? "lux_qgemm_i4_tc_wa_bf16" : "lux_qgemm_i4_tc_wa_f16");
     return map_cuda(e, "lux_qgemm_i4_tc_wa");
 }
 
 
-const void* kernel_addr_qgemm_i4_tc_wa_bf16() { return (const void*)lux_qgemm_i4_tc_wa<true, 2, false>; }
-const void* kernel_addr_qgemm_i4_tc_wa_f16() { return (const void*)lux_qgemm_i4_tc_wa<false, 2, false>; }
-const void* kernel_addr_qgemm_i4_tc_wa_bf16_swiglu() { return (const void*)lux_qgemm_i4_tc_wa<true, 1, true>; }
-const void* kernel_addr_qgemm_i4_tc_wa_f16_swiglu() { return (const void*)lux_qgemm_i4_tc_wa<false, 1, true>; }
+const void* kernel_addr_qgemm_i4_tc_wa_bf16() { return (const void*)lux_qgemm_i4_tc_wa<true, 2, false, WA_BN>; }
+const void* kernel_addr_qgemm_i4_tc_wa_f16() { return (const void*)lux_qgemm_i4_tc_wa<false, 2, false, WA_BN>; }
+const void* kernel_addr_qgemm_i4_tc_wa_bf16_swiglu() { return (const void*)lux_qgemm_i4_tc_wa<true, 1, true, WA_BN>; }
+const void* kernel_addr_qgemm_i4_tc_wa_f16_swiglu() { return (const void*)lux_qgemm_i4_tc_wa<false, 1, true, WA_BN>; }
 
 }  // namespace luxcuda

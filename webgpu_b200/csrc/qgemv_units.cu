@@ -55,6 +55,7 @@
 #include <cudaTypedefs.h>
 
 #include <algorithm>
+#include <cstring>
 
 namespace luxcuda {
 

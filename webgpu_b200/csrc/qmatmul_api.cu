@@ -141,6 +141,8 @@ LuxBackendError ensure_stage(Context* ctx, size_t bytes) {
     if (ctx->d_stage) { cudaFree(ctx->d_stage); ctx->d_stage = nullptr; ctx->d_stage_bytes = 0; }
     LUX_CUDA_TRY(cudaHostAlloc(&ctx->h_stage, want, cudaHostAllocMapped));   // device-visible: small results are written into it directly
     ctx->h_stage_bytes = want;
+    ctx->d_stage_y = nullptr;
+    if (cudaHostGetDevicePointer(&ctx->d_stage_y, ctx->h_stage, 0) != cudaSuccess) { (void)cudaGetLastError(); ctx->d_stage_y = nullptr; }
     LUX_CUDA_TRY(cudaMalloc(&ctx->d_stage, want));
     ctx->d_stage_bytes = want;
     return LUX_BACKEND_OK;
@@ -202,20 +204,29 @@ LuxBackendError lux_cuda_qmatmul_host(LuxBackendContext* context, const LuxQMatm
     std::lock_guard<std::mutex> lock(ctx->mu);
     e = ensure_stage(ctx, y_off + yb);
     if (e != LUX_BACKEND_OK) return e;
-    // host -> pinned -> device, kernel, result -> pinned -> host: one stream wait in all.  A small
-    // result is written by the kernel straight into the pinned buffer (posted writes over PCIe),
-    // which takes the device-to-host copy and its DMA latency off the critical path; a large one
-    // (prefill) goes through device memory and one copy.
-    std::memcpy(ctx->h_stage, x_host, xb);
-    LUX_CUDA_TRY(cudaMemcpyAsync(ctx->d_stage, ctx->h_stage, xb, cudaMemcpyHostToDevice, ctx->stream));
-    a.x = ctx->d_stage;
-    void* y_mapped = nullptr;
-    const bool direct = yb <= ((size_t)256 << 10) &&
-                        cudaHostGetDevicePointer(&y_mapped, (char*)ctx->h_stage + y_off, 0) == cudaSuccess && y_mapped;
-    if (!direct) (void)cudaGetLastError();
-    a.y = direct ? y_mapped : (void*)((char*)ctx->d_stage + y_off);
-    e = dispatch(ctx, c);
-    if (e != LUX_BACKEND_OK) return e;
+    // Decode-sized calls are all fixed cost, so every step that can go, goes:
+    //   * x: up to 64 KB the runtime sends a host-to-device copy from ordinary memory inside the
+    //     command stream itself and returns, so x_host is handed over as it is (no staging copy,
+    //     no DMA read back over the bus); larger activations go through the pinned buffer;
+    //   * y: a small result is written by the kernel straight into the pinned buffer (posted writes
+    //     over the bus), which takes the device-to-host copy off the critical path;
+    //   * completion: one cudaStreamSynchronize.  (Measured and dropped: a completion flag in pinned
+    //     memory written by the kernel's last CTA and polled by the host was 3.5 us SLOWER per call
+    //     than the stream wait; carrying x in the kernel's parameter block instead of copying it
+    //     was 4 us slower, 8 KB of parameters costing more than the copy they replace.)
+    const bool direct = yb <= ((size_t)256 << 10) && ctx->d_stage_y;
+    a.y = direct ? (void*)((char*)ctx->d_stage_y + y_off) : (void*)((char*)ctx->d_stage + y_off);
+    {
+        if (xb <= ((size_t)64 << 10) && g_tune.host_pageable != 2) {
+            LUX_CUDA_TRY(cudaMemcpyAsync(ctx->d_stage, x_host, xb, cudaMemcpyHostToDevice, ctx->stream));
+        } else {
+            std::memcpy(ctx->h_stage, x_host, xb);
+            LUX_CUDA_TRY(cudaMemcpyAsync(ctx->d_stage, ctx->h_stage, xb, cudaMemcpyHostToDevice, ctx->stream));
+        }
+        a.x = ctx->d_stage;
+        e = dispatch(ctx, c);
+        if (e != LUX_BACKEND_OK) return e;
+    }
     if (!direct)
         LUX_CUDA_TRY(cudaMemcpyAsync((char*)ctx->h_stage + y_off, a.y, yb, cudaMemcpyDeviceToHost, ctx->stream));
     e = finish_op(ctx, false, "lux_cuda_qmatmul_host");
@@ -363,8 +374,8 @@ LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_tune_set(const char* key, int val
         {"gemv_i8_warps", &g_tune.gemv_i8_warps},   {"gemv_i8_kernel", &g_tune.gemv_i8_kernel}, {"peer_wait_limit", &g_tune.peer_wait_limit}, {"tp_fused_push", &g_tune.tp_fused_push},   {"gemm_tc_bn", &g_tune.gemm_tc_bn},
         {"gemv_i4_kernel", &g_tune.gemv_i4_kernel}, {"gemv_stream_cg", &g_tune.gemv_stream_cg},
         {"gemv_stream_stages", &g_tune.gemv_stream_stages}, {"gemv_stream_warps", &g_tune.gemv_stream_warps},
-        {"gemv_units_ks", &g_tune.gemv_units_ks}, {"gemv_units_stages", &g_tune.gemv_units_stages}, {"gemv_units_cg", &g_tune.gemv_units_cg}, {"gemv_units_pre", &g_tune.gemv_units_pre}, {"gemv_units_fx", &g_tune.gemv_units_fx}, {"gemv_units_warps", &g_tune.gemv_units_warps}, {"gemv_units_planes", &g_tune.gemv_units_planes},
-        {"gemm_tc_stages", &g_tune.gemm_tc_stages}, {"gemm_tc_splitk", &g_tune.gemm_tc_splitk}, {"gemm_tc_ma", &g_tune.gemm_tc_ma}, {"gemm_tc_groups", &g_tune.gemm_tc_groups}, {"gemm_tc_kernel", &g_tune.gemm_tc_kernel}, {"gemm_min_m", &g_tune.gemm_min_m}, {"pdl", &g_tune.pdl},
+        {"gemv_units_ks", &g_tune.gemv_units_ks}, {"gemv_units_stages", &g_tune.gemv_units_stages}, {"gemv_units_cg", &g_tune.gemv_units_cg}, {"gemv_units_pre", &g_tune.gemv_units_pre}, {"gemv_units_fx", &g_tune.gemv_units_fx}, {"gemv_units_warps", &g_tune.gemv_units_warps}, {"gemv_units_planes", &g_tune.gemv_units_planes}, {"host_pageable", &g_tune.host_pageable},
+        {"gemm_tc_stages", &g_tune.gemm_tc_stages}, {"gemm_tc_splitk", &g_tune.gemm_tc_splitk}, {"gemm_tc_ma", &g_tune.gemm_tc_ma}, {"gemm_wa_narrow", &g_tune.gemm_wa_narrow}, {"gemm_tc_groups", &g_tune.gemm_tc_groups}, {"gemm_tc_kernel", &g_tune.gemm_tc_kernel}, {"gemm_min_m", &g_tune.gemm_min_m}, {"pdl", &g_tune.pdl},
     };
     for (auto& t : table)
         if (std::strcmp(t.k, key) == 0) { *t.v = value; return LUX_BACKEND_OK; }
