@@ -443,7 +443,7 @@ def bench_tp(args, peaks):
 
     # ---- the one-GPU anchor of the scaling curve: the same FFN, unsharded, on rank 0 of this box ----
     tp1 = None
-    if rank == 0:
+    if rank == 0 and not args.skip_tp1:
         tp1 = ffn_tp1_block(rig, args, peaks, M, x, gate_up, down)
     if world > 1:
         dist.barrier()
@@ -634,8 +634,8 @@ def bench_tp(args, peaks):
                     "d2h_bytes_per_step": int(M * d["H"] * 2), "us_per_step": e2e_sec * 1e6, "path": e2e_path},
             "gpu_launches": (2 if world == 1 else 3) * args.steps, "clocks": clocks,
             "parity_rel_l2": parity, "parity_rows": parity_rows, "ranks_identical": ranks_identical,
-            "tp1_us_same_box": tp1["us"], "ffn70b_cfg5_tp1": tp1,
-            "strong_scaling_efficiency": tp1["us"] / (world * sec * 1e6),
+            "tp1_us_same_box": tp1["us"] if tp1 else None, "ffn70b_cfg5_tp1": tp1,
+            "strong_scaling_efficiency": tp1["us"] / (world * sec * 1e6) if tp1 else None,
         }
     if line is not None and M >= 12:
         # From 12 batch rows on both FFN kernels run on the tensor cores: the roofline that bounds
@@ -737,6 +737,7 @@ def main():
     ap.add_argument("--collective", default="push", choices=["push", "nccl"],
                     help="all-reduce of the tensor-parallel FFN: the plugin's push all-reduce over peer memory "
                          "(falls back to NCCL if the peer mapping is refused) or NCCL")
+    ap.add_argument("--skip-tp1", action="store_true", help="N > 1: leave out the one-GPU anchor run on rank 0")
     ap.add_argument("--skip-ffn", action="store_true", help="N = 1: leave out the configuration-5 one-GPU block")
     ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE",
                     help="override a launch heuristic (lux_cuda_tune_set), e.g. gemv_i4_kernel=2")
