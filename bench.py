@@ -231,6 +231,12 @@ def bench_single(args, peaks):
     sec, graph = rig.time_graph(launch, len(pool), args.steps, args.warmup)
     kernel = rig.backend.last_kernel_name()          # the library picks a kernel per shape
     captured = rig.backend.launch_count() - l0
+    # the same GEMV as a long chain (2400 launches): with programmatic dependent launch every kernel's
+    # start overlaps its predecessor's drain, and the two ends of the chain weigh nothing.  Reported
+    # beside the headline so that the launch-overlap effect can be told from the kernel itself.
+    sec_chain = sec
+    if args.steps < 2400:
+        sec_chain, _ = rig.time_graph(launch, len(pool), 2400, 5)
     # keep the same load running a little longer so that the clock sampler sees it
     t_end = time.time() + 0.4
     with torch.cuda.stream(rig.stream):
@@ -350,7 +356,8 @@ def bench_single(args, peaks):
                      "traffic_source": NCU_TRAFFIC_CONFIG2["source"] + " (one ncu capture of this kernel on this workload, per launch)",
                      "peak_source": peaks["source"],
                      "frac_of_nominal_8tbs": achieved / NOMINAL_HBM_GBS, "algorithmic_bytes": abytes,
-                     "kernel": kernel},
+                     "kernel": kernel,
+                     "chain_of_2400": {"us": sec_chain * 1e6, "frac": abytes / sec_chain / 1e9 / peaks["hbm"]}},
         "cpu_baseline": {"value": wbytes / cpu_sec / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
                          "sample": f"{reps} full config-2 GEMVs (oracle/cpu_baseline.c: -O3, scale and zero-point "
                                    f"hoisted per group, OpenMP over rows)",
@@ -364,6 +371,51 @@ def bench_single(args, peaks):
     }
     line.update(extra)
     return line
+
+
+# ----------------------------------------------------------------------------------------
+# --workload sweep: configuration 4 (Llama-3-8B decode linears at batch 1, 4, 16, 64) and the
+# kernels either side of the linear layers.  Not the headline: the numbers DESIGN.md quotes.
+# ----------------------------------------------------------------------------------------
+
+def bench_sweep(args, peaks):
+    from webgpu_b200 import synth
+
+    rig = Rig(0, args.tune)
+    B, ctx, torch = rig.B, rig.ctx, rig.torch
+    steps = min(args.steps, 120)
+    out = {"metric": "qmatmul GEMV weight GB/s", "unit": "GB/s", "n_gpus": 1, "steps": steps, "warmup": max(args.warmup, 3),
+           "config": {"workload": "int4_g128 decode sweep (config 4): qkv / o / gate_up / down at batch 1, 4, 16, 64",
+                      "l2": "weight copies rotated per step so that every launch streams from HBM",
+                      "timing": "CUDA graph replays, CUDA events on the launching stream"},
+           "data": "synthetic", "layers": {}}
+    for name in synth.SWEEP_LAYERS:
+        _, layer = synth.config4(name, 1)
+        pool = rig.pool(layer, int(2.9 * L2_BYTES))
+        for M in synth.SWEEP_M:
+            x, _ = synth.config4(name, M)
+            xb, yb = ctx.upload(x), ctx.alloc(M * layer.N * 2)
+            sec, _ = rig.time_graph(lambda i: ctx.qmatmul(xb, pool[i % len(pool)], yb, M, B.F16, flags=B.FLAG_NO_SYNC),
+                                    len(pool), steps, args.warmup)
+            ab = algorithmic_bytes(layer, M, 2, 2)
+            out["layers"][f"{name}_m{M}"] = {
+                "us": sec * 1e6, "kernel": rig.backend.last_kernel_name(), "weight_gbs": layer.weight_bytes / sec / 1e9,
+                "frac_of_measured_hbm": ab / sec / 1e9 / peaks["hbm"], "tflops": 2.0 * M * layer.N * layer.K / sec / 1e12}
+        del pool
+    # the quantize kernel: f32 [14336, 4096] -> int4 g128 (reads 4 bytes, writes ~0.53 per element)
+    wf = torch.randn(14336, 4096, device="cuda", dtype=torch.float32)
+    wb = ctx.wrap(wf.data_ptr(), wf.numel() * 4)
+    qw, qs, qz = ctx.alloc(14336 * 2048), ctx.alloc(14336 * 32 * 2), ctx.alloc(14336 * 16)
+    import ctypes as C
+    d = B.make_desc(0, 14336, 4096, 4, 128, B.F32, B.F16, B.F32, B.FLAG_NO_SYNC)
+    lib = rig.backend.lib
+    sec, _ = rig.time_graph(lambda i: lib.lux_cuda_qquantize(ctx.handle, C.byref(d), wb.handle, qw.handle, qs.handle, qz.handle),
+                            1, steps, args.warmup)
+    qbytes = 14336 * 4096 * 4 + 14336 * 2048 + 14336 * 32 * 2 + 14336 * 16
+    out["quantize_int4_14336x4096"] = {"us": sec * 1e6, "gbs": qbytes / sec / 1e9, "frac_of_measured_hbm": qbytes / sec / 1e9 / peaks["hbm"],
+                                       "note": "235 MB read + 31 MB written per launch: larger than L2"}
+    ctx.sync()
+    return out
 
 
 # ----------------------------------------------------------------------------------------
@@ -733,7 +785,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=1, help="batch M of the tensor-parallel FFN workload")
-    ap.add_argument("--workload", default="auto", choices=["auto", "gemv", "tp_mlp"])
+    ap.add_argument("--workload", default="auto", choices=["auto", "gemv", "tp_mlp", "sweep"])
     ap.add_argument("--collective", default="push", choices=["push", "nccl"],
                     help="all-reduce of the tensor-parallel FFN: the plugin's push all-reduce over peer memory "
                          "(falls back to NCCL if the peer mapping is refused) or NCCL")
@@ -748,7 +800,10 @@ def main():
     else:
         _, _, world = dist_env()
         use_tp = args.workload == "tp_mlp" or (args.workload == "auto" and (args.gpus > 1 or world > 1))
-        line = bench_tp(args, peaks) if use_tp else bench_single(args, peaks)
+        if args.workload == "sweep":
+            line = bench_sweep(args, peaks)
+        else:
+            line = bench_tp(args, peaks) if use_tp else bench_single(args, peaks)
     if line is not None:
         print(json.dumps(line))
 

@@ -16,7 +16,7 @@
 // negative inputs are stored as 0.  LUX_QQUANT_FLAG_SHIFTED selects the usual
 // clamp(round(v / scale) + zp, 0, 15) instead (an extension, not the reference's arithmetic).
 //
-// A warp owns 256 consecutive elements of a row, 8 per lane: two int4 groups of 128 (16 lanes
+// A warp works on 256 consecutive elements of a row at a time, 8 per lane: two int4 groups of 128 (16 lanes
 // each) or eight int8 groups of 32 (4 lanes each).  Group minimum and maximum by shuffles inside the
 // group's lanes; one 4-byte (int4) or 8-byte (int8) store per lane, coalesced over the warp; the two
 // int4 zero-points of a warp share one byte of the zero-point table (low nibble first).
@@ -63,77 +63,93 @@ __device__ __forceinline__ void load8(const QuantParams& p, size_t idx, float (&
 }
 
 // BITS = 4: groups of 128 (16 lanes); BITS = 8: groups of 32 (4 lanes), symmetric only.
+// A warp takes QCH consecutive 256-element chunks of a row and requests all of them before it
+// reduces the first: 4 KB in flight per warp, so that a streaming kernel with this little
+// arithmetic keeps HBM busy.
+constexpr int QCH = 4;
+
 template <int BITS, bool SYM>
 __global__ void __launch_bounds__(256) lux_qquantize(const QuantParams p) {
     constexpr int GL = BITS == 4 ? 16 : 4;                  // lanes per group
     const int lane = threadIdx.x & 31;
     const size_t wid = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-    const size_t n = wid / (size_t)p.chunks_per_row;
-    const int c = (int)(wid - n * (size_t)p.chunks_per_row);
+    const int wpr = (p.chunks_per_row + QCH - 1) / QCH;     // warps per row
+    const size_t n = wid / (size_t)wpr;
     if (n >= (size_t)p.N) return;
-    const int k0 = c * 256 + lane * 8;
-    const bool live = k0 < p.K;                              // K is a multiple of the group size, so of 8
-    float v[8];
-    float mx = -1e30f, mn = 1e30f;                           // the shader's seeds (:169-170)
-    if (live) {
-        load8(p, n * (size_t)p.K + k0, v);
+    const int c0 = (int)(wid - n * (size_t)wpr) * QCH;
+    float v[QCH][8];
+    bool live[QCH];
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
-            mx = fmaxf(mx, v[i]);
-            mn = fminf(mn, v[i]);
+    for (int ch = 0; ch < QCH; ch++) {
+        const int k0 = (c0 + ch) * 256 + lane * 8;
+        live[ch] = k0 < p.K;                                 // K is a multiple of the group size, so of 8
+        if (live[ch]) load8(p, n * (size_t)p.K + k0, v[ch]);
+    }
+#pragma unroll
+    for (int ch = 0; ch < QCH; ch++) {
+        const int c = c0 + ch;
+        const int k0 = c * 256 + lane * 8;
+        if (c >= p.chunks_per_row) break;                    // warp-uniform
+        float mx = -1e30f, mn = 1e30f;                       // the shader's seeds (:169-170)
+        if (live[ch]) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                mx = fmaxf(mx, v[ch][i]);
+                mn = fminf(mn, v[ch][i]);
+            }
         }
-    }
 #pragma unroll
-    for (int o = GL / 2; o > 0; o >>= 1) {
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
-    }
-    float scale;
-    int zp = 0;
-    if (SYM) {
-        const float amax = fmaxf(fabsf(mx), fabsf(mn));
-        scale = __fdiv_rn(amax, BITS == 4 ? 7.0f : 127.0f);
-    } else {
-        scale = __fdiv_rn(mx - mn, 15.0f);
-        zp = min(max(__float2int_rz(rintf(__fdiv_rn(-mn, scale))), 0), 15);   // before the guard, as in the shader
-    }
-    if (scale == 0.0f) scale = 1.0f;
-    // compact table: an f16 table stores the rounded scale, and the values are quantized with the
-    // number the table holds (what dequantize will multiply by)
-    __half s16 = __float2half_rn(scale);
-    if (p.scale_dtype == LUX_QDTYPE_F16) scale = __half2float(s16);
-    const int g = k0 / (BITS == 4 ? 128 : 32);
-    if (live && (lane % GL) == 0) {
-        if (p.scale_dtype == LUX_QDTYPE_F16) reinterpret_cast<__half*>(p.scales)[n * (size_t)p.G + g] = s16;
-        else reinterpret_cast<float*>(p.scales)[n * (size_t)p.G + g] = scale;
-    }
-    if (BITS == 4 && !SYM) {
-        const int zp_hi = __shfl_sync(0xffffffffu, live ? zp : 0, 16);
-        if (lane == 0 && live) p.zeros[n * (size_t)p.ZS + c] = (uint8_t)(zp | (zp_hi << 4));
-    }
-    if (!live) return;
-    int q[8];
-#pragma unroll
-    for (int i = 0; i < 8; i++) q[i] = __float2int_rz(rintf(__fdiv_rn(v[i], scale)));   // saturating; NaN -> 0
-    if (BITS == 4) {
-        uint32_t word = 0;
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            int nib;
-            if (SYM) nib = min(max(q[i], -8), 7) + 8;
-            else if (p.shifted) nib = min(max(min(max(q[i], -32), 32) + zp, 0), 15);   // pre-clamped: a saturated q must not wrap
-            else nib = min(max(q[i], 0), 15);                         // (clamp(q, 0, 15) - zp) + zp, clamped again
-            word |= (uint32_t)nib << (4 * i);
+        for (int o = GL / 2; o > 0; o >>= 1) {
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
         }
-        reinterpret_cast<uint32_t*>(p.w)[(n * (size_t)p.K + k0) >> 3] = word;
-    } else {
-        uint32_t lo = 0, hi = 0;
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            lo |= ((uint32_t)min(max(q[i], -128), 127) & 0xFFu) << (8 * i);
-            hi |= ((uint32_t)min(max(q[4 + i], -128), 127) & 0xFFu) << (8 * i);
+        float scale;
+        int zp = 0;
+        if (SYM) {
+            const float amax = fmaxf(fabsf(mx), fabsf(mn));
+            scale = __fdiv_rn(amax, BITS == 4 ? 7.0f : 127.0f);
+        } else {
+            scale = __fdiv_rn(mx - mn, 15.0f);
+            zp = min(max(__float2int_rz(rintf(__fdiv_rn(-mn, scale))), 0), 15);   // before the guard, as in the shader
         }
-        reinterpret_cast<uint2*>(p.w)[(n * (size_t)p.K + k0) >> 3] = make_uint2(lo, hi);
+        if (scale == 0.0f) scale = 1.0f;
+        // compact table: an f16 table stores the rounded scale, and the values are quantized with the
+        // number the table holds (what dequantize will multiply by)
+        const __half s16 = __float2half_rn(scale);
+        if (p.scale_dtype == LUX_QDTYPE_F16) scale = __half2float(s16);
+        const int g = k0 / (BITS == 4 ? 128 : 32);
+        if (live[ch] && (lane % GL) == 0) {
+            if (p.scale_dtype == LUX_QDTYPE_F16) reinterpret_cast<__half*>(p.scales)[n * (size_t)p.G + g] = s16;
+            else reinterpret_cast<float*>(p.scales)[n * (size_t)p.G + g] = scale;
+        }
+        if (BITS == 4 && !SYM) {
+            const int zp_hi = __shfl_sync(0xffffffffu, live[ch] ? zp : 0, 16);
+            if (lane == 0 && live[ch]) p.zeros[n * (size_t)p.ZS + c] = (uint8_t)(zp | (zp_hi << 4));
+        }
+        if (!live[ch]) continue;
+        int q[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) q[i] = __float2int_rz(rintf(__fdiv_rn(v[ch][i], scale)));   // saturating; NaN -> 0
+        if (BITS == 4) {
+            uint32_t word = 0;
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                int nib;
+                if (SYM) nib = min(max(q[i], -8), 7) + 8;
+                else if (p.shifted) nib = min(max(min(max(q[i], -32), 32) + zp, 0), 15);   // pre-clamped: a saturated q must not wrap
+                else nib = min(max(q[i], 0), 15);                         // (clamp(q, 0, 15) - zp) + zp, clamped again
+                word |= (uint32_t)nib << (4 * i);
+            }
+            reinterpret_cast<uint32_t*>(p.w)[(n * (size_t)p.K + k0) >> 3] = word;
+        } else {
+            uint32_t lo = 0, hi = 0;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                lo |= ((uint32_t)min(max(q[i], -128), 127) & 0xFFu) << (8 * i);
+                hi |= ((uint32_t)min(max(q[4 + i], -128), 127) & 0xFFu) << (8 * i);
+            }
+            reinterpret_cast<uint2*>(p.w)[(n * (size_t)p.K + k0) >> 3] = make_uint2(lo, hi);
+        }
     }
 }
 
@@ -177,7 +193,7 @@ extern "C" LuxBackendError lux_cuda_qquantize(LuxBackendContext* context, const 
     p.scale_dtype = (int)d->scale_dtype;
     p.shifted = (d->flags & LUX_QQUANT_FLAG_SHIFTED) ? 1 : 0;
     p.chunks_per_row = (int)((K + 255) / 256);
-    const size_t warps = N * (size_t)p.chunks_per_row;
+    const size_t warps = N * (size_t)((p.chunks_per_row + QCH - 1) / QCH);
     const unsigned grid = (unsigned)((warps + 7) / 8);
     cudaSetDevice(ctx->device);
     if (d->bits == 8) lux_qquantize<8, true><<<grid, 256, 0, ctx->stream>>>(p);
