@@ -33,6 +33,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import sys
@@ -414,6 +415,38 @@ def bench_sweep(args, peaks):
     qbytes = 14336 * 4096 * 4 + 14336 * 2048 + 14336 * 32 * 2 + 14336 * 16
     out["quantize_int4_14336x4096"] = {"us": sec * 1e6, "gbs": qbytes / sec / 1e9, "frac_of_measured_hbm": qbytes / sec / 1e9 / peaks["hbm"],
                                        "note": "235 MB read + 31 MB written per launch: larger than L2"}
+    del wf
+    # decode attention over an f32 KV cache with Llama-3-8B's heads (32 query, 8 key/value, 128 wide):
+    # contiguous cache (sdpa_kv_cache) and 16-token pages (paged_attention), bytes = K and V read once
+    H, HKV, D = 32, 8, 128
+    out["attention_decode"] = {}
+    for batch, ctx_len in ((1, 4096), (1, 32768), (8, 4096), (32, 4096)):
+        kv_bytes = 2 * batch * HKV * ctx_len * D * 4
+        copies = max(1, -(-int(2.9 * L2_BYTES) // kv_bytes))
+        caches = [(torch.randn(batch, HKV, ctx_len, D, device="cuda"), torch.randn(batch, HKV, ctx_len, D, device="cuda")) for _ in range(copies)]
+        wrapped = [(ctx.wrap(k.data_ptr(), k.numel() * 4), ctx.wrap(v.data_ptr(), v.numel() * 4)) for k, v in caches]
+        q = torch.randn(batch, H, 1, D, device="cuda")
+        o = torch.empty_like(q)
+        qb, ob = ctx.wrap(q.data_ptr(), q.numel() * 4), ctx.wrap(o.data_ptr(), o.numel() * 4)
+        scale = 1.0 / math.sqrt(D)
+        sec, _ = rig.time_graph(lambda i: ctx.sdpa_kv_cache(qb, wrapped[i % copies][0], wrapped[i % copies][1], ob, batch, H, HKV, 1,
+                                                            ctx_len - 1, ctx_len, D, scale, flags=B.FLAG_NO_SYNC), copies, steps, args.warmup)
+        entry = {"contiguous_us": sec * 1e6, "contiguous_gbs": kv_bytes / sec / 1e9, "contiguous_frac_of_measured_hbm": kv_bytes / sec / 1e9 / peaks["hbm"]}
+        # the same bytes seen as 16-token pages in a shuffled order
+        bs = 16
+        nblk = ctx_len // bs
+        table = torch.stack([torch.randperm(nblk, device="cuda") + s * nblk for s in range(batch)]).to(torch.int32).contiguous()
+        lens = torch.full((batch,), ctx_len, device="cuda", dtype=torch.int32)
+        tb, lb = ctx.wrap(table.data_ptr(), table.numel() * 4), ctx.wrap(lens.data_ptr(), lens.numel() * 4)
+        q3, o3 = ctx.wrap(q.data_ptr(), q.numel() * 4), ctx.wrap(o.data_ptr(), o.numel() * 4)
+        # [batch, kv_heads, ctx, D] read as [batch * ctx / 16 blocks][...]: the bytes of a block are then not one
+        # (block, head) tile, which changes what is computed, not what is read; timing only
+        sec, _ = rig.time_graph(lambda i: ctx.paged_attention(q3, wrapped[i % copies][0], wrapped[i % copies][1], tb, lb, o3, batch, H, HKV, D,
+                                                              bs, nblk, scale, flags=B.FLAG_NO_SYNC), copies, steps, args.warmup)
+        entry.update({"paged16_us": sec * 1e6, "paged16_gbs": kv_bytes / sec / 1e9, "paged16_frac_of_measured_hbm": kv_bytes / sec / 1e9 / peaks["hbm"],
+                      "kv_mb": kv_bytes / 1e6})
+        out["attention_decode"][f"b{batch}_ctx{ctx_len}"] = entry
+        del caches, wrapped
     ctx.sync()
     return out
 

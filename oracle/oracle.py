@@ -70,6 +70,14 @@ def lib() -> C.CDLL:
         L.orc_dynamic_quantize.argtypes = [vp, C.c_size_t, i32, vp, vp]
         L.orc_compute_group_scales.argtypes = [vp, C.c_size_t, i32, i32, vp]
         L.orc_quantize.argtypes = [vp, C.c_size_t, i32, i32, vp, vp]
+        L.orc_rope_freq.argtypes = [u32, u32, f32]
+        L.orc_rope_freq.restype = f32
+        L.orc_rope_precompute_cache.argtypes = [u32, u32, f32, vp, vp]
+        L.orc_rope.argtypes = [vp, vp, vp, vp, vp, u32, u32, u32, u32, f32, u32, f32, i32]
+        L.orc_sdpa.argtypes = [vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u32, f32, i32]
+        L.orc_sdpa_kv_cache.argtypes = [vp, vp, vp, vp, u32, u32, u32, u32, u32, u32, u32, f32, i32]
+        L.orc_update_kv_cache.argtypes = [vp, vp, vp, vp, u32, u32, u32, u32, u32, u32]
+        L.orc_paged_attention.argtypes = [vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u32, f32, u32]
         _lib = L
     return _lib
 
@@ -280,6 +288,82 @@ def rms_norm_f32(x, weight, eps: float) -> np.ndarray:
     x = np.ascontiguousarray(x, np.float32)
     out = np.empty_like(x)
     lib().orc_rms_norm_f32(_ptr(x), _ptr(np.ascontiguousarray(weight, np.float32)), _ptr(out), x.shape[0], x.shape[1], eps)
+    return out
+
+
+# -- attention side (attention_oracle.c) ----------------------------------------------------
+
+
+def _f32c(a):
+    return np.ascontiguousarray(a, np.float32)
+
+
+def rope_cache(max_seq_len: int, head_dim: int, theta_base: float):
+    """rope_precompute_cache: (cos, sin), each [max_seq_len, head_dim / 2]."""
+    cos = np.empty((max_seq_len, head_dim // 2), np.float32)
+    sin = np.empty_like(cos)
+    assert lib().orc_rope_precompute_cache(max_seq_len, head_dim, theta_base, _ptr(cos), _ptr(sin)) == 0
+    return cos, sin
+
+
+def rope(x, cos=None, sin=None, position_ids=None, theta_base: float = 10000.0, position_offset: int = 0,
+         ntk_scale: float = 0.0, backward: bool = False) -> np.ndarray:
+    """The rotation of gpu/rope.wgsl on x [batch, seq, heads, head_dim] (adjacent pairs)."""
+    x = _f32c(x)
+    B, S, H, D = x.shape
+    out = np.empty_like(x)
+    cos = None if cos is None else _f32c(cos)
+    sin = None if sin is None else _f32c(sin)
+    pid = None if position_ids is None else np.ascontiguousarray(position_ids, np.uint32)
+    rc = lib().orc_rope(_ptr(x), _ptr(out), None if cos is None else _ptr(cos), None if sin is None else _ptr(sin),
+                        None if pid is None else _ptr(pid), B, S, H, D, theta_base, position_offset, ntk_scale, int(backward))
+    assert rc == 0, rc
+    return out
+
+
+def sdpa(q, k, v, scale: float, causal: bool = False, want_lse: bool = False):
+    """sdpa_basic / sdpa_mqa: q [B, H, Sq, D], k and v [B, Hkv, Skv, D]."""
+    q, k, v = _f32c(q), _f32c(k), _f32c(v)
+    B, H, Sq, D = q.shape
+    Hkv, Skv = k.shape[1], k.shape[2]
+    out = np.empty_like(q)
+    lse = np.empty((B, H, Sq), np.float32) if want_lse else None
+    rc = lib().orc_sdpa(_ptr(q), _ptr(k), _ptr(v), _ptr(out), None if lse is None else _ptr(lse), B, H, Hkv, Sq, Skv, D, scale,
+                        int(causal))
+    assert rc == 0, rc
+    return (out, lse) if want_lse else out
+
+
+def sdpa_kv_cache(q, k_cache, v_cache, cache_len: int, scale: float, causal_append: bool = False) -> np.ndarray:
+    """sdpa_kv_cache: q [B, H, Sq, D], caches [B, Hkv, max_len, D] with the new tokens already appended."""
+    q, k_cache, v_cache = _f32c(q), _f32c(k_cache), _f32c(v_cache)
+    B, H, Sq, D = q.shape
+    Hkv, max_len = k_cache.shape[1], k_cache.shape[2]
+    out = np.empty_like(q)
+    rc = lib().orc_sdpa_kv_cache(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), B, H, Hkv, Sq, cache_len, max_len, D, scale,
+                                 int(causal_append))
+    assert rc == 0, rc
+    return out
+
+
+def update_kv_cache(k, v, k_cache, v_cache, cache_len: int) -> None:
+    """update_kv_cache, in place on the two caches (float32, C-contiguous)."""
+    k, v = _f32c(k), _f32c(v)
+    assert k_cache.dtype == np.float32 and k_cache.flags.c_contiguous and v_cache.flags.c_contiguous
+    B, Hkv, Sq, D = k.shape
+    assert lib().orc_update_kv_cache(_ptr(k), _ptr(v), _ptr(k_cache), _ptr(v_cache), B, Hkv, Sq, cache_len, k_cache.shape[2], D) == 0
+
+
+def paged_attention(q, k_cache, v_cache, block_tables, context_lens, scale: float, partition_size: int = 0, out=None) -> np.ndarray:
+    """paged_attention_v1 (partition_size 0) or v2 partial + reduce: q [S, H, D], caches [blocks, Hkv, block_size, D]."""
+    q, k_cache, v_cache = _f32c(q), _f32c(k_cache), _f32c(v_cache)
+    bt = np.ascontiguousarray(block_tables, np.int32)
+    cl = np.ascontiguousarray(context_lens, np.int32)
+    S, H, D = q.shape
+    out = np.zeros_like(q) if out is None else out
+    rc = lib().orc_paged_attention(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(bt), _ptr(cl), _ptr(out), S, H, k_cache.shape[1], D,
+                                   k_cache.shape[2], bt.shape[1], scale, partition_size)
+    assert rc == 0, rc
     return out
 
 

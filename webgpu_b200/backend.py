@@ -39,6 +39,7 @@ CAP_TENSOR_OPS, CAP_MATMUL, CAP_CUSTOM_KERNELS = 1 << 0, 1 << 1, 1 << 4
 F32, F16, BF16 = 0, 1, 2
 NOALLOC_MAX_BYTES = 1 << 20          # LUX_QMLP_NOALLOC_MAX_BYTES
 FLAG_NO_SYNC, FLAG_SWIGLU, FLAG_WEIGHTS_VOLATILE, FLAG_QUANT_SHIFTED = 1, 2, 4, 8
+FLAG_ATTN_CAUSAL, FLAG_ROPE_BACKWARD = 16, 32               # lux/gpu/attention_ext.h
 ROUTE_NONE, ROUTE_GEMV_I8, ROUTE_SKINNY_I4, ROUTE_GEMM_I4_TC = range(4)
 
 VTBL_FIELDS = [
@@ -113,6 +114,8 @@ EXPORTED_SYMBOLS = [
     "lux_cuda_peer_comm_create", "lux_cuda_peer_comm_connect", "lux_cuda_peer_comm_connect_ptrs",
     "lux_cuda_peer_comm_window", "lux_cuda_peer_comm_window_bytes", "lux_cuda_peer_allreduce",
     "lux_cuda_peer_comm_destroy", "lux_cuda_qmlp_tp",
+    "lux_cuda_rope_precompute_cache_f32", "lux_cuda_rope_f32", "lux_cuda_rope_qk_f32", "lux_cuda_sdpa_f32",
+    "lux_cuda_update_kv_cache_f32", "lux_cuda_sdpa_kv_cache_f32", "lux_cuda_paged_attention_f32",
 ]
 PEER_HANDLE_BYTES = 64
 
@@ -216,6 +219,14 @@ class Backend:
         L.lux_cuda_matmul_int8.argtypes = [_vp, _vp, _vp, _vp, _int, _int, _int]
         L.lux_cuda_matmul_int4_int8.argtypes = [_vp, _vp, _vp, _vp, _int, _int, _int]
         L.lux_cuda_requantize_int32_to_int8.argtypes = [_vp, _vp, _vp, _sz, C.c_float, C.c_float, C.c_int32]
+        u32, f32 = C.c_uint32, C.c_float
+        L.lux_cuda_rope_precompute_cache_f32.argtypes = [_vp, _vp, _vp, u32, u32, f32, u32]
+        L.lux_cuda_rope_f32.argtypes = [_vp] * 6 + [u32] * 4 + [f32, u32, f32, u32]
+        L.lux_cuda_rope_qk_f32.argtypes = [_vp] * 5 + [u32] * 7
+        L.lux_cuda_sdpa_f32.argtypes = [_vp] * 6 + [u32] * 6 + [f32, u32]
+        L.lux_cuda_update_kv_cache_f32.argtypes = [_vp] * 5 + [u32] * 7
+        L.lux_cuda_sdpa_kv_cache_f32.argtypes = [_vp] * 5 + [u32] * 7 + [f32, u32]
+        L.lux_cuda_paged_attention_f32.argtypes = [_vp] * 7 + [u32] * 6 + [f32, u32]
         L.lux_cuda_qmlp.argtypes = [_vp, C.POINTER(QMlpDesc)] + [_vp] * 9
         L.lux_cuda_qmlp_noalloc.argtypes = [_vp, C.POINTER(QMlpDesc)] + [_vp] * 8
         L.lux_cuda_peer_comm_create.restype = C.c_int
@@ -540,6 +551,49 @@ class Context:
     def requantize(self, x: Buffer, out: Buffer, n: int, input_scale: float, output_scale: float, zero_point: int) -> None:
         _check(self.backend.lib.lux_cuda_requantize_int32_to_int8(self.handle, x.handle, out.handle, n, input_scale,
                                                                   output_scale, zero_point), "lux_cuda_requantize_int32_to_int8")
+
+    # attention side (lux/gpu/attention_ext.h); every tensor is an f32 Buffer in the shader's layout
+    def rope_precompute_cache(self, cos: Buffer, sin: Buffer, max_seq_len: int, head_dim: int, theta_base: float, flags: int = 0) -> None:
+        _check(self.backend.lib.lux_cuda_rope_precompute_cache_f32(self.handle, cos.handle, sin.handle, max_seq_len, head_dim,
+                                                                   theta_base, flags), "lux_cuda_rope_precompute_cache_f32")
+
+    def rope(self, x: Buffer, out: Buffer, batch: int, seq: int, heads: int, head_dim: int, cos: Buffer | None = None,
+             sin: Buffer | None = None, position_ids: Buffer | None = None, theta_base: float = 10000.0,
+             position_offset: int = 0, ntk_scale: float = 0.0, flags: int = 0) -> None:
+        h = lambda b: b.handle if b is not None else None
+        _check(self.backend.lib.lux_cuda_rope_f32(self.handle, x.handle, out.handle, h(cos), h(sin), h(position_ids), batch, seq,
+                                                  heads, head_dim, theta_base, position_offset, ntk_scale, flags), "lux_cuda_rope_f32")
+
+    def rope_qk(self, q: Buffer, k: Buffer, cos: Buffer, sin: Buffer, batch: int, seq: int, heads: int, kv_heads: int,
+                head_dim: int, position_offset: int = 0, flags: int = 0) -> None:
+        _check(self.backend.lib.lux_cuda_rope_qk_f32(self.handle, q.handle, k.handle, cos.handle, sin.handle, batch, seq, heads,
+                                                     kv_heads, head_dim, position_offset, flags), "lux_cuda_rope_qk_f32")
+
+    def sdpa(self, q: Buffer, k: Buffer, v: Buffer, out: Buffer, batch: int, heads: int, kv_heads: int, seq_q: int, seq_kv: int,
+             head_dim: int, scale: float, lse: Buffer | None = None, flags: int = 0) -> None:
+        _check(self.backend.lib.lux_cuda_sdpa_f32(self.handle, q.handle, k.handle, v.handle, out.handle,
+                                                  lse.handle if lse is not None else None, batch, heads, kv_heads, seq_q, seq_kv,
+                                                  head_dim, scale, flags), "lux_cuda_sdpa_f32")
+
+    def update_kv_cache(self, k: Buffer, v: Buffer, k_cache: Buffer, v_cache: Buffer, batch: int, kv_heads: int, seq_q: int,
+                        cache_len: int, max_cache_len: int, head_dim: int, flags: int = 0) -> None:
+        _check(self.backend.lib.lux_cuda_update_kv_cache_f32(self.handle, k.handle, v.handle, k_cache.handle, v_cache.handle, batch,
+                                                             kv_heads, seq_q, cache_len, max_cache_len, head_dim, flags),
+               "lux_cuda_update_kv_cache_f32")
+
+    def sdpa_kv_cache(self, q: Buffer, k_cache: Buffer, v_cache: Buffer, out: Buffer, batch: int, heads: int, kv_heads: int,
+                      seq_q: int, cache_len: int, max_cache_len: int, head_dim: int, scale: float, flags: int = 0) -> None:
+        _check(self.backend.lib.lux_cuda_sdpa_kv_cache_f32(self.handle, q.handle, k_cache.handle, v_cache.handle, out.handle, batch,
+                                                           heads, kv_heads, seq_q, cache_len, max_cache_len, head_dim, scale, flags),
+               "lux_cuda_sdpa_kv_cache_f32")
+
+    def paged_attention(self, q: Buffer, k_cache: Buffer, v_cache: Buffer, block_tables: Buffer, context_lens: Buffer, out: Buffer,
+                        num_seqs: int, heads: int, kv_heads: int, head_dim: int, block_size: int, max_blocks_per_seq: int,
+                        scale: float, flags: int = 0) -> None:
+        _check(self.backend.lib.lux_cuda_paged_attention_f32(self.handle, q.handle, k_cache.handle, v_cache.handle,
+                                                             block_tables.handle, context_lens.handle, out.handle, num_seqs, heads,
+                                                             kv_heads, head_dim, block_size, max_blocks_per_seq, scale, flags),
+               "lux_cuda_paged_attention_f32")
 
     def qmlp(self, x: Buffer, gate_up: DeviceQLayer, down: DeviceQLayer, h: Buffer, y: Buffer, M: int,
              act_dtype: int, flags: int = 0) -> None:

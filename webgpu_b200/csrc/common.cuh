@@ -47,6 +47,8 @@ struct Context {
     uint32_t*      d_absmax = nullptr;      // device word for lux_cuda_dynamic_quantize's tensor-wide max (allocated with the context)
     void*          d_splitk = nullptr;      // split-K exchange of the weights-in-TMEM GEMM: 128 KB per CTA pair,
     size_t         d_splitk_bytes = 0;      // allocated with the context (no entry point allocates for it)
+    void*          d_attn = nullptr;        // partial results of attention calls that split the keys over CTAs:
+    size_t         d_attn_bytes = 0;        // 16 MB, allocated with the context (a call takes fewer slices rather than allocate)
     std::mutex     mu;                      // guards the staging buffers
     int            sm_count = 148;
     // A kernel of this library that WRITES a buffer a later matmul may bind as weights, scales or

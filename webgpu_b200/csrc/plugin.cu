@@ -112,8 +112,13 @@ static LuxBackendContext* cuda_create_context(int device_index) {
                                        (size_t)(ctx->prop.multiProcessorCount / 4) * (384u << 10));
         ok = cudaMalloc(&ctx->d_splitk, ctx->d_splitk_bytes) == cudaSuccess;
     }
+    if (ok) {
+        ctx->d_attn_bytes = 16u << 20;
+        ok = cudaMalloc(&ctx->d_attn, ctx->d_attn_bytes) == cudaSuccess;
+    }
     if (!ok) {
         cudaGetLastError();
+        if (ctx->d_attn) cudaFree(ctx->d_attn);
         if (ctx->d_splitk) cudaFree(ctx->d_splitk);
         if (ctx->d_absmax) cudaFree(ctx->d_absmax);
         if (ctx->h_status) cudaFreeHost(ctx->h_status);
@@ -135,6 +140,7 @@ static void cuda_destroy_context(LuxBackendContext* context) {
     cudaStreamSynchronize(ctx->stream);
     if (ctx->h_stage) cudaFreeHost(ctx->h_stage);
     if (ctx->d_stage) cudaFree(ctx->d_stage);
+    if (ctx->d_attn) cudaFree(ctx->d_attn);
     if (ctx->d_splitk) cudaFree(ctx->d_splitk);
     if (ctx->d_absmax) cudaFree(ctx->d_absmax);
     if (ctx->h_status) cudaFreeHost(ctx->h_status);
