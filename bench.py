@@ -390,7 +390,8 @@ def bench_sweep(args, peaks):
                       "l2": "weight copies rotated per step so that every launch streams from HBM",
                       "timing": "CUDA graph replays, CUDA events on the launching stream"},
            "data": "synthetic", "layers": {}}
-    for name in synth.SWEEP_LAYERS:
+    attention_only = args.workload == "attention"       # the decode-attention block alone (small enough to profile)
+    for name in ([] if attention_only else synth.SWEEP_LAYERS):
         _, layer = synth.config4(name, 1)
         pool = rig.pool(layer, int(2.9 * L2_BYTES))
         for M in synth.SWEEP_M:
@@ -404,23 +405,27 @@ def bench_sweep(args, peaks):
                 "frac_of_measured_hbm": ab / sec / 1e9 / peaks["hbm"], "tflops": 2.0 * M * layer.N * layer.K / sec / 1e12}
         del pool
     # the quantize kernel: f32 [14336, 4096] -> int4 g128 (reads 4 bytes, writes ~0.53 per element)
-    wf = torch.randn(14336, 4096, device="cuda", dtype=torch.float32)
-    wb = ctx.wrap(wf.data_ptr(), wf.numel() * 4)
-    qw, qs, qz = ctx.alloc(14336 * 2048), ctx.alloc(14336 * 32 * 2), ctx.alloc(14336 * 16)
-    import ctypes as C
-    d = B.make_desc(0, 14336, 4096, 4, 128, B.F32, B.F16, B.F32, B.FLAG_NO_SYNC)
-    lib = rig.backend.lib
-    sec, _ = rig.time_graph(lambda i: lib.lux_cuda_qquantize(ctx.handle, C.byref(d), wb.handle, qw.handle, qs.handle, qz.handle),
-                            1, steps, args.warmup)
-    qbytes = 14336 * 4096 * 4 + 14336 * 2048 + 14336 * 32 * 2 + 14336 * 16
-    out["quantize_int4_14336x4096"] = {"us": sec * 1e6, "gbs": qbytes / sec / 1e9, "frac_of_measured_hbm": qbytes / sec / 1e9 / peaks["hbm"],
-                                       "note": "235 MB read + 31 MB written per launch: larger than L2"}
-    del wf
+    if not attention_only:
+        wf = torch.randn(14336, 4096, device="cuda", dtype=torch.float32)
+        wb = ctx.wrap(wf.data_ptr(), wf.numel() * 4)
+        qw, qs, qz = ctx.alloc(14336 * 2048), ctx.alloc(14336 * 32 * 2), ctx.alloc(14336 * 16)
+        import ctypes as C
+        d = B.make_desc(0, 14336, 4096, 4, 128, B.F32, B.F16, B.F32, B.FLAG_NO_SYNC)
+        lib = rig.backend.lib
+        sec, _ = rig.time_graph(lambda i: lib.lux_cuda_qquantize(ctx.handle, C.byref(d), wb.handle, qw.handle, qs.handle, qz.handle),
+                                1, steps, args.warmup)
+        qbytes = 14336 * 4096 * 4 + 14336 * 2048 + 14336 * 32 * 2 + 14336 * 16
+        out["quantize_int4_14336x4096"] = {"us": sec * 1e6, "gbs": qbytes / sec / 1e9, "frac_of_measured_hbm": qbytes / sec / 1e9 / peaks["hbm"],
+                                           "note": "235 MB read + 31 MB written per launch: larger than L2"}
+        del wf
     # decode attention over an f32 KV cache with Llama-3-8B's heads (32 query, 8 key/value, 128 wide):
     # contiguous cache (sdpa_kv_cache) and 16-token pages (paged_attention), bytes = K and V read once
     H, HKV, D = 32, 8, 128
     out["attention_decode"] = {}
-    for batch, ctx_len in ((1, 4096), (1, 32768), (8, 4096), (32, 4096)):
+    shapes = ((1, 4096), (1, 32768), (8, 4096), (32, 4096))
+    if args.attention_shape:
+        shapes = (tuple(int(v) for v in args.attention_shape.split("x")),)
+    for batch, ctx_len in shapes:
         kv_bytes = 2 * batch * HKV * ctx_len * D * 4
         copies = max(1, -(-int(2.9 * L2_BYTES) // kv_bytes))
         caches = [(torch.randn(batch, HKV, ctx_len, D, device="cuda"), torch.randn(batch, HKV, ctx_len, D, device="cuda")) for _ in range(copies)]
@@ -818,7 +823,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=1, help="batch M of the tensor-parallel FFN workload")
-    ap.add_argument("--workload", default="auto", choices=["auto", "gemv", "tp_mlp", "sweep"])
+    ap.add_argument("--workload", default="auto", choices=["auto", "gemv", "tp_mlp", "sweep", "attention"])
+    ap.add_argument("--attention-shape", default="", help="attention workload: one BATCHxCONTEXT shape instead of the built-in four")
     ap.add_argument("--collective", default="push", choices=["push", "nccl"],
                     help="all-reduce of the tensor-parallel FFN: the plugin's push all-reduce over peer memory "
                          "(falls back to NCCL if the peer mapping is refused) or NCCL")
@@ -833,7 +839,7 @@ def main():
     else:
         _, _, world = dist_env()
         use_tp = args.workload == "tp_mlp" or (args.workload == "auto" and (args.gpus > 1 or world > 1))
-        if args.workload == "sweep":
+        if args.workload in ("sweep", "attention"):
             line = bench_sweep(args, peaks)
         else:
             line = bench_tp(args, peaks) if use_tp else bench_single(args, peaks)

@@ -12,19 +12,29 @@
 //   * a producer warp streams 32-key chunks of K and V into a ring in shared memory with bulk
 //     copies (cp.async.bulk, one per contiguous run: a whole chunk for a contiguous cache, one per
 //     page for a paged one, the page numbers taken from a copy of the block table in shared
-//     memory), each chunk signalled through an mbarrier; up to four chunks are in flight;
+//     memory), each chunk signalled through an mbarrier; two CTAs of nine warps share an SM, each
+//     with a ring of three chunks (D = 128);
 //   * eight consumer warps share a chunk: a key is handled by 8 lanes, each holding 16-byte columns
-//     of the row, so a warp takes 4 keys per step; every lane keeps up to 4 query rows in registers
+//     of the row, so a warp takes 4 keys per step; every lane keeps two query rows in registers
 //     and runs the running-maximum softmax (the rule of sdpa_flash, :217-362) on its own keys; lanes,
 //     warps and, for long contexts, CTAs are merged at the end by the same rule (the partition
 //     statistics of paged_attention_v2, paged.wgsl:351-405, are this merge);
-//   * keys are split over CTAs when there are fewer (sequence, KV head) pairs than SMs; a small
-//     second kernel, resident early through programmatic dependent launch, merges the slices.
-// Every wait is bounded: a wait that gives up sets the CTA's abort flag, every warp leaves its loop,
-// the device status word reports 0x7C050008 and the output of that CTA is not written.
+//   * only ONE thread per CTA polls an mbarrier (warp 0, for the chunk to land).  Everything else
+//     waits on named barriers (bar.sync / bar.arrive), where the hardware parks a warp until the
+//     count is reached: the other consumer warps for "chunk ready", the producer for "stage free".
+//     With every warp polling its mbarrier the kernel ran at 2.2-5.1 TB/s depending on how many
+//     warps happened to be waiting; parked, at 5.0-6.5 TB/s on the same shapes (polls travel the same
+//     queue as shared-memory loads and shuffles, and starved the warps that had work);
+//   * keys are split over CTAs when there are fewer (sequence, KV head) pairs than SM slots, and
+//     each CTA walks its chunks from a different starting point; a small second kernel, resident
+//     early through programmatic dependent launch, merges the slices.
+// The one polling wait is bounded: if it gives up it sets the CTA's abort flag, every warp leaves
+// its loop (the consumers first release the stages the producer may be parked on), the device
+// status word reports 0x7C050008 and the output of that CTA is not written.
 #include <algorithm>
 #include <cmath>
 #include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 #include "tc_ptx.cuh"
@@ -39,9 +49,11 @@ using namespace tcptx;
 constexpr int ATT_CW = 8;                       // consumer warps
 constexpr int ATT_THREADS = (ATT_CW + 1) * 32;  // + the producer warp
 constexpr int ATT_CK = 32;                      // keys per staged chunk
-constexpr int ATT_MAX_STAGES = 4;
+constexpr int ATT_MAX_STAGES = 6;
+constexpr int ATT_CTAS_PER_SM = 2;
 constexpr int ATT_TABLE = 2048;                 // block-table entries a CTA keeps in shared memory
 constexpr int ATT_HEADER = 128;                 // barriers + abort flag
+constexpr size_t ATT_SMEM_BUDGET = 110u << 10;        // per CTA: two CTAs share an SM
 constexpr float ATT_NEG = -3.0e38f;             // "no key seen yet" in the base-2 score domain
 constexpr float ATT_LOG2E = 1.4426950408889634f;
 constexpr float ATT_LN2 = 0.6931471805599453f;
@@ -69,14 +81,33 @@ struct AttnParams {
     float qscale;                // scale * log2(e)
 };
 
+// 2^x for x <= 0 (results below the normal range flush to 0), one MUFU operation
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Named barriers: a warp that waits on one is parked by the hardware and issues nothing, unlike a
+// warp polling an mbarrier, whose polls share the queue that shared-memory loads and shuffles go
+// through.  With eight warps polling for every chunk the warps that had work ran 2-3 times slower.
+__device__ __forceinline__ void named_sync(uint32_t id, uint32_t threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+__device__ __forceinline__ void named_arrive(uint32_t id, uint32_t threads) {
+    asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+constexpr uint32_t ATT_BAR_READY = 1;           // consumer warps: the chunk has landed (warp 0 polled for it)
+constexpr uint32_t ATT_BAR_FREE0 = 2;           // + stage: every consumer warp is done with the stage (producer waits)
+
 __device__ __forceinline__ uint32_t row_len(const AttnParams& p, uint32_t qi, uint32_t kv_len) {
     return p.causal ? min(p.causal_base + qi + 1u, kv_len) : kv_len;
 }
 
-template <int VPL, int RT>
-__global__ void __launch_bounds__(ATT_THREADS, 1) lux_attn_stream_f32(const AttnParams p) {
+template <int VPL, int RT, bool FULL>
+__global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) lux_attn_stream_f32(const AttnParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
-    const uint32_t bar_full = smem_u32(smem), bar_empty = bar_full + 8u * ATT_MAX_STAGES;
+    const uint32_t bar_full = smem_u32(smem);
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + 16 * ATT_MAX_STAGES);
     int32_t* table = reinterpret_cast<int32_t*>(smem + ATT_HEADER);
     float* stages = reinterpret_cast<float*>(smem + ATT_HEADER + (p.block_size ? ATT_TABLE * 4 : 0));
@@ -106,12 +137,16 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) lux_attn_stream_f32(const Attn
     const uint32_t k_end = min(lmax, k_begin + p.split_keys);
     const uint32_t nchunks = k_end > k_begin ? (k_end - k_begin + ATT_CK - 1) / ATT_CK : 0u;
     const uint32_t tbl0 = p.block_size ? k_begin / p.block_size : 0u;
+    // Every CTA walks its chunks from a different starting point (and wraps around), so that the CTAs
+    // of a wave, which start together and advance at the same pace, are not all at the same offset
+    // of equally spaced slices.
+    const uint32_t rot = nchunks ? (blockIdx.x * 2654435761u >> 8) % nchunks : 0u;
+    auto chunk_at = [&](uint32_t c) { const uint32_t cc = c + rot; return cc >= nchunks ? cc - nchunks : cc; };
 
     if (tid == 0) {
         *abort_flag = 0u;
         for (uint32_t s = 0; s < NS; s++) {
             mbar_init(bar_full + 8u * s, 1u);
-            mbar_init(bar_empty + 8u * s, ATT_CW);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -142,8 +177,11 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) lux_attn_stream_f32(const Attn
         // ---- producer: one chunk = keys [t0, t0 + nk) of K and of V ------------------------------
         for (uint32_t c = 0; c < nchunks; c++) {
             const uint32_t s = c % NS;
-            if (c >= NS && !warp_wait_relaxed(bar_empty + 8u * s, ((c / NS) - 1u) & 1u, abort_flag, lane)) break;
-            const uint32_t t0 = k_begin + c * ATT_CK, nk = min((uint32_t)ATT_CK, k_end - t0);
+            if (c >= NS) {
+                named_sync(ATT_BAR_FREE0 + s, ATT_THREADS);          // all consumer warps have left the stage
+                if (*abort_flag) break;
+            }
+            const uint32_t t0 = k_begin + chunk_at(c) * ATT_CK, nk = min((uint32_t)ATT_CK, k_end - t0);
             const uint32_t bar = bar_full + 8u * s;
             float* ks = stages + s * stage_floats;
             float* vs = ks + (size_t)ATT_CK * D;
@@ -174,7 +212,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) lux_attn_stream_f32(const Attn
             const uint32_t r = row0 + rg * RT + i;
             const bool valid = r < R;
             const uint32_t qi = valid ? r / p.group : 0u, head = g * p.group + (valid ? r % p.group : 0u);
-            len[i] = valid ? row_len(p, qi, kv_len) : 0u;
+            len[i] = valid ? row_len(p, qi, kv_len) : 0xffffffffu;       // a padding row: q = 0, never written, never masks a chunk
             const float* qr = p.q + (((size_t)b * p.heads + head) * p.seq_q + qi) * D;
             m[i] = ATT_NEG;
             l[i] = 0.0f;
@@ -186,75 +224,114 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) lux_attn_stream_f32(const Attn
                 o[i][j] = make_float4(0.f, 0.f, 0.f, 0.f);
             }
         }
-        for (uint32_t c = 0; c < nchunks; c++) {
-            const uint32_t s = c % NS;
-            if (!warp_wait(bar_full + 8u * s, (c / NS) & 1u, abort_flag, lane)) break;
-            const float* ks = stages + s * stage_floats;
-            const float* vs = ks + (size_t)ATT_CK * D;
-            const uint32_t t0 = k_begin + c * ATT_CK, nk = min((uint32_t)ATT_CK, k_end - t0);
-            for (uint32_t kb = kslot * 4u; kb < nk; kb += wpg * 4u) {
-                const uint32_t key = kb + (uint32_t)kg, t = t0 + key;
-                const bool inb = key < nk;
-                float sc[RT];
+        // One step: the warp's four keys (one per group of 8 lanes) against its RT rows.  The
+        // running maximum of a lane is only raised when a score passes it by more than 8 (in the
+        // base-2 domain), so weights stay below 2^8 and the common step has no rescaling in it:
+        // scores, one exp2 per row, the weighted sum.  MASKED steps (the last chunk of a slice, a
+        // causal edge) check each key against the chunk and each row's length.
+        const uint32_t row_bytes = D * 4u, lane_off = (uint32_t)sub * 16u;
+        auto lds4 = [](uint32_t addr) {
+            float4 r;
+            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w) : "r"(addr));
+            return r;
+        };
+        auto step = [&](auto masked, uint32_t kaddr, uint32_t vaddr, bool inb, uint32_t t) {
+            constexpr bool MASKED = decltype(masked)::value;
+            float sc[RT];
 #pragma unroll
-                for (int i = 0; i < RT; i++) sc[i] = 0.0f;
+            for (int i = 0; i < RT; i++) sc[i] = 0.0f;
 #pragma unroll
-                for (int j = 0; j < VPL; j++) {
-                    float4 kk = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (inb && col_ok[j]) kk = *(reinterpret_cast<const float4*>(ks + (size_t)key * D) + j * 8 + sub);
+            for (int j = 0; j < VPL; j++) {
+                float4 kk = make_float4(0.f, 0.f, 0.f, 0.f);
+                if ((FULL || col_ok[j]) && (!MASKED || inb)) kk = lds4(kaddr + (uint32_t)j * 128u);
 #pragma unroll
-                    for (int i = 0; i < RT; i++)
-                        sc[i] = fmaf(q[i][j].x, kk.x, fmaf(q[i][j].y, kk.y, fmaf(q[i][j].z, kk.z, fmaf(q[i][j].w, kk.w, sc[i]))));
-                }
+                for (int i = 0; i < RT; i++)
+                    sc[i] = fmaf(q[i][j].x, kk.x, fmaf(q[i][j].y, kk.y, fmaf(q[i][j].z, kk.z, fmaf(q[i][j].w, kk.w, sc[i]))));
+            }
+#pragma unroll
+            for (int i = 0; i < RT; i++) {
+                sc[i] += __shfl_xor_sync(0xffffffffu, sc[i], 1);
+                sc[i] += __shfl_xor_sync(0xffffffffu, sc[i], 2);
+                sc[i] += __shfl_xor_sync(0xffffffffu, sc[i], 4);
+            }
+            bool vis[RT], up = false, any = false;
+#pragma unroll
+            for (int i = 0; i < RT; i++) {
+                vis[i] = !MASKED || (inb && t < len[i]);
+                up |= vis[i] && sc[i] > m[i] + 8.0f;
+                any |= vis[i];
+            }
+            if (__any_sync(0xffffffffu, up)) {
 #pragma unroll
                 for (int i = 0; i < RT; i++) {
-                    sc[i] += __shfl_xor_sync(0xffffffffu, sc[i], 1);
-                    sc[i] += __shfl_xor_sync(0xffffffffu, sc[i], 2);
-                    sc[i] += __shfl_xor_sync(0xffffffffu, sc[i], 4);
-                }
-                float pw[RT];
-                bool any = false;
-#pragma unroll
-                for (int i = 0; i < RT; i++) {
-                    const bool vis = inb && t < len[i];
-                    const float mn = vis ? fmaxf(m[i], sc[i]) : m[i];
-                    if (mn > m[i]) {
-                        const float alpha = exp2f(m[i] - mn);
-                        l[i] *= alpha;
-#pragma unroll
-                        for (int j = 0; j < VPL; j++) {
-                            o[i][j].x *= alpha; o[i][j].y *= alpha; o[i][j].z *= alpha; o[i][j].w *= alpha;
-                        }
-                        m[i] = mn;
-                    }
-                    pw[i] = vis ? exp2f(sc[i] - mn) : 0.0f;
-                    l[i] += pw[i];
-                    any |= vis;
-                }
-                if (any) {
+                    const float mn = vis[i] ? fmaxf(m[i], sc[i]) : m[i];
+                    const float alpha = ex2(m[i] - mn);
+                    l[i] *= alpha;
 #pragma unroll
                     for (int j = 0; j < VPL; j++) {
-                        float4 vv = make_float4(0.f, 0.f, 0.f, 0.f);
-                        if (col_ok[j]) vv = *(reinterpret_cast<const float4*>(vs + (size_t)key * D) + j * 8 + sub);
+                        o[i][j].x *= alpha; o[i][j].y *= alpha; o[i][j].z *= alpha; o[i][j].w *= alpha;
+                    }
+                    m[i] = mn;
+                }
+            }
+            float pw[RT];
 #pragma unroll
-                        for (int i = 0; i < RT; i++) {
-                            o[i][j].x = fmaf(pw[i], vv.x, o[i][j].x);
-                            o[i][j].y = fmaf(pw[i], vv.y, o[i][j].y);
-                            o[i][j].z = fmaf(pw[i], vv.z, o[i][j].z);
-                            o[i][j].w = fmaf(pw[i], vv.w, o[i][j].w);
-                        }
+            for (int i = 0; i < RT; i++) {
+                pw[i] = ex2(sc[i] - m[i]);
+                if (MASKED && !vis[i]) pw[i] = 0.0f;
+                l[i] += pw[i];
+            }
+            if (!MASKED || any) {
+#pragma unroll
+                for (int j = 0; j < VPL; j++) {
+                    float4 vv = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (FULL || col_ok[j]) vv = lds4(vaddr + (uint32_t)j * 128u);
+#pragma unroll
+                    for (int i = 0; i < RT; i++) {
+                        o[i][j].x = fmaf(pw[i], vv.x, o[i][j].x);
+                        o[i][j].y = fmaf(pw[i], vv.y, o[i][j].y);
+                        o[i][j].z = fmaf(pw[i], vv.z, o[i][j].z);
+                        o[i][j].w = fmaf(pw[i], vv.w, o[i][j].w);
                     }
                 }
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_empty + 8u * s);
+        };
+        uint32_t min_len = 0xffffffffu;
+#pragma unroll
+        for (int i = 0; i < RT; i++) min_len = min(min_len, len[i]);
+        const uint32_t stage0 = smem_u32(stages), stage_bytes = 2u * ATT_CK * row_bytes, v_off = ATT_CK * row_bytes;
+        for (uint32_t c = 0; c < nchunks; c++) {
+            const uint32_t s = c % NS;
+            // one poller per CTA: warp 0 waits for the copies, the named barrier releases the other seven
+            if (warp == 0) warp_wait(bar_full + 8u * s, (c / NS) & 1u, abort_flag, lane);
+            named_sync(ATT_BAR_READY, ATT_CW * 32);
+            if (*abort_flag) {
+                // the producer may be parked on the stages this warp would still have released
+                for (uint32_t cc = c; cc < c + NS && cc + NS < nchunks; cc++) named_arrive(ATT_BAR_FREE0 + cc % NS, ATT_THREADS);
+                break;
+            }
+            const uint32_t t0 = k_begin + chunk_at(c) * ATT_CK, nk = min((uint32_t)ATT_CK, k_end - t0);
+            const uint32_t kchunk = stage0 + s * stage_bytes + lane_off;
+            if (nk == ATT_CK && t0 + ATT_CK <= min_len) {
+                for (uint32_t kb = kslot * 4u; kb < ATT_CK; kb += wpg * 4u) {
+                    const uint32_t ka = kchunk + (kb + (uint32_t)kg) * row_bytes;
+                    step(std::false_type{}, ka, ka + v_off, true, 0u);
+                }
+            } else {
+                for (uint32_t kb = kslot * 4u; kb < nk; kb += wpg * 4u) {
+                    const uint32_t key = kb + (uint32_t)kg, ka = kchunk + key * row_bytes;
+                    step(std::true_type{}, ka, ka + v_off, key < nk, t0 + key);
+                }
+            }
+            // done with the stage (not needed for the last NS chunks: nobody refills them)
+            if (c + NS < nchunks) named_arrive(ATT_BAR_FREE0 + s, ATT_THREADS);
         }
         // the four key slots of the warp, merged by the running-maximum rule
 #pragma unroll
         for (int i = 0; i < RT; i++) {
             float mm = fmaxf(m[i], __shfl_xor_sync(0xffffffffu, m[i], 8));
             mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, 16));
-            const float alpha = exp2f(m[i] - mm);
+            const float alpha = ex2(m[i] - mm);
             m[i] = mm;
             l[i] *= alpha;
             l[i] += __shfl_xor_sync(0xffffffffu, l[i], 8);
@@ -313,7 +390,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) lux_attn_stream_f32(const Attn
         float L = 0.0f, acc = 0.0f;
         for (uint32_t w = 0; w < wpg; w++) {
             const float* src = mrg + ((size_t)(w * p.rgp + rgi) * RT + ii) * MS;
-            const float wgt = exp2f(src[D] - M);
+            const float wgt = ex2(src[D] - M);
             L = fmaf(src[D + 1], wgt, L);
             acc = fmaf(src[d], wgt, acc);
         }
@@ -549,14 +626,17 @@ uint32_t pow2ceil(uint32_t v) {
 }
 
 using AttnKernel = void (*)(const AttnParams);
-template <int VPL, int RT> AttnKernel stream_kernel() { return lux_attn_stream_f32<VPL, RT>; }
-AttnKernel pick_stream(int vpl, int rt) {
+template <int VPL, int RT> AttnKernel stream_kernel(bool full) {
+    return full ? lux_attn_stream_f32<VPL, RT, true> : lux_attn_stream_f32<VPL, RT, false>;
+}
+// full: head_dim is exactly VPL * 32, so no lane has a column to skip
+AttnKernel pick_stream(int vpl, int rt, bool full) {
     switch (vpl * 10 + rt) {
-        case 11: return stream_kernel<1, 1>(); case 12: return stream_kernel<1, 2>(); case 14: return stream_kernel<1, 4>();
-        case 21: return stream_kernel<2, 1>(); case 22: return stream_kernel<2, 2>(); case 24: return stream_kernel<2, 4>();
-        case 31: return stream_kernel<3, 1>(); case 32: return stream_kernel<3, 2>(); case 34: return stream_kernel<3, 4>();
-        case 41: return stream_kernel<4, 1>(); case 42: return stream_kernel<4, 2>(); case 44: return stream_kernel<4, 4>();
-        case 81: return stream_kernel<8, 1>(); case 82: return stream_kernel<8, 2>();
+        case 11: return stream_kernel<1, 1>(full); case 12: return stream_kernel<1, 2>(full);
+        case 21: return stream_kernel<2, 1>(full); case 22: return stream_kernel<2, 2>(full);
+        case 31: return stream_kernel<3, 1>(full); case 32: return stream_kernel<3, 2>(full);
+        case 41: return stream_kernel<4, 1>(full); case 42: return stream_kernel<4, 2>(full);
+        case 81: return stream_kernel<8, 1>(full);
     }
     return nullptr;
 }
@@ -582,51 +662,67 @@ LuxBackendError attn_launch(Context* ctx, AttnParams& p, uint32_t max_keys, uint
     int vpl = (int)((D + 31) / 32);
     if (vpl > 4) vpl = 8;
     const uint32_t R = p.group * p.seq_q;
-    int rt = R >= 3 ? 4 : (int)R;
-    if (vpl == 8 && rt == 4) rt = 2;
+    // two query rows per lane: more would halve the shared-memory reads per row, but the registers
+    // of four rows leave one CTA of nine warps per SM, too few to hide the latency of each step
+    const int rt = R >= 2 && vpl <= 4 ? 2 : 1;
     p.rgp = pow2ceil(std::min<uint32_t>((R + rt - 1) / rt, ATT_CW));
     const uint32_t rpb = rt * p.rgp;
     p.row_blocks = (R + rpb - 1) / rpb;
     const size_t items = (size_t)p.batch * p.kv_heads * p.row_blocks;
-    // slices of the keys: enough CTAs for every SM when there are few (sequence, KV head) pairs, at
-    // least 128 keys each; the block-table copy and the scratch for the partial results cap them
-    uint32_t nsplit = 1;
-    if (items < (size_t)ctx->sm_count && max_keys > 128) nsplit = std::min<uint32_t>((uint32_t)(ctx->sm_count / items), (max_keys + 127) / 128);
+    // Slices of the keys.  CTAs run two per SM, so the grid should fill whole waves of 2 x SMs; a slice
+    // costs a CTA start-up and a row in the merge, about as much as streaming 64 keys, and is at
+    // least 128 keys long.  The block-table copy caps the pages a slice may span.
+    auto geometry = [&](uint32_t want) {
+        p.split_keys = std::max<uint32_t>(((max_keys + want - 1) / want + ATT_CK - 1) / ATT_CK * ATT_CK, ATT_CK);
+        p.nsplit = std::max<uint32_t>((max_keys + p.split_keys - 1) / p.split_keys, 1u);
+    };
+    uint32_t min_split = 1;
     if (p.block_size) {
-        const uint64_t cap = (uint64_t)(ATT_TABLE - 2) * p.block_size;
-        nsplit = std::max<uint32_t>(nsplit, (uint32_t)((max_keys + cap - 1) / cap));
+        // a slice (a multiple of the chunk) spans at most split_keys / block_size + 2 pages
+        const uint64_t cap = (uint64_t)(ATT_TABLE - 2) * p.block_size / ATT_CK * ATT_CK;
+        min_split = (uint32_t)std::max<uint64_t>((max_keys + cap - 1) / cap, 1);
     }
-    nsplit = std::max(nsplit, 1u);
-    p.split_keys = std::max<uint32_t>(((max_keys + nsplit - 1) / nsplit + ATT_CK - 1) / ATT_CK * ATT_CK, ATT_CK);
-    p.nsplit = std::max<uint32_t>((max_keys + p.split_keys - 1) / p.split_keys, 1u);
+    uint32_t best = min_split;
+    double best_score = -1.0;
+    const uint32_t sm = (uint32_t)ctx->sm_count * ATT_CTAS_PER_SM;
+    for (uint32_t n = min_split; n <= 256; n++) {
+        geometry(n);
+        if (p.nsplit != n) continue;                                   // rounding to chunks merged this count into a smaller one
+        if (n > min_split && p.split_keys < 128) break;
+        const double ctas = (double)items * n, waves = std::ceil(ctas / sm);
+        const double score = ctas / (waves * sm) * p.split_keys / (p.split_keys + 64.0);
+        if (score > best_score * 1.02) {                               // a larger count has to earn its merge
+            best_score = score;
+            best = n;
+        }
+        if (ctas > 8.0 * sm) break;
+    }
+    geometry(g_tune.attn_splits > 0 ? std::max<uint32_t>((uint32_t)g_tune.attn_splits, min_split) : best);
     if (p.nsplit > 256) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;     // a context beyond 256 x 2046 pages
     const size_t part_bytes = p.nsplit > 1 ? out_rows * p.nsplit * (D + 2) * 4 : 0;
     if (part_bytes > ctx->d_attn_bytes) {
         // fewer slices than wanted rather than an allocation inside a call
         const uint32_t fit = (uint32_t)(ctx->d_attn_bytes / (out_rows * (D + 2) * 4));
-        if (fit < 2 && p.block_size && (uint64_t)max_keys > (uint64_t)(ATT_TABLE - 2) * p.block_size) return LUX_BACKEND_ERROR_OUT_OF_MEMORY;
-        nsplit = std::max(fit, 1u);
-        if (p.block_size) {
-            const uint64_t cap = (uint64_t)(ATT_TABLE - 2) * p.block_size;
-            if ((uint64_t)nsplit * cap < max_keys) return LUX_BACKEND_ERROR_OUT_OF_MEMORY;
-        }
-        p.split_keys = std::max<uint32_t>(((max_keys + nsplit - 1) / nsplit + ATT_CK - 1) / ATT_CK * ATT_CK, ATT_CK);
-        p.nsplit = std::max<uint32_t>((max_keys + p.split_keys - 1) / p.split_keys, 1u);
+        if (std::max(fit, 1u) < min_split) return LUX_BACKEND_ERROR_OUT_OF_MEMORY;
+        geometry(std::max(fit, 1u));
     }
     p.part = p.nsplit > 1 ? (float*)ctx->d_attn : nullptr;
     const size_t stage_bytes = (size_t)2 * ATT_CK * D * 4;
     const size_t fixed = ATT_HEADER + (p.block_size ? ATT_TABLE * 4 : 0);
-    p.stages = (uint32_t)std::min<size_t>(ATT_MAX_STAGES, ((200u << 10) - fixed) / stage_bytes);
+    // heads wider than 128 take the whole SM's shared memory (one CTA per SM)
+    const size_t budget = D > 128 ? 2 * ATT_SMEM_BUDGET : ATT_SMEM_BUDGET;
+    p.stages = (uint32_t)std::min<size_t>(ATT_MAX_STAGES, (budget - fixed) / stage_bytes);
     const size_t smem = fixed + p.stages * stage_bytes;
-    AttnKernel kfn = pick_stream(vpl, rt);
+    const bool full = D == (uint32_t)vpl * 32u;
+    AttnKernel kfn = pick_stream(vpl, rt, full);
     if (!kfn || p.stages < 2) return LUX_BACKEND_ERROR_INTERNAL;
     static std::mutex mu;
-    static bool attr_set[16][9][5];
+    static bool attr_set[16][9][3][2];
     {
         std::lock_guard<std::mutex> lk(mu);
-        bool& done = attr_set[ctx->device & 15][vpl][rt];
+        bool& done = attr_set[ctx->device & 15][vpl][rt][full ? 1 : 0];
         if (!done) {
-            if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 << 10) != cudaSuccess)
+            if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(2 * ATT_SMEM_BUDGET)) != cudaSuccess)
                 return map_cuda(cudaGetLastError(), what);
             done = true;
         }
@@ -636,7 +732,7 @@ LuxBackendError attn_launch(Context* ctx, AttnParams& p, uint32_t max_keys, uint
     kfn<<<(unsigned)ctas, ATT_THREADS, smem, ctx->stream>>>(p);
     count_launch("lux_attn_stream_f32");
     if (p.nsplit > 1) {
-        cudaError_t e = launch_pdl(true, lux_attn_merge_f32, dim3((unsigned)out_rows), dim3(128), 0, ctx->stream, 1, (const float*)p.part,
+        cudaError_t e = launch_pdl(g_tune.pdl != 2, lux_attn_merge_f32, dim3((unsigned)out_rows), dim3(128), 0, ctx->stream, 1, (const float*)p.part,
                                    p.out, p.lse, p.context_lens, p.heads * p.seq_q, p.nsplit, D);
         if (e != cudaSuccess) return map_cuda(e, what);
         count_launch("lux_attn_merge_f32");
