@@ -46,6 +46,25 @@ def ffn70b(ctx):
     return d, gate_up, down, ctx.upload_layer(gate_up), ctx.upload_layer(down)
 
 
+@pytest.mark.parametrize("M", [3, 4])
+@pytest.mark.parametrize("name", list(synth.SWEEP_LAYERS))
+def test_config4_batches_3_and_4_default_route(ctx, backend, name, M):
+    """Batches of three and four rows take the block-fixed-point kernel (two 8-column MMA tiles per
+    weight fragment, a three-row batch padded to four) wherever the activations at three or four
+    byte planes fit beside the weight FIFOs: the K = 4096 layers.  `down` (K = 14336) stays with the
+    ring kernel."""
+    x, layer = synth.config4(name, M)
+    xb, L = ctx.upload(x), ctx.upload_layer(layer)
+    yb = ctx.alloc(M * layer.N * 2)
+    ctx.qmatmul(xb, L, yb, M, B.F16)
+    want = "lux_qgemv_i4_g128_stream" if layer.K > 8192 else "lux_qgemv_i4_g128_units_fx"
+    assert backend.last_kernel_name() == want
+    y = yb.to_host(np.float16, (M, layer.N))
+    ref = orc.qmatmul(x, *layer.triple, bits=4, group=128)
+    assert orc.rel_l2(y, ref) < 5e-3
+    assert ctx.last_device_status() == 0
+
+
 @pytest.mark.parametrize("M", [32, 256])
 def test_config5_full_size_default_route(ctx, backend, ffn70b, M):
     """gate_up 8192 -> 57344 with the SwiGLU epilogue, down 28672 -> 8192, and the two chained

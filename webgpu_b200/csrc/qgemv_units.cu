@@ -427,7 +427,7 @@ __global__ void __launch_bounds__(UW * 32, 1) lux_qgemv_i4_g128_units(const Unit
     }
 }
 
-// ---- block-fixed-point variant, batch MM = 1 or 2 ------------------------------------------------
+// ---- block-fixed-point variant, batch MM = 1, 2 or 4 (three rows run as four) -------------------------
 // Here the FIFOs are filled by TMA instead of cp.async: per-lane copies stall the REQUESTING warp
 // once the SM's load queue is full, which kept the compute warps from computing while the
 // memory pipe was busy.  One elected lane per warp asks for a whole chunk (one 3-D box:
@@ -436,8 +436,9 @@ __global__ void __launch_bounds__(UW * 32, 1) lux_qgemv_i4_g128_units(const Unit
 // gives up sets a flag, every warp leaves its loop, and the status word reports it.
 //
 // Shared memory: [FIFOs: UW x S x CG KB, 1024-byte aligned]
-// [xq: G x (4 planes x MM) x 128 signed bytes, each 128 in B-fragment order]
-// [xmeta: G x 8 columns x {coef, digit sum}; column = plane (MM = 1) or 2 plane + m (MM = 2)]
+// [xq: G x NT column tiles x (planes x MMT) x 128 signed bytes, each 128 in B-fragment order; a column tile
+//  is the 8-column B operand of one MMA and holds MMT = min(MM, 2) batch rows, NT = MM / MMT tiles]
+// [xmeta: G x NT x 8 columns x {coef, digit sum}; column = plane (MM = 1) or 2 plane + (m & 1)]
 // [scales][zero-points][partials: units_cap x 16 rows x MM float][unit table][barriers][flag]
 //
 // B-fragment order of one (group, plane, batch row): lane column t' = k >> 5 owns 32 bytes; inside,
@@ -495,14 +496,17 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
     constexpr int NACC = SWIGLU ? 2 : 1;
     constexpr int CHUNK = CG * 1024;
     constexpr int UW = UWT;                             // warps per CTA (shadows the file-wide 16)
-    const int XG = p.planes * MM * 128;                 // bytes of xq per group
+    constexpr int MMT = MM < 2 ? MM : 2;                // batch rows per column tile
+    constexpr int NT = MM / MMT;                        // column tiles (MMAs per weight fragment pair)
+    const int XT = p.planes * MMT * 128;                // bytes of xq per (group, column tile)
+    const int XG = XT * NT;                             // bytes of xq per group
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
 
     unsigned char* fifo = smem + (size_t)warp * p.S * CHUNK;
     unsigned char* xq = smem + (size_t)UW * p.S * CHUNK;
     float4* xmeta = reinterpret_cast<float4*>(xq + (size_t)p.G * XG);
-    __half* ssm = reinterpret_cast<__half*>(xmeta + (size_t)p.G * 4);
+    __half* ssm = reinterpret_cast<__half*>(xmeta + (size_t)p.G * 4 * NT);
     unsigned char* zsm = reinterpret_cast<unsigned char*>(ssm + (size_t)p.rows_cap * p.G);
     float* part = reinterpret_cast<float*>(zsm + (((size_t)p.rows_cap * p.ZS + 15) & ~(size_t)15));
     int4* utab = reinterpret_cast<int4*>(part + (size_t)p.units_cap * 16 * MM);
@@ -596,7 +600,7 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
     // ---- x -> block fixed point, four signed byte planes in B-fragment order -----------------
     for (int c = tid; c < npieces; c += UW * 32) {
         const uint4 s4 = __ldg(reinterpret_cast<const uint4*>(p.x) + c);
-        const int m = (MM == 2 && c >= p.G * 16) ? 1 : 0, cg16 = c - m * p.G * 16;
+        const int m = MM == 1 ? 0 : c / (p.G * 16), cg16 = c - m * p.G * 16;
         const int grp = cg16 >> 4, l16 = cg16 & 15;
         float v[8];
         {
@@ -664,7 +668,7 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
 #pragma unroll
         for (int pl = 0; pl < 4; pl++) {
             if (pl == 3 && p.planes == 3) break;             // the fourth digit of a 23-bit number is 0
-            unsigned char* dst = xq + (size_t)grp * XG + (pl * MM + m) * 128 + tq * 32;
+            unsigned char* dst = xq + (size_t)grp * XG + (m / MMT) * XT + (pl * MMT + (m % MMT)) * 128 + tq * 32;
             *reinterpret_cast<uint32_t*>(dst + ((0 * 2 + jp) * 2 + bb) * 4) = pw[pl][0];
             *reinterpret_cast<uint32_t*>(dst + ((1 * 2 + jp) * 2 + bb) * 4) = pw[pl][1];
         }
@@ -686,14 +690,14 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
             // Lane t of a consumer reads one float4 = {coef, digit sum} of its columns 2t and 2t+1.
             // Every float of the group's four entries is written here exactly once; columns
             // without a plane behind them get coefficient 0 (their accumulators hold garbage).
-            float4* xm = xmeta + grp * 4;
+            float4* xm = xmeta + (grp * NT + m / MMT) * 4;
             if (MM == 1) {
                 xm[0] = make_float4(down, (float)s0, down * 256.0f, (float)s1);
                 xm[1] = make_float4(down * 65536.0f, (float)s2, p.planes == 4 ? down * 16777216.0f : 0.f, (float)s3);
                 xm[2] = make_float4(0.f, 0.f, 0.f, 0.f);
                 xm[3] = make_float4(0.f, 0.f, 0.f, 0.f);
             } else {
-                float2* x2 = reinterpret_cast<float2*>(xm) + m;          // .xy for m = 0, .zw for m = 1
+                float2* x2 = reinterpret_cast<float2*>(xm) + (m % MMT);  // .xy for the tile's first row, .zw for its second
                 x2[0] = make_float2(down, (float)s0);
                 x2[2] = make_float2(down * 256.0f, (float)s1);
                 x2[4] = make_float2(down * 65536.0f, (float)s2);
@@ -709,11 +713,12 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
     __syncthreads();
 
     // lanes of column g >= 4*MM multiply garbage that nobody reads: point them at a valid column
-    const int col = min(g, p.planes * MM - 1);
+    const int col = min(g, p.planes * MMT - 1);
     const int xcol_off = col * 128 + t * 32;
     const int rg = rho(g);                               // tile row behind fragment row g
-    float res[2][2];                                     // [row half][column 2t / 2t+1 of the lane]
-    res[0][0] = res[0][1] = res[1][0] = res[1][1] = 0.0f;
+    float res[NT][2][2];                                 // [column tile][row half][column 2t / 2t+1 of the lane]
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) res[nt][0][0] = res[nt][0][1] = res[nt][1][0] = res[nt][1][1] = 0.0f;
     constexpr int MAGIC = 0x4B400000;                    // float 1.5 * 2^23: MAGIC + i reads as 12582912 + i
 
     int slot = 0;
@@ -768,59 +773,69 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
 #pragma unroll
         for (int u = 0; u < CG; u++) {
             const uint4 qa = wq[2 * u], qb = wq[2 * u + 1];
-            const unsigned char* xg = xq + (size_t)(gi0 + u) * XG + xcol_off;
-            const uint4 xlo = *reinterpret_cast<const uint4*>(xg);          // even k: word pairs 0, 1
-            const uint4 xhi = *reinterpret_cast<const uint4*>(xg + 16);     // odd k
-            // the accumulator starts at MAGIC, so that it can be read as a float afterwards
-            int acc[4] = {MAGIC, MAGIC, MAGIC, MAGIC};
             constexpr uint32_t MH = 0xf0f0f0f0u;
-            mma16832_u8s8(acc, qa.x, qb.x, qa.y, qb.y, xlo.x, xlo.y);                          // R  x Xe
-            mma16832_u8s8(acc, qa.x & MH, qb.x & MH, qa.y & MH, qb.y & MH, xhi.x, xhi.y);      // H  x (Zo - Xe)
-            mma16832_u8s8(acc, qa.z, qb.z, qa.w, qb.w, xlo.z, xlo.w);
-            mma16832_u8s8(acc, qa.z & MH, qb.z & MH, qa.w & MH, qb.w & MH, xhi.z, xhi.w);
-            // columns 2t, 2t+1 of this lane: coefficient 2^(E-22) 256^plane and digit sum
-            const float4 xm = xmeta[(gi0 + u) * 4 + t];
+            const uint32_t ha0 = qa.x & MH, hb0 = qb.x & MH, ha1 = qa.y & MH, hb1 = qb.y & MH;
+            const uint32_t ha2 = qa.z & MH, hb2 = qb.z & MH, ha3 = qa.w & MH, hb3 = qb.w & MH;
             // -zp as a float: 12582912 - (12582912 + zp)
             const float nza = 12582912.0f - __uint_as_float(0x4B400000u | ((za >> (4 * u)) & 0xFu));
             const float nzb = 12582912.0f - __uint_as_float(0x4B400000u | ((zb >> (4 * u)) & 0xFu));
-            // integer sum (n - zp) X of the column = acc - zp * digit-sum, all exact in f32:
-            // |acc| < 2^22 (64 bytes x 255 x 128 + 64 x 240 x 128), |zp * sum| < 2^18
-            float v[2][2];                               // [row half][column]
 #pragma unroll
-            for (int j = 0; j < 2; j++) {
-                const float ds = j ? xm.w : xm.y;
-                v[0][j] = fmaf(nza, ds, __int_as_float(acc[j]) - 12582912.0f);
-                v[1][j] = fmaf(nzb, ds, __int_as_float(acc[2 + j]) - 12582912.0f);
-            }
-            if (MM == 1) {
-                // both columns are planes of batch row 0: combine them before the scale
-                res[0][0] = fmaf(fsa[u], fmaf(xm.z, v[0][1], xm.x * v[0][0]), res[0][0]);
-                res[1][0] = fmaf(fsb[u], fmaf(xm.z, v[1][1], xm.x * v[1][0]), res[1][0]);
-            } else {
-                res[0][0] = fmaf(fsa[u] * xm.x, v[0][0], res[0][0]);
-                res[0][1] = fmaf(fsa[u] * xm.z, v[0][1], res[0][1]);
-                res[1][0] = fmaf(fsb[u] * xm.x, v[1][0], res[1][0]);
-                res[1][1] = fmaf(fsb[u] * xm.z, v[1][1], res[1][1]);
+            for (int nt = 0; nt < NT; nt++) {
+                const unsigned char* xg = xq + (size_t)(gi0 + u) * XG + nt * XT + xcol_off;
+                const uint4 xlo = *reinterpret_cast<const uint4*>(xg);          // even k: word pairs 0, 1
+                const uint4 xhi = *reinterpret_cast<const uint4*>(xg + 16);     // odd k
+                // the accumulator starts at MAGIC, so that it can be read as a float afterwards
+                int acc[4] = {MAGIC, MAGIC, MAGIC, MAGIC};
+                mma16832_u8s8(acc, qa.x, qb.x, qa.y, qb.y, xlo.x, xlo.y);      // R  x Xe
+                mma16832_u8s8(acc, ha0, hb0, ha1, hb1, xhi.x, xhi.y);          // H  x (Zo - Xe)
+                mma16832_u8s8(acc, qa.z, qb.z, qa.w, qb.w, xlo.z, xlo.w);
+                mma16832_u8s8(acc, ha2, hb2, ha3, hb3, xhi.z, xhi.w);
+                // columns 2t, 2t+1 of this lane: coefficient 2^(E-22) 256^plane and digit sum
+                const float4 xm = xmeta[((gi0 + u) * NT + nt) * 4 + t];
+                // integer sum (n - zp) X of the column = acc - zp * digit-sum, all exact in f32:
+                // |acc| < 2^22 (64 bytes x 255 x 128 + 64 x 240 x 128), |zp * sum| < 2^18
+                float v[2][2];                               // [row half][column]
+#pragma unroll
+                for (int j = 0; j < 2; j++) {
+                    const float ds = j ? xm.w : xm.y;
+                    v[0][j] = fmaf(nza, ds, __int_as_float(acc[j]) - 12582912.0f);
+                    v[1][j] = fmaf(nzb, ds, __int_as_float(acc[2 + j]) - 12582912.0f);
+                }
+                if (MM == 1) {
+                    // both columns are planes of batch row 0: combine them before the scale
+                    res[nt][0][0] = fmaf(fsa[u], fmaf(xm.z, v[0][1], xm.x * v[0][0]), res[nt][0][0]);
+                    res[nt][1][0] = fmaf(fsb[u], fmaf(xm.z, v[1][1], xm.x * v[1][0]), res[nt][1][0]);
+                } else {
+                    res[nt][0][0] = fmaf(fsa[u] * xm.x, v[0][0], res[nt][0][0]);
+                    res[nt][0][1] = fmaf(fsa[u] * xm.z, v[0][1], res[nt][0][1]);
+                    res[nt][1][0] = fmaf(fsb[u] * xm.x, v[1][0], res[nt][1][0]);
+                    res[nt][1][1] = fmaf(fsb[u] * xm.z, v[1][1], res[nt][1][1]);
+                }
             }
         }
         // end of a unit: add the planes (lanes t) and drop the partial sums into the unit's slot
         if (ccur.ci == NC - 1) {
             const int ul = warp + ccur.ui * UW;
 #pragma unroll
-            for (int h = 0; h < 2; h++)
+            for (int nt = 0; nt < NT; nt++)
 #pragma unroll
-                for (int m = 0; m < MM; m++) {
-                    res[h][m] += __shfl_xor_sync(0xffffffffu, res[h][m], 1);
-                    res[h][m] += __shfl_xor_sync(0xffffffffu, res[h][m], 2);
-                }
+                for (int h = 0; h < 2; h++)
+#pragma unroll
+                    for (int m = 0; m < MMT; m++) {
+                        res[nt][h][m] += __shfl_xor_sync(0xffffffffu, res[nt][h][m], 1);
+                        res[nt][h][m] += __shfl_xor_sync(0xffffffffu, res[nt][h][m], 2);
+                    }
             if (t == 0) {
 #pragma unroll
-                for (int m = 0; m < MM; m++) {
-                    part[((size_t)ul * 16 + rg) * MM + m] = res[0][m];
-                    part[((size_t)ul * 16 + rg + 8) * MM + m] = res[1][m];
-                }
+                for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                    for (int m = 0; m < MMT; m++) {
+                        part[((size_t)ul * 16 + rg) * MM + nt * MMT + m] = res[nt][0][m];
+                        part[((size_t)ul * 16 + rg + 8) * MM + nt * MMT + m] = res[nt][1][m];
+                    }
             }
-            res[0][0] = res[0][1] = res[1][0] = res[1][1] = 0.0f;
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) res[nt][0][0] = res[nt][0][1] = res[nt][1][0] = res[nt][1][1] = 0.0f;
         }
         advance(ccur);
     }
@@ -855,6 +870,7 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
         const unsigned long long t0 = peer_timer_ns();
         for (int o = tid; o < npairs && !failed; o += UW * 32) {
             const int m = o % MM, r2 = (o / MM) & 7, tl = o / (8 * MM);
+            if (m >= p.M) continue;                               // the padding row of a three-row batch
             const float* v0 = part + ((size_t)(tl * p.U) * 16 + 2 * r2) * MM + m;
             float s0 = 0.0f, s1 = 0.0f;
             for (int k = 0; k < p.U; k++) {                       // fixed order: deterministic
@@ -907,6 +923,7 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
     const int nout = ntiles * 16 * MM;
     for (int o = tid; o < nout; o += UW * 32) {
         const int m = o % MM, r = (o / MM) & 15, tl = o / (16 * MM);
+        if (m >= p.M) continue;                                   // the padding row of a three-row batch
         float sum[NACC];
 #pragma unroll
         for (int a = 0; a < NACC; a++) {
@@ -985,8 +1002,10 @@ LuxBackendError launch_qgemv_i4_units(Context* ctx, const QArgs& a) {
         (reinterpret_cast<uintptr_t>(a.w) & 15) || (reinterpret_cast<uintptr_t>(a.x) & 15))
         return LUX_BACKEND_ERROR_NOT_SUPPORTED;
     if (a.swiglu && (((size_t)nout * a.G * 2) & 15)) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
-    // batch 1 and 2 use the block-fixed-point variant unless the tunable says otherwise
-    const bool fx = a.M <= 2 && g_tune.gemv_units_fx != 2;
+    // batch 1..4 use the block-fixed-point variant (three rows run as four) unless the tunable says
+    // otherwise; a batch of 3 or 4 whose activations do not fit beside the FIFOs falls back to the f16 form
+    bool fx = a.M <= 4 && g_tune.gemv_units_fx != 2;
+    const int mm = a.M == 3 ? 4 : a.M;                    // batch rows the fixed-point kernel is instantiated for
 
     // Chunk size: 4 groups when the group count allows, else 2.
     int cg = g_tune.gemv_units_cg == 2 || g_tune.gemv_units_cg == 4 ? g_tune.gemv_units_cg : ((a.G & 3) ? 2 : 4);
@@ -1043,10 +1062,10 @@ LuxBackendError launch_qgemv_i4_units(Context* ctx, const QArgs& a) {
         p.units_cap = pl.tiles_per_cta * nacc * pl.U;
         p.rows_cap = pl.tiles_per_cta * 16 * nacc;
         p.planes = planes;
-        const size_t x_bytes = fx ? (size_t)a.G * planes * a.M * 128 + (size_t)a.G * 4 * sizeof(float4)
+        const size_t x_bytes = fx ? (size_t)a.G * planes * mm * 128 + (size_t)a.G * 4 * ((mm + 1) / 2) * sizeof(float4)
                                   : (size_t)a.M * p.xstride + (size_t)a.G * 8 * MT * sizeof(float2);
         const size_t meta_bytes = (size_t)p.rows_cap * a.G * 2 + (((size_t)p.rows_cap * p.ZS + 15) & ~(size_t)15);
-        const size_t part_bytes = fx ? (size_t)p.units_cap * 16 * a.M * sizeof(float)
+        const size_t part_bytes = fx ? (size_t)p.units_cap * 16 * mm * sizeof(float)
                                      : (size_t)p.units_cap * MT * 8 * p.tmax * sizeof(float4);
         // the fixed-point variant also holds its barriers and flag, and 1024 bytes of alignment slack
         pl.fixed = x_bytes + meta_bytes + part_bytes + (size_t)p.units_cap * sizeof(int4) +
@@ -1080,7 +1099,12 @@ LuxBackendError launch_qgemv_i4_units(Context* ctx, const QArgs& a) {
         return false;
     };
     if (fx && g_tune.gemv_units_warps == 8) planned = plan_planes(8, (size_t)113 * 1024, 2);
-    if (!planned && (!fx || g_tune.gemv_units_warps != 8)) planned = plan_planes(UW, (size_t)227 * 1024, fx ? 1 : 2);
+    if (!planned && (!fx || g_tune.gemv_units_warps != 8)) planned = plan_planes(UW, (size_t)227 * 1024, fx ? (mm == 4 ? 2 : 1) : 2);
+    if (!planned && fx && a.M > 2) {
+        if (g_tune.gemv_i4_kernel != 3) return LUX_BACKEND_ERROR_NOT_SUPPORTED;     // the caller has faster kernels for this shape
+        fx = false;
+        planned = plan_planes(UW, (size_t)227 * 1024, 2);
+    }
     if (!planned) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
     UnitsParams& p = pl.p;
     const int grid = pl.grid;
@@ -1111,9 +1135,12 @@ LuxBackendError launch_qgemv_i4_units(Context* ctx, const QArgs& a) {
         if (a.M == 1)
             e = a.swiglu ? launch_units_fx_cg<1, true>(pdl, cg, pl.uw, map, p, grid, smem, ctx->stream)
                          : launch_units_fx_cg<1, false>(pdl, cg, pl.uw, map, p, grid, smem, ctx->stream);
-        else
+        else if (a.M == 2)
             e = a.swiglu ? launch_units_fx_cg<2, true>(pdl, cg, pl.uw, map, p, grid, smem, ctx->stream)
                          : launch_units_fx_cg<2, false>(pdl, cg, pl.uw, map, p, grid, smem, ctx->stream);
+        else
+            e = a.swiglu ? launch_units_fx_cg<4, true>(pdl, cg, pl.uw, map, p, grid, smem, ctx->stream)
+                         : launch_units_fx_cg<4, false>(pdl, cg, pl.uw, map, p, grid, smem, ctx->stream);
     } else if (a.M == 1) {
         e = a.swiglu ? launch_units_cg<1, true, true>(cg, p, grid, smem, ctx->stream)
                      : launch_units_cg<1, false, true>(cg, p, grid, smem, ctx->stream);

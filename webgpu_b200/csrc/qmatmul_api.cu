@@ -94,7 +94,7 @@ LuxBackendError dispatch(Context* ctx, const Checked& c) {
             const QArgs& a = c.a;
             // Batch 1 and 2: the warp-autonomous kernel in its fixed-point variant is the fastest
             // wherever its shared-memory plan fits.
-            if (g_tune.gemv_i4_kernel == 3 || (g_tune.gemv_i4_kernel == 0 && a.M <= 2)) {
+            if (g_tune.gemv_i4_kernel == 3 || (g_tune.gemv_i4_kernel == 0 && a.M <= 4)) {
                 LuxBackendError e = launch_qgemv_i4_units(ctx, a);
                 if (e != LUX_BACKEND_ERROR_NOT_SUPPORTED || g_tune.gemv_i4_kernel == 3) return e;
             }
