@@ -293,11 +293,15 @@ LUX_GPU_PLUGIN_EXPORT const char* lux_cuda_last_kernel_name(void);
  * (1 register-staged, 2 bulk-copy ring, 3 warp-autonomous units), gemv_i4_warps, gemv_i4_row_tiles, gemv_stream_warps, gemv_stream_cg, gemv_stream_stages,
  * gemv_units_ks, gemv_units_stages, gemv_units_cg, gemv_units_pre, gemv_units_fx, gemv_i8_warps, gemm_tc_bn,
  * gemm_tc_stages, gemm_tc_ma, gemm_tc_kernel (1 lux_qgemm_i4_tc, 2 lux_qgemm_i4_tc_wa wherever it applies), gemm_tc_splitk (1, 2, 4),
- * gemm_tc_groups, gemm_min_m (smallest batch handed to lux_qgemm_i4_tc_wa, default 12), pdl (2: no programmatic dependent launch), peer_wait_limit, tp_fused_push.  Unknown keys return INVALID_ARGUMENT.  Process-wide;
+ * gemm_tc_groups, gemm_min_m (smallest batch handed to lux_qgemm_i4_tc_wa, default 12), pdl (2: no programmatic dependent launch), peer_wait_limit, tp_fused_push,
+ * gemv_units_warps, gemv_units_planes, gemm_wa_narrow, host_pageable, attn_splits.  Unknown keys return INVALID_ARGUMENT.  Process-wide;
  * not part of the drop-in surface. */
 LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_tune_set(const char* key, int value);
 
-/* Status word of the last device-side bounded wait that gave up (0 = none). */
+/* What the context's most recent synchronising call found in the device status word: 0 if every
+ * device-side check since the synchronising call before it passed, else the code of the check that
+ * failed (a bounded wait that gave up, a block-table entry or rope position out of range); the call
+ * itself returned LUX_BACKEND_ERROR_DEVICE_LOST. */
 LUX_GPU_PLUGIN_EXPORT uint32_t lux_cuda_last_device_status(LuxBackendContext* ctx);
 
 #ifdef __cplusplus

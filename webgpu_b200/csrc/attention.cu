@@ -753,6 +753,13 @@ size_t mul(std::initializer_list<uint64_t> v) {
 
 }  // namespace
 
+// entries of the kernel table (kernel_table.cu): the Llama-shaped instance of the streaming kernel
+const void* kernel_addr_attn_stream_f32() { return (const void*)lux_attn_stream_f32<4, 2, true>; }
+const void* kernel_addr_attn_merge_f32() { return (const void*)lux_attn_merge_f32; }
+const void* kernel_addr_attn_plain_f32() { return (const void*)lux_attn_plain_f32; }
+const void* kernel_addr_rope_f32() { return (const void*)lux_rope_f32; }
+const void* kernel_addr_kv_append_f32() { return (const void*)lux_kv_append_f32; }
+
 }  // namespace luxcuda
 
 using namespace luxcuda;

@@ -34,6 +34,7 @@ LuxBackendError finish_op(Context* ctx, bool no_sync, const char* what) {
         *(volatile uint32_t*)ctx->h_status = 0;
         return LUX_BACKEND_ERROR_DEVICE_LOST;
     }
+    ctx->last_status = 0;                    // what lux_cuda_last_device_status reports belongs to the latest wait
     return LUX_BACKEND_OK;
 }
 

@@ -487,6 +487,12 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
 }
 __device__ __forceinline__ int rho(int g) { return (g >> 1) | ((g & 1) << 2); }
 
+// Accumulator chains per group of four MMAs (1, 2 or 4).  One chain of four dependent mma.sync is the
+// fastest: with four independent accumulators (added as floats afterwards) config 2 went from 7.45 to
+// 8.3 us and a batch of four on config 4's gate_up from 19.1 to 19.9 us, so the chain's latency is not
+// what the loop waits for; its time follows the NUMBER of mma.sync and of the operations around them.
+constexpr int FXCH = 1;
+
 template <int MM, bool SWIGLU, int CG, int UWT>
 __global__ void __launch_bounds__(UWT * 32, UWT == 8 ? 2 : 1)
 lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const UnitsParams p) {
@@ -598,8 +604,8 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
     pdl_wait();
 
     // ---- x -> block fixed point, four signed byte planes in B-fragment order -----------------
-    for (int c = tid; c < npieces; c += UW * 32) {
-        const uint4 s4 = __ldg(reinterpret_cast<const uint4*>(p.x) + c);
+    // a thread's pieces are requested together (one round trip to L2 per MM pieces, not one each)
+    auto convert = [&](int c, const uint4 s4) {
         const int m = MM == 1 ? 0 : c / (p.G * 16), cg16 = c - m * p.G * 16;
         const int grp = cg16 >> 4, l16 = cg16 & 15;
         float v[8];
@@ -704,6 +710,19 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
                 x2[6] = make_float2(p.planes == 4 ? down * 16777216.0f : 0.f, (float)s3);
             }
         }
+    };
+    for (int c0 = tid; c0 < npieces; c0 += UW * 32 * MM) {
+        uint4 s4v[MM];
+#pragma unroll
+        for (int i = 0; i < MM; i++) {
+            const int c = c0 + i * UW * 32;
+            if (c < npieces) s4v[i] = __ldg(reinterpret_cast<const uint4*>(p.x) + c);
+        }
+#pragma unroll
+        for (int i = 0; i < MM; i++) {
+            const int c = c0 + i * UW * 32;
+            if (c < npieces) convert(c, s4v[i]);          // warp-uniform: npieces is a multiple of 32
+        }
     }
     // fill the rest of the FIFO (the async engine queues the requests: nothing stalls here; asked
     // for before the conversion they only delay the first chunk and the tables: measured slower)
@@ -784,22 +803,31 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
                 const unsigned char* xg = xq + (size_t)(gi0 + u) * XG + nt * XT + xcol_off;
                 const uint4 xlo = *reinterpret_cast<const uint4*>(xg);          // even k: word pairs 0, 1
                 const uint4 xhi = *reinterpret_cast<const uint4*>(xg + 16);     // odd k
-                // the accumulator starts at MAGIC, so that it can be read as a float afterwards
-                int acc[4] = {MAGIC, MAGIC, MAGIC, MAGIC};
-                mma16832_u8s8(acc, qa.x, qb.x, qa.y, qb.y, xlo.x, xlo.y);      // R  x Xe
-                mma16832_u8s8(acc, ha0, hb0, ha1, hb1, xhi.x, xhi.y);          // H  x (Zo - Xe)
-                mma16832_u8s8(acc, qa.z, qb.z, qa.w, qb.w, xlo.z, xlo.w);
-                mma16832_u8s8(acc, ha2, hb2, ha3, hb3, xhi.z, xhi.w);
+                // every accumulator starts at MAGIC, so that it reads as a float without a conversion
+                int acc[FXCH][4];
+#pragma unroll
+                for (int ch = 0; ch < FXCH; ch++) acc[ch][0] = acc[ch][1] = acc[ch][2] = acc[ch][3] = MAGIC;
+                mma16832_u8s8(acc[0], qa.x, qb.x, qa.y, qb.y, xlo.x, xlo.y);               // R  x Xe
+                mma16832_u8s8(acc[1 % FXCH], ha0, hb0, ha1, hb1, xhi.x, xhi.y);           // H  x (Zo - Xe)
+                mma16832_u8s8(acc[2 % FXCH], qa.z, qb.z, qa.w, qb.w, xlo.z, xlo.w);
+                mma16832_u8s8(acc[3 % FXCH], ha2, hb2, ha3, hb3, xhi.z, xhi.w);
                 // columns 2t, 2t+1 of this lane: coefficient 2^(E-22) 256^plane and digit sum
                 const float4 xm = xmeta[((gi0 + u) * NT + nt) * 4 + t];
                 // integer sum (n - zp) X of the column = acc - zp * digit-sum, all exact in f32:
                 // |acc| < 2^22 (64 bytes x 255 x 128 + 64 x 240 x 128), |zp * sum| < 2^18
+                float fa[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    fa[e] = __int_as_float(acc[0][e]) - 12582912.0f;
+#pragma unroll
+                    for (int ch = 1; ch < FXCH; ch++) fa[e] += __int_as_float(acc[ch][e]) - 12582912.0f;
+                }
                 float v[2][2];                               // [row half][column]
 #pragma unroll
                 for (int j = 0; j < 2; j++) {
                     const float ds = j ? xm.w : xm.y;
-                    v[0][j] = fmaf(nza, ds, __int_as_float(acc[j]) - 12582912.0f);
-                    v[1][j] = fmaf(nzb, ds, __int_as_float(acc[2 + j]) - 12582912.0f);
+                    v[0][j] = fmaf(nza, ds, fa[j]);
+                    v[1][j] = fmaf(nzb, ds, fa[2 + j]);
                 }
                 if (MM == 1) {
                     // both columns are planes of batch row 0: combine them before the scale
@@ -1159,5 +1187,6 @@ const void* kernel_addr_qgemv_i4_units() { return (const void*)lux_qgemv_i4_g128
 const void* kernel_addr_qgemv_i4_units_fx() { return (const void*)lux_qgemv_i4_g128_units_fx<1, false, 4, 16>; }
 const void* kernel_addr_qgemv_i4_units_fx_swiglu() { return (const void*)lux_qgemv_i4_g128_units_fx<1, true, 4, 16>; }
 const void* kernel_addr_qgemv_i4_units_fx_batch2() { return (const void*)lux_qgemv_i4_g128_units_fx<2, false, 4, 16>; }
+const void* kernel_addr_qgemv_i4_units_fx_batch4() { return (const void*)lux_qgemv_i4_g128_units_fx<4, false, 4, 16>; }
 
 }  // namespace luxcuda
