@@ -91,14 +91,8 @@ __device__ __forceinline__ float ex2(float x) {
 // Named barriers: a warp that waits on one is parked by the hardware and issues nothing, unlike a
 // warp polling an mbarrier, whose polls share the queue that shared-memory loads and shuffles go
 // through.  With eight warps polling for every chunk the warps that had work ran 2-3 times slower.
-__device__ __forceinline__ void named_sync(uint32_t id, uint32_t threads) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
-__device__ __forceinline__ void named_arrive(uint32_t id, uint32_t threads) {
-    asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
-constexpr uint32_t ATT_BAR_READY = 1;           // consumer warps: the chunk has landed (warp 0 polled for it)
-constexpr uint32_t ATT_BAR_FREE0 = 2;           // + stage: every consumer warp is done with the stage (producer waits)
+constexpr int ATT_BAR_READY = 1;           // consumer warps: the chunk has landed (warp 0 polled for it)
+constexpr int ATT_BAR_FREE0 = 2;           // + stage: every consumer warp is done with the stage (producer waits)
 
 __device__ __forceinline__ uint32_t row_len(const AttnParams& p, uint32_t qi, uint32_t kv_len) {
     return p.causal ? min(p.causal_base + qi + 1u, kv_len) : kv_len;
@@ -178,7 +172,7 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) lux_attn_stream_
         for (uint32_t c = 0; c < nchunks; c++) {
             const uint32_t s = c % NS;
             if (c >= NS) {
-                named_sync(ATT_BAR_FREE0 + s, ATT_THREADS);          // all consumer warps have left the stage
+                named_bar_sync<ATT_BAR_FREE0>(s, ATT_THREADS);          // all consumer warps have left the stage
                 if (*abort_flag) break;
             }
             const uint32_t t0 = k_begin + chunk_at(c) * ATT_CK, nk = min((uint32_t)ATT_CK, k_end - t0);
@@ -304,10 +298,10 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) lux_attn_stream_
             const uint32_t s = c % NS;
             // one poller per CTA: warp 0 waits for the copies, the named barrier releases the other seven
             if (warp == 0) warp_wait(bar_full + 8u * s, (c / NS) & 1u, abort_flag, lane);
-            named_sync(ATT_BAR_READY, ATT_CW * 32);
+            named_bar_sync_c<ATT_BAR_READY>(ATT_CW * 32);
             if (*abort_flag) {
                 // the producer may be parked on the stages this warp would still have released
-                for (uint32_t cc = c; cc < c + NS && cc + NS < nchunks; cc++) named_arrive(ATT_BAR_FREE0 + cc % NS, ATT_THREADS);
+                for (uint32_t cc = c; cc < c + NS && cc + NS < nchunks; cc++) named_bar_arrive<ATT_BAR_FREE0>(cc % NS, ATT_THREADS);
                 break;
             }
             const uint32_t t0 = k_begin + chunk_at(c) * ATT_CK, nk = min((uint32_t)ATT_CK, k_end - t0);
@@ -324,7 +318,7 @@ __global__ void __launch_bounds__(ATT_THREADS, ATT_CTAS_PER_SM) lux_attn_stream_
                 }
             }
             // done with the stage (not needed for the last NS chunks: nobody refills them)
-            if (c + NS < nchunks) named_arrive(ATT_BAR_FREE0 + s, ATT_THREADS);
+            if (c + NS < nchunks) named_bar_arrive<ATT_BAR_FREE0>(s, ATT_THREADS);
         }
         // the four key slots of the warp, merged by the running-maximum rule
 #pragma unroll

@@ -136,6 +136,38 @@ extern Tunables g_tune;
 //     activations are read, and anything is written, only after it.
 // In a kernel launched without the attribute both calls do nothing.
 #ifdef __CUDACC__
+
+// Named barriers with the barrier number as an immediate (a number held in a register makes the
+// compiler reserve all sixteen of the CTA's barriers).  `base` + `i`, i in 0..7.
+#ifdef __CUDACC__
+template <int ID> __device__ __forceinline__ void named_bar_sync_c(uint32_t threads) {
+    asm volatile("bar.sync %0, %1;" ::"n"(ID), "r"(threads) : "memory");
+}
+template <int ID> __device__ __forceinline__ void named_bar_arrive_c(uint32_t threads) {
+    asm volatile("bar.arrive %0, %1;" ::"n"(ID), "r"(threads) : "memory");
+}
+template <int BASE> __device__ __forceinline__ void named_bar_sync(uint32_t i, uint32_t threads) {
+    switch (i) {
+        case 0: named_bar_sync_c<BASE + 0>(threads); break;
+        case 1: named_bar_sync_c<BASE + 1>(threads); break;
+        case 2: named_bar_sync_c<BASE + 2>(threads); break;
+        case 3: named_bar_sync_c<BASE + 3>(threads); break;
+        case 4: named_bar_sync_c<BASE + 4>(threads); break;
+        default: named_bar_sync_c<BASE + 5>(threads); break;
+    }
+}
+template <int BASE> __device__ __forceinline__ void named_bar_arrive(uint32_t i, uint32_t threads) {
+    switch (i) {
+        case 0: named_bar_arrive_c<BASE + 0>(threads); break;
+        case 1: named_bar_arrive_c<BASE + 1>(threads); break;
+        case 2: named_bar_arrive_c<BASE + 2>(threads); break;
+        case 3: named_bar_arrive_c<BASE + 3>(threads); break;
+        case 4: named_bar_arrive_c<BASE + 4>(threads); break;
+        default: named_bar_arrive_c<BASE + 5>(threads); break;
+    }
+}
+#endif
+
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
