@@ -132,6 +132,8 @@ def dist_env():
 class Rig:
     """Plugin context bound to a torch stream, so CUDA events see the kernels."""
 
+    eager = False       # time_graph: enqueue the timed launches one by one instead of replaying a graph
+
     def __init__(self, local_rank: int, tunes=()):
         import torch
         from webgpu_b200 import backend as B
@@ -191,10 +193,14 @@ class Rig:
             if align is not None:
                 align()
             e0.record(self.stream)
-            for _ in range(steps // glen):
-                g.replay()
-            if g2 is not None:
-                g2.replay()
+            if self.eager:
+                for i in range(steps):
+                    launch(i)
+            else:
+                for _ in range(steps // glen):
+                    g.replay()
+                if g2 is not None:
+                    g2.replay()
             e1.record(self.stream)
             torch.cuda.synchronize()
             return e0.elapsed_time(e1) * 1e-3 / steps, g
@@ -840,9 +846,11 @@ def main():
                          "(falls back to NCCL if the peer mapping is refused) or NCCL")
     ap.add_argument("--skip-tp1", action="store_true", help="N > 1: leave out the one-GPU anchor run on rank 0")
     ap.add_argument("--skip-ffn", action="store_true", help="N = 1: leave out the configuration-5 one-GPU block")
+    ap.add_argument("--eager", action="store_true", help="time plain launches queued behind the spin kernel instead of CUDA-graph replays")
     ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE",
                     help="override a launch heuristic (lux_cuda_tune_set), e.g. gemv_i4_kernel=2")
     args = ap.parse_args()
+    Rig.eager = args.eager
     peaks = measured_peaks()
     if args.impl == "reference":
         line = bench_reference(args)
