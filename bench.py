@@ -424,6 +424,57 @@ def bench_sweep(args, peaks):
         out["quantize_int4_14336x4096"] = {"us": sec * 1e6, "gbs": qbytes / sec / 1e9, "frac_of_measured_hbm": qbytes / sec / 1e9 / peaks["hbm"],
                                            "note": "235 MB read + 31 MB written per launch: larger than L2"}
         del wf
+    if not attention_only:
+        # the f32 slots either side of a linear layer and the integer path: blocking calls (the vtable's
+        # convention), timed with events around each call on 268 MB tensors (larger than L2)
+        def timed(call, reps=5):
+            for _ in range(2):
+                call()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            total = 0.0
+            for _ in range(reps):
+                e0.record(rig.stream)
+                call()
+                e1.record(rig.stream)
+                torch.cuda.synchronize()
+                total += e0.elapsed_time(e1) * 1e-3
+            return total / reps
+        rows, dim = 8192, 8192
+        xt = torch.randn(rows, dim, device="cuda")
+        ot = torch.empty_like(xt)
+        gt = torch.randn(dim, device="cuda")
+        xb_, ob_, gb_ = (ctx.wrap(t.data_ptr(), t.numel() * 4) for t in (xt, ot, gt))
+        nbytes = 2 * rows * dim * 4
+        ops = {"rms_norm": lambda: ctx.rms_norm_f32(xb_, gb_, ob_, rows, dim, 1e-5),
+               "layer_norm": lambda: ctx.layer_norm_f32(xb_, gb_, gb_, ob_, rows, dim, 1e-5),
+               "softmax": lambda: ctx.softmax_f32(xb_, ob_, rows, dim),
+               "silu": lambda: ctx.unary_f32("silu", xb_, ob_, rows * dim),
+               "gelu": lambda: ctx.unary_f32("gelu", xb_, ob_, rows * dim),
+               "transpose": lambda: ctx.transpose_f32(xb_, ob_, rows, dim)}
+        out["tensor_slots_8192x8192_f32"] = {}
+        with torch.cuda.stream(rig.stream):
+            for name, call in ops.items():
+                sec = timed(call)
+                out["tensor_slots_8192x8192_f32"][name] = {"us": sec * 1e6, "gbs": nbytes / sec / 1e9,
+                                                           "frac_of_measured_hbm": nbytes / sec / 1e9 / peaks["hbm"]}
+            del xt, ot
+            # W8A8: C[M, N] (i32) = A[M, K] (i8) . B[K, N] (i8) on mma.sync.m16n8k32.s8; and the quantize step before it
+            Mi = Ni = Ki = 4096
+            at = torch.randint(-127, 128, (Mi, Ki), device="cuda", dtype=torch.int8)
+            bt = torch.randint(-127, 128, (Ki, Ni), device="cuda", dtype=torch.int8)
+            ct = torch.empty(Mi, Ni, device="cuda", dtype=torch.int32)
+            ab_, bb_, cb_ = ctx.wrap(at.data_ptr(), at.numel()), ctx.wrap(bt.data_ptr(), bt.numel()), ctx.wrap(ct.data_ptr(), ct.numel() * 4)
+            sec = timed(lambda: ctx.matmul_int8(ab_, bb_, cb_, Mi, Ni, Ki))
+            out["matmul_int8_4096"] = {"us": sec * 1e6, "tops": 2.0 * Mi * Ni * Ki / sec / 1e12, "kernel": rig.backend.last_kernel_name()}
+            ft = torch.randn(64 << 20, device="cuda")
+            qt = torch.empty(64 << 20, device="cuda", dtype=torch.int8)
+            st = torch.empty(4, device="cuda")
+            fb_, qb_, sb_ = ctx.wrap(ft.data_ptr(), ft.numel() * 4), ctx.wrap(qt.data_ptr(), qt.numel()), ctx.wrap(st.data_ptr(), 16)
+            sec = timed(lambda: ctx.dynamic_quantize(fb_, qb_, sb_, ft.numel()))
+            dq_bytes = ft.numel() * (4 + 4 + 1)            # read for the maximum, read again, write int8
+            out["dynamic_quantize_64m"] = {"us": sec * 1e6, "gbs": dq_bytes / sec / 1e9, "frac_of_measured_hbm": dq_bytes / sec / 1e9 / peaks["hbm"],
+                                           "note": "two passes over 268 MB (tensor-wide maximum, then quantize) + 67 MB written"}
+            del at, bt, ct, ft, qt
     # decode attention over an f32 KV cache with Llama-3-8B's heads (32 query, 8 key/value, 128 wide):
     # contiguous cache (sdpa_kv_cache) and 16-token pages (paged_attention), bytes = K and V read once
     H, HKV, D = 32, 8, 128

@@ -23,7 +23,9 @@ def _pack_int4_twos(v):
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 16, 16), (16, 128, 64), (130, 144, 208), (512, 4096, 4096), (33, 48, 4112),
-                                   (7, 5, 13), (64, 30, 64), (20, 64, 50)])
+                                   (7, 5, 13), (64, 30, 64), (20, 64, 50),
+                                   # the tcgen05 kernel: one tile, ragged M / N, a K tail, N not a multiple of 4
+                                   (128, 256, 256), (130, 300, 272), (1000, 1000, 1008), (257, 513, 4096)])
 def test_matmul_int8_bit_exact(ctx, backend, M, N, K):
     a = RNG.integers(-128, 128, size=(M, K), dtype=np.int8)
     b = RNG.integers(-128, 128, size=(K, N), dtype=np.int8)
@@ -32,12 +34,23 @@ def test_matmul_int8_bit_exact(ctx, backend, M, N, K):
     got = cb.to_host(np.int32, (M, N))
     want = a.astype(np.float64) @ b.astype(np.float64)      # |sum| <= K * 2^14 < 2^53: exact in f64 (and fits int32)
     assert np.array_equal(got, want.astype(np.int32))
+    if M * N >= 128 * 256 and K >= 256 and K % 16 == 0:
+        assert backend.last_kernel_name() == "lux_matmul_int8_tcgen05"
+        # the mma.sync kernel gives the same bits
+        backend.tune("int_matmul_kernel", 1)
+        try:
+            ctx.matmul_int8(ab, bb, cb, M, N, K)
+            assert backend.last_kernel_name() == "lux_matmul_int8"
+        finally:
+            backend.tune("int_matmul_kernel", 0)
+        assert np.array_equal(cb.to_host(np.int32, (M, N)), got)
     if M * N * K <= 1 << 22:
         assert np.array_equal(got, orc.matmul_int(a, b, M, N, K, 8))
 
 
-def test_matmul_int8_extremes(ctx):
-    M, N, K = 32, 32, 4096
+@pytest.mark.parametrize("M,N", [(32, 32), (128, 256)])
+def test_matmul_int8_extremes(ctx, M, N):
+    K = 4096
     a = np.full((M, K), -128, np.int8)
     b = np.full((K, N), -128, np.int8)
     ab, bb, cb = ctx.upload(a), ctx.upload(b), ctx.alloc(M * N * 4)
@@ -49,7 +62,7 @@ def test_matmul_int8_extremes(ctx):
     assert (cb.to_host(np.int32, (M, N)) == -K * 128 * 127).all()
 
 
-@pytest.mark.parametrize("M,N,K", [(16, 16, 16), (128, 256, 128), (100, 80, 96), (4096, 512, 4096), (9, 7, 10), (3, 16, 24)])
+@pytest.mark.parametrize("M,N,K", [(16, 16, 16), (128, 256, 128), (100, 80, 96), (4096, 512, 4096), (9, 7, 10), (3, 16, 24), (200, 260, 304)])
 def test_matmul_int4_int8_bit_exact(ctx, M, N, K):
     w = RNG.integers(-8, 8, size=(M, K), dtype=np.int8)
     b = RNG.integers(-128, 128, size=(K, N), dtype=np.int8)

@@ -47,6 +47,8 @@ struct Context {
     uint32_t*      d_absmax = nullptr;      // device word for lux_cuda_dynamic_quantize's tensor-wide max (allocated with the context)
     void*          d_splitk = nullptr;      // split-K exchange of the weights-in-TMEM GEMM: 128 KB per CTA pair,
     size_t         d_splitk_bytes = 0;      // allocated with the context (no entry point allocates for it)
+    void*          d_int = nullptr;         // lux_cuda_matmul_int8 on the tcgen05 path: B transposed (and A unpacked), grown on demand
+    size_t         d_int_bytes = 0;
     void*          d_attn = nullptr;        // partial results of attention calls that split the keys over CTAs:
     size_t         d_attn_bytes = 0;        // 16 MB, allocated with the context (a call takes fewer slices rather than allocate)
     std::mutex     mu;                      // guards the staging buffers
@@ -118,6 +120,7 @@ struct Tunables {
     int pdl = 0;                 // programmatic dependent launch of the persistent kernels: 0/1 on, 2 off
     int gemm_min_m = 0;          // smallest batch the weights-in-TMEM GEMM takes from the streaming kernels (0 = built-in)
     int gemm_tc_kernel = 0;      // 0 auto, 1 lux_qgemm_i4_tc, 2 lux_qgemm_i4_tc_wa wherever it applies
+    int int_matmul_kernel = 0;   // lux_cuda_matmul_int8 / _int4_int8: 0 tcgen05 for large shapes, 1 mma.sync kernels only
     int attn_splits = 0;         // attention: slices of the keys per (sequence, KV head, row block); 0 = choose
     int gemm_wa_narrow = 0;      // weights-in-TMEM GEMM, batch <= 64: 0 narrow tile (two CTAs per SM) when the launch has more CTAs
                                  // than SMs, 1 always, 2 never
@@ -208,6 +211,7 @@ inline cudaError_t launch_pdl(bool allow, void (*kfn)(KArgs...), dim3 grid, dim3
 #endif
 
 // ---- kernel launchers (defined in the .cu file named after each kernel family) ------
+LuxBackendError launch_matmul_int8_tcgen05(Context* ctx, const void* a, const void* b, int* c, int M, int N, int K, bool a_int4);
 
 // Where a kernel's epilogue pushes its 16-bit outputs for the push all-reduce (allreduce_push.cu):
 // every rank's window, this rank's number, the communicator's epoch counter.  world <= 1: no push.

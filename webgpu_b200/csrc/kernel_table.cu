@@ -34,6 +34,7 @@ const void* kernel_addr_qgemm_i4_tc_wa_f16_swiglu();
 const void* kernel_addr_qgemv_i4_units_fx_swiglu();
 const void* kernel_addr_qgemv_i4_units_fx_batch2();
 const void* kernel_addr_qgemv_i4_units_fx_batch4();
+const void* kernel_addr_matmul_int8_tcgen05();
 const void* kernel_addr_attn_stream_f32();
 const void* kernel_addr_attn_merge_f32();
 const void* kernel_addr_attn_plain_f32();
@@ -73,6 +74,7 @@ const Entry kTable[] = {
     {"lux_qgemv_i4_g128_units_fx_swiglu", luxcuda::kernel_addr_qgemv_i4_units_fx_swiglu, 512, 1, 1},
     {"lux_qgemv_i4_g128_units_fx_batch2", luxcuda::kernel_addr_qgemv_i4_units_fx_batch2, 512, 1, 1},
     {"lux_qgemv_i4_g128_units_fx_batch4", luxcuda::kernel_addr_qgemv_i4_units_fx_batch4, 512, 1, 1},
+    {"lux_matmul_int8_tcgen05",    luxcuda::kernel_addr_matmul_int8_tcgen05, 192, 1, 1},
     {"lux_attn_stream_f32",        luxcuda::kernel_addr_attn_stream_f32,    288, 1, 1},
     {"lux_attn_merge_f32",         luxcuda::kernel_addr_attn_merge_f32,     128, 1, 1},
     {"lux_attn_plain_f32",         luxcuda::kernel_addr_attn_plain_f32,     256, 1, 1},

@@ -141,6 +141,7 @@ static void cuda_destroy_context(LuxBackendContext* context) {
     cudaStreamSynchronize(ctx->stream);
     if (ctx->h_stage) cudaFreeHost(ctx->h_stage);
     if (ctx->d_stage) cudaFree(ctx->d_stage);
+    if (ctx->d_int) cudaFree(ctx->d_int);
     if (ctx->d_attn) cudaFree(ctx->d_attn);
     if (ctx->d_splitk) cudaFree(ctx->d_splitk);
     if (ctx->d_absmax) cudaFree(ctx->d_absmax);

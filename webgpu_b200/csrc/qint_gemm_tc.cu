@@ -1,0 +1,264 @@
+// qint_gemm_tc.cu -- int8 x int8 -> int32 matmul on the 5th-generation tensor cores
+// (tcgen05.mma kind::i8, accumulators in tensor memory), behind lux_cuda_matmul_int8 and
+// lux_cuda_matmul_int4_int8 for shapes large enough to fill tiles.
+//
+// The shader (luxcpp/webgpu kernels/wgsl/gpu/quantized.wgsl:497-555) walks 16 x 16 tiles with one
+// scalar multiply-add per thread and k; the mma.sync kernel in qint_matmul.cu reaches 220 TOP/s on
+// this GPU, a twentieth of what its tensor cores do through tcgen05.  Integer arithmetic is exact
+// (int32 accumulation, wrapping like the shader's i32), so the result is bit-identical either way.
+//
+// C[M, N] = A[M, K] . B[K, N]:
+//   * both operands must reach the tensor core K-major.  A is (row-major, K contiguous).  B is
+//     row-major [K, N], N contiguous, so a first kernel writes B^T [N, K] into the context's scratch
+//     (64 x 64 byte tiles through shared memory); for int4 x int8 another sign-extends A's two's
+//     complement nibbles (quantized.wgsl:150-158) to bytes.  Both passes move K*N (+ M*K) bytes,
+//     a few percent of the matmul's time;
+//   * a CTA owns a 128 x 256 tile of C: 256 int32 accumulator columns in tensor memory;
+//   * warp 0 (one thread): TMA producer, one 128 x 128-byte box of A and one 256 x 128-byte box of
+//     B^T per stage (128 k; 128-byte swizzle), four stages;
+//   * warp 1 (one thread): per stage one wait, four tcgen05.mma.kind::i8 (128 x 256 x 32) and one
+//     tcgen05.commit that frees the stage;
+//   * warps 2-5: epilogue, tcgen05.ld 32 columns at a time, 128-byte stores per thread.
+// K tails and ragged M / N are covered by the TMA's zero fill and by masked stores.  Every mbarrier
+// wait is bounded (the abort flag, status 0x7C05000B).  No cluster, no multicast.
+#include <algorithm>
+#include <mutex>
+
+#include "common.cuh"
+#include "tc_ptx.cuh"
+
+namespace luxcuda {
+
+bool encode_tensor_map_u8(void* map, int rank, const void* base, const uint64_t* dims, const uint64_t* strides_bytes,
+                          const uint32_t* box, bool swizzle128);
+
+namespace {
+
+using namespace tcptx;
+
+constexpr int I8_BM = 128, I8_BN = 256, I8_KB = 128;       // tile of C; k (= bytes) per stage
+constexpr int I8_STAGES = 4;
+constexpr int I8_A_BYTES = I8_BM * I8_KB, I8_B_BYTES = I8_BN * I8_KB;
+constexpr int I8_THREADS = 6 * 32;
+constexpr size_t I8_SMEM = 1024 + (size_t)I8_STAGES * (I8_A_BYTES + I8_B_BYTES) + 256;
+
+// Instruction descriptor for kind::i8: D = s32 (bits 4-5 = 2), A and B signed 8-bit (bits 7-9 and
+// 10-12 = 1), both K-major, N >> 3 at bits 17-22, M >> 4 at bits 24-28.
+__host__ __device__ constexpr uint32_t i8_idesc() {
+    return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(I8_BN >> 3) << 17) | ((uint32_t)(I8_BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
+}
+
+struct I8Params {
+    int* c;
+    uint32_t* status;
+    int M, N, K;
+};
+
+__global__ void __launch_bounds__(I8_THREADS, 1)
+lux_matmul_int8_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const I8Params p) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    unsigned char* a_ring = smem;
+    unsigned char* b_ring = a_ring + (size_t)I8_STAGES * I8_A_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(b_ring + (size_t)I8_STAGES * I8_B_BYTES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * I8_STAGES + 1);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * I8_BN, m0 = blockIdx.y * I8_BM;
+    const int KB = (p.K + I8_KB - 1) / I8_KB;
+    const uint32_t bar0 = smem_u32(bars);
+    auto full = [&](int s) { return bar0 + 8u * (uint32_t)s; };
+    auto empty = [&](int s) { return bar0 + 8u * (uint32_t)(I8_STAGES + s); };
+    const uint32_t acc_full = bar0 + 8u * (uint32_t)(2 * I8_STAGES);
+
+    if (tid == 0) {
+        for (int s = 0; s < I8_STAGES; s++) {
+            mbar_init(full(s), 1);
+            mbar_init(empty(s), 1);
+        }
+        mbar_init(acc_full, 1);
+        *abort_flag = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), 256);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kb = 0; kb < KB; kb++) {
+                const int s = kb % I8_STAGES;
+                if (kb >= I8_STAGES && !mbar_wait(empty(s), (uint32_t)((kb / I8_STAGES) - 1) & 1u, abort_flag)) break;
+                mbar_expect_tx(full(s), (uint32_t)(I8_A_BYTES + I8_B_BYTES));     // boxes past an edge are zero-filled and still counted
+                tma_load_2d(smem_u32(a_ring + (size_t)s * I8_A_BYTES), &map_a, kb * I8_KB, m0, full(s));
+                tma_load_2d(smem_u32(b_ring + (size_t)s * I8_B_BYTES), &map_b, kb * I8_KB, n0, full(s));
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = i8_idesc();
+            bool ok = true;
+            for (int kb = 0; kb < KB; kb++) {
+                const int s = kb % I8_STAGES;
+                ok = mbar_wait(full(s), (uint32_t)(kb / I8_STAGES) & 1u, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                const uint64_t a_desc = make_kmajor_sw128_desc(smem_u32(a_ring + (size_t)s * I8_A_BYTES));
+                const uint64_t b_desc = make_kmajor_sw128_desc(smem_u32(b_ring + (size_t)s * I8_B_BYTES));
+#pragma unroll
+                for (int k = 0; k < I8_KB / 32; k++)      // 32 k = 32 bytes inside the 128-byte swizzle row: +2 in the address field
+                    umma_i8(tmem_base, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
+                umma_commit(empty(s));
+            }
+            if (ok) umma_commit(acc_full);
+        }
+    } else {
+        // epilogue warps: TMEM lane quarter = warp % 4 (a warp reaches only its own quarter)
+        const int quad = warp & 3;
+        bool ok = warp_wait(acc_full, 0u, abort_flag, lane);
+        if (ok) {
+            tc_fence_after();
+            const int row = m0 + quad * 32 + lane;
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+            const bool vec = (p.N & 3) == 0;
+#pragma unroll 1
+            for (int c0 = 0; c0 < I8_BN; c0 += 32) {
+                if (n0 + c0 >= p.N) break;                 // warp-uniform
+                uint32_t v[32];
+                tmem_ld32(lane_addr + (uint32_t)c0, v);
+                tmem_ld_wait();
+                if (row < p.M) {
+                    int* dst = p.c + (size_t)row * p.N + n0 + c0;
+                    if (vec && n0 + c0 + 32 <= p.N) {
+#pragma unroll
+                        for (int j = 0; j < 8; j++)
+                            *reinterpret_cast<int4*>(dst + 4 * j) = make_int4((int)v[4 * j], (int)v[4 * j + 1], (int)v[4 * j + 2], (int)v[4 * j + 3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (n0 + c0 + j < p.N) dst[j] = (int)v[j];
+                    }
+                }
+            }
+            tc_fence_before();
+        }
+    }
+    __syncthreads();
+    if (*abort_flag) {
+        if (tid == 0 && p.status) atomicOr(p.status, 0x7C05000Bu);
+        for (int i = 0; i < 64; i++) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 256);
+    }
+}
+
+// B [K, N] (N contiguous) -> B^T [N, K] (K contiguous), bytes; 64 x 64 tiles
+__global__ void __launch_bounds__(256) lux_transpose_i8(const uint8_t* __restrict__ b, uint8_t* __restrict__ bt, int K, int N) {
+    __shared__ uint8_t tile[64][64 + 4];
+    const int k0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+    for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+        const int r = i >> 4, c4 = (i & 15) * 4;            // row k0 + r, columns n0 + c4 .. +3
+        uint32_t w = 0;
+        if (k0 + r < K) {
+            if (n0 + c4 + 3 < N && (N & 3) == 0) w = *reinterpret_cast<const uint32_t*>(b + (size_t)(k0 + r) * N + n0 + c4);
+            else
+                for (int j = 0; j < 4; j++)
+                    if (n0 + c4 + j < N) w |= (uint32_t)b[(size_t)(k0 + r) * N + n0 + c4 + j] << (8 * j);
+        }
+        *reinterpret_cast<uint32_t*>(&tile[r][c4]) = w;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+        const int n = i >> 4, k4 = (i & 15) * 4;            // output row n0 + n, columns k0 + k4 .. +3
+        if (n0 + n >= N) continue;
+        const uint32_t w = (uint32_t)tile[k4][n] | ((uint32_t)tile[k4 + 1][n] << 8) | ((uint32_t)tile[k4 + 2][n] << 16) |
+                           ((uint32_t)tile[k4 + 3][n] << 24);
+        if (k0 + k4 + 3 < K) *reinterpret_cast<uint32_t*>(bt + (size_t)(n0 + n) * K + k0 + k4) = w;      // K % 16 == 0: aligned
+        else
+            for (int j = 0; j < 4; j++)
+                if (k0 + k4 + j < K) bt[(size_t)(n0 + n) * K + k0 + k4 + j] = (uint8_t)(w >> (8 * j));
+    }
+}
+
+// int4 [M, K/2] (two's complement nibbles, element 2j in the low nibble of byte j) -> int8 [M, K]
+__global__ void __launch_bounds__(256) lux_unpack_s4_s8(const uint8_t* __restrict__ a4, uint8_t* __restrict__ a8, size_t bytes) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < bytes; i += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t v = a4[i];
+        const uint32_t lo = v & 0xFu, hi = v >> 4;
+        const uint32_t slo = lo | ((lo & 8u) ? 0xF0u : 0u), shi = hi | ((hi & 8u) ? 0xF0u : 0u);
+        *reinterpret_cast<uint16_t*>(a8 + 2 * i) = (uint16_t)(slo | (shi << 8));
+    }
+}
+
+}  // namespace
+
+// Returns NOT_SUPPORTED for shapes this kernel does not take (the caller falls back to the
+// mma.sync kernels): fewer than a tile's worth of work, K not a multiple of 16, unaligned views.
+LuxBackendError launch_matmul_int8_tcgen05(Context* ctx, const void* a, const void* b, int* c, int M, int N, int K, bool a_int4) {
+    if (K % 16 || (size_t)M * N < (size_t)I8_BM * I8_BN || K < 256) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c)) & 15u) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+    const size_t bt_bytes = ((size_t)N * K + 255) & ~(size_t)255, a8_bytes = a_int4 ? (((size_t)M * K + 255) & ~(size_t)255) : 0;
+    {
+        // scratch for B^T (and the unpacked A): grown on demand, kept with the context
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        if (ctx->d_int_bytes < bt_bytes + a8_bytes) {
+            cudaStreamSynchronize(ctx->stream);
+            if (ctx->d_int) cudaFree(ctx->d_int);
+            ctx->d_int = nullptr;
+            ctx->d_int_bytes = 0;
+            if (cudaMalloc(&ctx->d_int, bt_bytes + a8_bytes) != cudaSuccess) {
+                (void)cudaGetLastError();
+                return LUX_BACKEND_ERROR_NOT_SUPPORTED;          // the mma.sync kernel needs no scratch
+            }
+            ctx->d_int_bytes = bt_bytes + a8_bytes;
+        }
+    }
+    uint8_t* bt = (uint8_t*)ctx->d_int;
+    uint8_t* a8 = bt + bt_bytes;
+    lux_transpose_i8<<<dim3((N + 63) / 64, (K + 63) / 64), 256, 0, ctx->stream>>>((const uint8_t*)b, bt, K, N);
+    count_launch();
+    if (a_int4) {
+        const size_t bytes = (size_t)M * K / 2;
+        lux_unpack_s4_s8<<<(unsigned)std::min<size_t>((bytes + 255) / 256, (size_t)ctx->sm_count * 16), 256, 0, ctx->stream>>>((const uint8_t*)a, a8, bytes);
+        count_launch();
+    }
+    CUtensorMap ma, mb;
+    const uint64_t adims[2] = {(uint64_t)K, (uint64_t)M}, bdims[2] = {(uint64_t)K, (uint64_t)N};
+    const uint64_t strides[1] = {(uint64_t)K};
+    const uint32_t abox[2] = {(uint32_t)I8_KB, (uint32_t)I8_BM}, bbox[2] = {(uint32_t)I8_KB, (uint32_t)I8_BN};
+    if (!encode_tensor_map_u8(&ma, 2, a_int4 ? (const void*)a8 : a, adims, strides, abox, true)) return LUX_BACKEND_ERROR_INTERNAL;
+    if (!encode_tensor_map_u8(&mb, 2, bt, bdims, strides, bbox, true)) return LUX_BACKEND_ERROR_INTERNAL;
+    static std::atomic<bool> configured[64];
+    int dev = ctx->device & 63;
+    if (!configured[dev].load(std::memory_order_relaxed)) {
+        if (cudaFuncSetAttribute(lux_matmul_int8_tcgen05, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)I8_SMEM) != cudaSuccess)
+            return map_cuda(cudaGetLastError(), "lux_matmul_int8_tcgen05");
+        configured[dev].store(true, std::memory_order_relaxed);
+    }
+    I8Params p{c, ctx->d_status, M, N, K};
+    lux_matmul_int8_tcgen05<<<dim3((N + I8_BN - 1) / I8_BN, (M + I8_BM - 1) / I8_BM), I8_THREADS, I8_SMEM, ctx->stream>>>(ma, mb, p);
+    count_launch(a_int4 ? "lux_matmul_int4_int8_tcgen05" : "lux_matmul_int8_tcgen05");
+    return LUX_BACKEND_OK;
+}
+
+const void* kernel_addr_matmul_int8_tcgen05() { return (const void*)lux_matmul_int8_tcgen05; }
+
+}  // namespace luxcuda

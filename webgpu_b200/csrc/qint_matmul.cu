@@ -213,6 +213,13 @@ LuxBackendError matmul_int(LuxBackendContext* context, LuxBackendBuffer* a, LuxB
     const size_t a_bytes = A4 ? ((size_t)M * K + 1) / 2 : (size_t)M * K;
     if (ba->size < a_bytes || bb->size < (size_t)K * N || bc->size < (size_t)M * N * 4) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
     cudaSetDevice(ctx->device);
+    // matmuls with at least a 128 x 256 tile of outputs go to the tcgen05 kernel (qint_gemm_tc.cu);
+    // int_matmul_kernel = 1 keeps everything on the mma.sync kernels below
+    if (g_tune.int_matmul_kernel != 1) {
+        LuxBackendError e = launch_matmul_int8_tcgen05(ctx, ba->ptr, bb->ptr, (int*)bc->ptr, M, N, K, A4);
+        if (e == LUX_BACKEND_OK) return finish_op(ctx, false, what);
+        if (e != LUX_BACKEND_ERROR_NOT_SUPPORTED) return e;
+    }
     const bool tiled = K % 16 == 0 && N % 16 == 0 && aligned16(ba->ptr) && aligned16(bb->ptr) && aligned16(bc->ptr) &&
                        (N + TN - 1) / TN <= 65535 * 32 && (M + TM - 1) / TM <= 65535;
     if (tiled) {
