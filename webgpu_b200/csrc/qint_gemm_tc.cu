@@ -103,7 +103,7 @@ lux_matmul_int8_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_
         if (lane == 0) {
             for (int kb = 0; kb < KB; kb++) {
                 const int s = kb % I8_STAGES;
-                if (kb >= I8_STAGES && !mbar_wait(empty(s), (uint32_t)((kb / I8_STAGES) - 1) & 1u, abort_flag)) break;
+                if (kb >= I8_STAGES && !mbar_wait_relaxed(empty(s), (uint32_t)((kb / I8_STAGES) - 1) & 1u, abort_flag)) break;
                 mbar_expect_tx(full(s), (uint32_t)(I8_A_BYTES + I8_B_BYTES));     // boxes past an edge are zero-filled and still counted
                 tma_load_2d(smem_u32(a_ring + (size_t)s * I8_A_BYTES), &map_a, kb * I8_KB, m0, full(s));
                 tma_load_2d(smem_u32(b_ring + (size_t)s * I8_B_BYTES), &map_b, kb * I8_KB, n0, full(s));
@@ -130,7 +130,9 @@ lux_matmul_int8_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_
     } else {
         // epilogue warps: TMEM lane quarter = warp % 4 (a warp reaches only its own quarter)
         const int quad = warp & 3;
-        bool ok = warp_wait(acc_full, 0u, abort_flag, lane);
+        // (sleeping between polls: these four warps wait for the whole main loop, and tight polls next to
+        // the MMA-issuing thread make its own satisfied waits several times dearer)
+        bool ok = warp_wait_relaxed(acc_full, 0u, abort_flag, lane);
         if (ok) {
             tc_fence_after();
             const int row = m0 + quad * 32 + lane;
@@ -170,31 +172,42 @@ lux_matmul_int8_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_
     }
 }
 
-// B [K, N] (N contiguous) -> B^T [N, K] (K contiguous), bytes; 64 x 64 tiles
+// B [K, N] (N contiguous) -> B^T [N, K] (K contiguous), bytes; 64 x 64 tiles.  A full tile goes
+// through 4 x 4 byte blocks transposed in registers (prmt) and 16-byte stores; edge tiles byte by byte.
+__device__ __forceinline__ uint32_t prmt_i8(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
 __global__ void __launch_bounds__(256) lux_transpose_i8(const uint8_t* __restrict__ b, uint8_t* __restrict__ bt, int K, int N) {
-    __shared__ uint8_t tile[64][64 + 4];
-    const int k0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
-    for (int i = threadIdx.x; i < 64 * 16; i += 256) {
-        const int r = i >> 4, c4 = (i & 15) * 4;            // row k0 + r, columns n0 + c4 .. +3
-        uint32_t w = 0;
-        if (k0 + r < K) {
-            if (n0 + c4 + 3 < N && (N & 3) == 0) w = *reinterpret_cast<const uint32_t*>(b + (size_t)(k0 + r) * N + n0 + c4);
-            else
-                for (int j = 0; j < 4; j++)
-                    if (n0 + c4 + j < N) w |= (uint32_t)b[(size_t)(k0 + r) * N + n0 + c4 + j] << (8 * j);
-        }
-        *reinterpret_cast<uint32_t*>(&tile[r][c4]) = w;
+    __shared__ uint32_t st[64][17];                        // [n][k / 4], one word of padding per row
+    const int k0 = blockIdx.y * 64, n0 = blockIdx.x * 64, t = threadIdx.x;
+    if (k0 + 64 <= K && n0 + 64 <= N && (N & 3) == 0) {
+        const int kr = t >> 4, nc = t & 15;                // rows k0 + 4 kr .. + 3, columns n0 + 4 nc .. + 3
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) w[i] = *reinterpret_cast<const uint32_t*>(b + (size_t)(k0 + 4 * kr + i) * N + n0 + 4 * nc);
+        const uint32_t t0 = prmt_i8(w[0], w[1], 0x5140), t1 = prmt_i8(w[2], w[3], 0x5140);
+        const uint32_t t2 = prmt_i8(w[0], w[1], 0x7362), t3 = prmt_i8(w[2], w[3], 0x7362);
+        st[4 * nc + 0][kr] = prmt_i8(t0, t1, 0x5410);
+        st[4 * nc + 1][kr] = prmt_i8(t0, t1, 0x7632);
+        st[4 * nc + 2][kr] = prmt_i8(t2, t3, 0x5410);
+        st[4 * nc + 3][kr] = prmt_i8(t2, t3, 0x7632);
+        __syncthreads();
+        const int n = t >> 2, q = t & 3;                   // output row n0 + n, bytes k0 + 16 q .. + 15
+        const uint4 v = make_uint4(st[n][4 * q], st[n][4 * q + 1], st[n][4 * q + 2], st[n][4 * q + 3]);
+        *reinterpret_cast<uint4*>(bt + (size_t)(n0 + n) * K + k0 + 16 * q) = v;       // K % 16 == 0 and a 256-byte aligned base
+        return;
+    }
+    uint8_t (*tile)[68] = reinterpret_cast<uint8_t (*)[68]>(st);
+    for (int i = t; i < 64 * 64; i += 256) {
+        const int r = i >> 6, c = i & 63;
+        tile[r][c] = (k0 + r < K && n0 + c < N) ? b[(size_t)(k0 + r) * N + n0 + c] : (uint8_t)0;
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < 64 * 16; i += 256) {
-        const int n = i >> 4, k4 = (i & 15) * 4;            // output row n0 + n, columns k0 + k4 .. +3
-        if (n0 + n >= N) continue;
-        const uint32_t w = (uint32_t)tile[k4][n] | ((uint32_t)tile[k4 + 1][n] << 8) | ((uint32_t)tile[k4 + 2][n] << 16) |
-                           ((uint32_t)tile[k4 + 3][n] << 24);
-        if (k0 + k4 + 3 < K) *reinterpret_cast<uint32_t*>(bt + (size_t)(n0 + n) * K + k0 + k4) = w;      // K % 16 == 0: aligned
-        else
-            for (int j = 0; j < 4; j++)
-                if (k0 + k4 + j < K) bt[(size_t)(n0 + n) * K + k0 + k4 + j] = (uint8_t)(w >> (8 * j));
+    for (int i = t; i < 64 * 64; i += 256) {
+        const int n = i >> 6, k = i & 63;
+        if (n0 + n < N && k0 + k < K) bt[(size_t)(n0 + n) * K + k0 + k] = tile[k][n];
     }
 }
 
