@@ -49,7 +49,7 @@ def test_div_and_unaligned_views(ctx, backend):
     assert orc.rel_l2(ob.to_host(np.float32, a.shape), orc.unary_f32("gelu", a)) < 1e-6
 
 
-@pytest.mark.parametrize("rows,cols", [(1, 1), (32, 32), (33, 65), (1000, 37), (4096, 4096)])
+@pytest.mark.parametrize("rows,cols", [(1, 1), (32, 32), (33, 65), (1000, 37), (4096, 4096), (64, 192), (128, 64), (4160, 4096)])
 def test_transpose(ctx, rows, cols):
     x = RNG.standard_normal((rows, cols)).astype(np.float32)
     xb, ob = ctx.upload(x), ctx.alloc(x.nbytes)

@@ -165,8 +165,25 @@ __global__ void __launch_bounds__(256) lux_requantize_i32_i8(const int* __restri
 // phase 1 of dynamic_quantize: max |x| over the tensor, as the bit pattern of a non-negative float
 __global__ void __launch_bounds__(256) lux_absmax_f32(const float* __restrict__ x, size_t n, uint32_t* __restrict__ out_bits) {
     float m = 0.0f;
-    const size_t stride = (size_t)gridDim.x * 256;
-    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += stride) m = fmaxf(m, fabsf(x[i]));
+    const size_t stride = (size_t)gridDim.x * 256, t0 = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if ((reinterpret_cast<uintptr_t>(x) & 15u) == 0) {
+        // 16-byte loads, two in flight per thread
+        const float4* x4 = reinterpret_cast<const float4*>(x);
+        const size_t n4 = n / 4;
+        size_t i = t0;
+        for (; i + stride < n4; i += 2 * stride) {
+            const float4 a = __ldg(x4 + i), b = __ldg(x4 + i + stride);
+            m = fmaxf(m, fmaxf(fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))),
+                               fmaxf(fmaxf(fabsf(b.x), fabsf(b.y)), fmaxf(fabsf(b.z), fabsf(b.w)))));
+        }
+        if (i < n4) {
+            const float4 a = __ldg(x4 + i);
+            m = fmaxf(m, fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))));
+        }
+        for (size_t j = n4 * 4 + t0; j < n; j += stride) m = fmaxf(m, fabsf(x[j]));
+    } else {
+        for (size_t i = t0; i < n; i += stride) m = fmaxf(m, fabsf(x[i]));
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
     if ((threadIdx.x & 31) == 0) atomicMax(out_bits, __float_as_uint(m));
@@ -181,12 +198,31 @@ __global__ void __launch_bounds__(256) lux_dynamic_quantize(const float* __restr
     if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = scale;
     const size_t octets = (n + 7) / 8;
     const size_t stride = (size_t)gridDim.x * 256;
+    // 16-byte loads and (int8) 8-byte stores where the views allow them
+    const bool vec = (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && (reinterpret_cast<uintptr_t>(out) & 7u) == 0;
     for (size_t o = (size_t)blockIdx.x * 256 + threadIdx.x; o < octets; o += stride) {
         int q[8];
+        if (vec && o * 8 + 8 <= n) {
+            const float4 a = __ldg(reinterpret_cast<const float4*>(x) + 2 * o), b = __ldg(reinterpret_cast<const float4*>(x) + 2 * o + 1);
+            const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 #pragma unroll
-        for (int j = 0; j < 8; j++) {
-            const size_t i = o * 8 + j;
-            q[j] = i < n ? __float2int_rz(rintf(__fdiv_rn(x[i], scale))) : 0;
+            for (int j = 0; j < 8; j++) q[j] = __float2int_rz(rintf(__fdiv_rn(v[j], scale)));
+            if (BITS == 8) {
+                uint32_t lo = 0, hi = 0;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    lo |= (uint32_t)(min(max(q[j], -128), 127) & 0xFF) << (8 * j);
+                    hi |= (uint32_t)(min(max(q[4 + j], -128), 127) & 0xFF) << (8 * j);
+                }
+                *reinterpret_cast<uint2*>(out + o * 8) = make_uint2(lo, hi);
+                continue;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const size_t i = o * 8 + j;
+                q[j] = i < n ? __float2int_rz(rintf(__fdiv_rn(x[i], scale))) : 0;
+            }
         }
         if (BITS == 4) {
             uint32_t w = 0;
