@@ -537,6 +537,14 @@ def test_host_pointer_variant_matches_device_variant(ctx):
     a = ctx.qmatmul_host(x, L)
     b = _run(ctx, x, layer)
     assert np.array_equal(a.view(np.uint16), b.view(np.uint16))
+    # the bound form (arguments marshalled once) reads x and fills `out` at every call
+    xs = x.copy()
+    out = np.zeros_like(a)
+    call = ctx.qmatmul_host_bound(xs, L, out)
+    assert call() is out and np.array_equal(out.view(np.uint16), a.view(np.uint16))
+    xs[:] = 2 * x
+    call()
+    assert np.array_equal(out.view(np.uint16), ctx.qmatmul_host(2 * x, L).view(np.uint16))
 
 
 def test_f32_slots(ctx):

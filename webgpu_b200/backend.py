@@ -502,6 +502,25 @@ class Context:
             raise BackendError(code, "lux_cuda_qmatmul_host")
         return out
 
+    def qmatmul_host_bound(self, x: np.ndarray, L: DeviceQLayer, out: np.ndarray, y_dtype: int | None = None, flags: int = 0):
+        """A decode loop's form of qmatmul_host: the arguments of lux_cuda_qmatmul_host for FIXED host
+        arrays x and out are marshalled once, and the returned function makes the call (it reads x and
+        fills out each time it is called; it returns out).  The arrays must stay alive and in place."""
+        assert x.flags.c_contiguous and out.flags.c_contiguous and out.flags.writeable
+        xd = np_dtype_code(x)
+        d = self._desc(L, x.shape[0], xd, xd if y_dtype is None else y_dtype, flags)
+        fn = self.backend.lib.lux_cuda_qmatmul_host
+        args = (C.c_void_p(self.handle), C.byref(d), C.c_void_p(x.ctypes.data), C.c_void_p(L.w.handle), C.c_void_p(L.scales.handle),
+                C.c_void_p(L.zeros.handle) if L.zeros else None, C.c_void_p(out.ctypes.data))
+        keep = (d, x, out, L)
+
+        def call(_fn=fn, _args=args, _keep=keep):
+            code = _fn(*_args)
+            if code != OK:
+                raise BackendError(code, "lux_cuda_qmatmul_host")
+            return _keep[2]
+        return call
+
     def qdequant(self, L: DeviceQLayer, out_dtype: int = F32) -> np.ndarray:
         out = self.alloc(L.N * L.K * (4 if out_dtype == F32 else 2))
         d = self._desc(L, 0, F32, out_dtype, 0)
