@@ -13,11 +13,12 @@
 //     (64 x 64 byte tiles through shared memory); for int4 x int8 another sign-extends A's two's
 //     complement nibbles (quantized.wgsl:150-158) to bytes.  Both passes move K*N (+ M*K) bytes,
 //     a few percent of the matmul's time;
-//   * a CTA owns a 128 x 256 tile of C: 256 int32 accumulator columns in tensor memory;
-//   * warp 0 (one thread): TMA producer, one 128 x 128-byte box of A and one 256 x 128-byte box of
-//     B^T per stage (128 k; 128-byte swizzle), four stages;
-//   * warp 1 (one thread): per stage one wait, four tcgen05.mma.kind::i8 (128 x 256 x 32) and one
-//     tcgen05.commit that frees the stage;
+//   * a CTA owns a 256 x 256 tile of C (128 x 256 when M <= 128): two int32 accumulators of 256
+//     columns each in tensor memory, fed by the same B tile;
+//   * warp 0 (one thread): TMA producer, one 256 x 128-byte box of A and one 256 x 128-byte box of
+//     B^T per stage (128 k; 128-byte swizzle), three stages (four with one accumulator);
+//   * warp 1 (one thread): per stage one wait, four tcgen05.mma.kind::i8 (128 x 256 x 32) per
+//     accumulator and one tcgen05.commit that frees the stage;
 //   * warps 2-5: epilogue, tcgen05.ld 32 columns at a time, 128-byte stores per thread.
 // K tails and ragged M / N are covered by the TMA's zero fill and by masked stores.  Every mbarrier
 // wait is bounded (the abort flag, status 0x7C05000B).  No cluster, no multicast.
@@ -37,10 +38,13 @@ namespace {
 using namespace tcptx;
 
 constexpr int I8_BM = 128, I8_BN = 256, I8_KB = 128;       // tile of C; k (= bytes) per stage
-constexpr int I8_STAGES = 4;
 constexpr int I8_A_BYTES = I8_BM * I8_KB, I8_B_BYTES = I8_BN * I8_KB;
 constexpr int I8_THREADS = 6 * 32;
-constexpr size_t I8_SMEM = 1024 + (size_t)I8_STAGES * (I8_A_BYTES + I8_B_BYTES) + 256;
+// MA = row tiles of 128 per CTA (1 or 2): two accumulators share every B tile, which cuts the bytes a CTA
+// pulls from L2 per multiply-add by a third (the one-tile form asks for 92 bytes per clock and SM at the
+// tensor pipe's rate and ran at half of it)
+__host__ __device__ constexpr int i8_stages(int ma) { return ma == 2 ? 3 : 4; }
+__host__ __device__ constexpr size_t i8_smem(int ma) { return 1024 + (size_t)i8_stages(ma) * (ma * I8_A_BYTES + I8_B_BYTES) + 256; }
 
 // Instruction descriptor for kind::i8: D = s32 (bits 4-5 = 2), A and B signed 8-bit (bits 7-9 and
 // 10-12 = 1), both K-major, N >> 3 at bits 17-22, M >> 4 at bits 24-28.
@@ -62,17 +66,20 @@ struct I8Params {
     int M, N, K;
 };
 
+template <int MA>
 __global__ void __launch_bounds__(I8_THREADS, 1)
 lux_matmul_int8_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const I8Params p) {
+    constexpr int I8_STAGES = i8_stages(MA);
+    constexpr int A_STAGE = MA * I8_A_BYTES;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     unsigned char* a_ring = smem;
-    unsigned char* b_ring = a_ring + (size_t)I8_STAGES * I8_A_BYTES;
+    unsigned char* b_ring = a_ring + (size_t)I8_STAGES * A_STAGE;
     uint64_t* bars = reinterpret_cast<uint64_t*>(b_ring + (size_t)I8_STAGES * I8_B_BYTES);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * I8_STAGES + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n0 = blockIdx.x * I8_BN, m0 = blockIdx.y * I8_BM;
+    const int n0 = blockIdx.x * I8_BN, m0 = blockIdx.y * (MA * I8_BM);
     const int KB = (p.K + I8_KB - 1) / I8_KB;
     const uint32_t bar0 = smem_u32(bars);
     auto full = [&](int s) { return bar0 + 8u * (uint32_t)s; };
@@ -91,7 +98,7 @@ lux_matmul_int8_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
     }
     if (warp == 1) {
-        tmem_alloc(smem_u32(tmem_slot), 256);
+        tmem_alloc(smem_u32(tmem_slot), MA * 256);
         tmem_relinquish();
     }
     tc_fence_before();
@@ -104,8 +111,8 @@ lux_matmul_int8_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_
             for (int kb = 0; kb < KB; kb++) {
                 const int s = kb % I8_STAGES;
                 if (kb >= I8_STAGES && !mbar_wait_relaxed(empty(s), (uint32_t)((kb / I8_STAGES) - 1) & 1u, abort_flag)) break;
-                mbar_expect_tx(full(s), (uint32_t)(I8_A_BYTES + I8_B_BYTES));     // boxes past an edge are zero-filled and still counted
-                tma_load_2d(smem_u32(a_ring + (size_t)s * I8_A_BYTES), &map_a, kb * I8_KB, m0, full(s));
+                mbar_expect_tx(full(s), (uint32_t)(A_STAGE + I8_B_BYTES));        // boxes past an edge are zero-filled and still counted
+                tma_load_2d(smem_u32(a_ring + (size_t)s * A_STAGE), &map_a, kb * I8_KB, m0, full(s));
                 tma_load_2d(smem_u32(b_ring + (size_t)s * I8_B_BYTES), &map_b, kb * I8_KB, n0, full(s));
             }
         }
@@ -118,11 +125,15 @@ lux_matmul_int8_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_
                 ok = mbar_wait(full(s), (uint32_t)(kb / I8_STAGES) & 1u, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
-                const uint64_t a_desc = make_kmajor_sw128_desc(smem_u32(a_ring + (size_t)s * I8_A_BYTES));
                 const uint64_t b_desc = make_kmajor_sw128_desc(smem_u32(b_ring + (size_t)s * I8_B_BYTES));
 #pragma unroll
-                for (int k = 0; k < I8_KB / 32; k++)      // 32 k = 32 bytes inside the 128-byte swizzle row: +2 in the address field
-                    umma_i8(tmem_base, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
+                for (int a = 0; a < MA; a++) {
+                    // accumulator a: rows a * 128 .. of the A box, TMEM columns a * 256 ..
+                    const uint64_t a_desc = make_kmajor_sw128_desc(smem_u32(a_ring + (size_t)s * A_STAGE + (size_t)a * I8_A_BYTES));
+#pragma unroll
+                    for (int k = 0; k < I8_KB / 32; k++)  // 32 k = 32 bytes inside the 128-byte swizzle row: +2 in the address field
+                        umma_i8(tmem_base + (uint32_t)(a * 256), a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
+                }
                 umma_commit(empty(s));
             }
             if (ok) umma_commit(acc_full);
@@ -135,26 +146,37 @@ lux_matmul_int8_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_
         bool ok = warp_wait_relaxed(acc_full, 0u, abort_flag, lane);
         if (ok) {
             tc_fence_after();
-            const int row = m0 + quad * 32 + lane;
-            const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
             const bool vec = (p.N & 3) == 0;
+            uint32_t* patch = reinterpret_cast<uint32_t*>(a_ring) + (warp - 2) * (32 * 33);   // the loads are over: the ring is free
 #pragma unroll 1
-            for (int c0 = 0; c0 < I8_BN; c0 += 32) {
-                if (n0 + c0 >= p.N) break;                 // warp-uniform
+            for (int cc = 0; cc < MA * I8_BN; cc += 32) {
+                const int a = cc / I8_BN, c0 = cc - a * I8_BN;
+                const int row = m0 + a * I8_BM + quad * 32 + lane;
+                const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * 256);
+                if (n0 + c0 >= p.N || m0 + a * I8_BM >= p.M) continue;   // warp-uniform
                 uint32_t v[32];
                 tmem_ld32(lane_addr + (uint32_t)c0, v);
                 tmem_ld_wait();
-                if (row < p.M) {
-                    int* dst = p.c + (size_t)row * p.N + n0 + c0;
-                    if (vec && n0 + c0 + 32 <= p.N) {
+                if (vec && n0 + c0 + 32 <= p.N) {
+                    // through this warp's 32 x 33-word patch of the (idle) ring, so that a store instruction
+                    // writes four whole 128-byte pieces of four rows instead of 16 bytes of 32 rows
 #pragma unroll
-                        for (int j = 0; j < 8; j++)
-                            *reinterpret_cast<int4*>(dst + 4 * j) = make_int4((int)v[4 * j], (int)v[4 * j + 1], (int)v[4 * j + 2], (int)v[4 * j + 3]);
-                    } else {
+                    for (int j = 0; j < 32; j++) patch[lane * 33 + j] = v[j];
+                    __syncwarp();
 #pragma unroll
-                        for (int j = 0; j < 32; j++)
-                            if (n0 + c0 + j < p.N) dst[j] = (int)v[j];
+                    for (int it = 0; it < 8; it++) {
+                        const int r = it * 4 + (lane >> 3), q = lane & 7;
+                        const int grow = m0 + a * I8_BM + quad * 32 + r;
+                        const uint32_t* src = patch + r * 33 + q * 4;
+                        if (grow < p.M)
+                            *reinterpret_cast<int4*>(p.c + (size_t)grow * p.N + n0 + c0 + q * 4) = make_int4((int)src[0], (int)src[1], (int)src[2], (int)src[3]);
                     }
+                    __syncwarp();
+                } else if (row < p.M) {
+                    int* dst = p.c + (size_t)row * p.N + n0 + c0;
+#pragma unroll
+                    for (int j = 0; j < 32; j++)
+                        if (n0 + c0 + j < p.N) dst[j] = (int)v[j];
                 }
             }
             tc_fence_before();
@@ -168,7 +190,7 @@ lux_matmul_int8_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_
     }
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, 256);
+        tmem_dealloc(tmem_base, MA * 256);
     }
 }
 
@@ -253,25 +275,29 @@ LuxBackendError launch_matmul_int8_tcgen05(Context* ctx, const void* a, const vo
         lux_unpack_s4_s8<<<(unsigned)std::min<size_t>((bytes + 255) / 256, (size_t)ctx->sm_count * 16), 256, 0, ctx->stream>>>((const uint8_t*)a, a8, bytes);
         count_launch();
     }
-    CUtensorMap ma, mb;
+    CUtensorMap ma_map, mb;
     const uint64_t adims[2] = {(uint64_t)K, (uint64_t)M}, bdims[2] = {(uint64_t)K, (uint64_t)N};
     const uint64_t strides[1] = {(uint64_t)K};
-    const uint32_t abox[2] = {(uint32_t)I8_KB, (uint32_t)I8_BM}, bbox[2] = {(uint32_t)I8_KB, (uint32_t)I8_BN};
-    if (!encode_tensor_map_u8(&ma, 2, a_int4 ? (const void*)a8 : a, adims, strides, abox, true)) return LUX_BACKEND_ERROR_INTERNAL;
+    const int ma = M > I8_BM ? 2 : 1;
+    const uint32_t abox[2] = {(uint32_t)I8_KB, (uint32_t)(ma * I8_BM)}, bbox[2] = {(uint32_t)I8_KB, (uint32_t)I8_BN};
+    if (!encode_tensor_map_u8(&ma_map, 2, a_int4 ? (const void*)a8 : a, adims, strides, abox, true)) return LUX_BACKEND_ERROR_INTERNAL;
     if (!encode_tensor_map_u8(&mb, 2, bt, bdims, strides, bbox, true)) return LUX_BACKEND_ERROR_INTERNAL;
     static std::atomic<bool> configured[64];
     int dev = ctx->device & 63;
     if (!configured[dev].load(std::memory_order_relaxed)) {
-        if (cudaFuncSetAttribute(lux_matmul_int8_tcgen05, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)I8_SMEM) != cudaSuccess)
+        if (cudaFuncSetAttribute(lux_matmul_int8_tcgen05<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)i8_smem(1)) != cudaSuccess ||
+            cudaFuncSetAttribute(lux_matmul_int8_tcgen05<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)i8_smem(2)) != cudaSuccess)
             return map_cuda(cudaGetLastError(), "lux_matmul_int8_tcgen05");
         configured[dev].store(true, std::memory_order_relaxed);
     }
     I8Params p{c, ctx->d_status, M, N, K};
-    lux_matmul_int8_tcgen05<<<dim3((N + I8_BN - 1) / I8_BN, (M + I8_BM - 1) / I8_BM), I8_THREADS, I8_SMEM, ctx->stream>>>(ma, mb, p);
+    const dim3 grid((N + I8_BN - 1) / I8_BN, (M + ma * I8_BM - 1) / (ma * I8_BM));
+    if (ma == 2) lux_matmul_int8_tcgen05<2><<<grid, I8_THREADS, i8_smem(2), ctx->stream>>>(ma_map, mb, p);
+    else lux_matmul_int8_tcgen05<1><<<grid, I8_THREADS, i8_smem(1), ctx->stream>>>(ma_map, mb, p);
     count_launch(a_int4 ? "lux_matmul_int4_int8_tcgen05" : "lux_matmul_int8_tcgen05");
     return LUX_BACKEND_OK;
 }
 
-const void* kernel_addr_matmul_int8_tcgen05() { return (const void*)lux_matmul_int8_tcgen05; }
+const void* kernel_addr_matmul_int8_tcgen05() { return (const void*)lux_matmul_int8_tcgen05<2>; }
 
 }  // namespace luxcuda
