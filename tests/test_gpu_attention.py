@@ -326,3 +326,39 @@ def test_paged_attention_bad_block_is_reported_not_followed(ctx):
         _paged(ctx, q, kc, vc, bad, cl, 0.125)
     assert err.value.code == B.DEVICE_LOST and ctx.last_device_status() == 0x7C050009
     _close(_paged(ctx, q, kc, vc, table, cl, 0.125), orc.paged_attention(q, kc, vc, table, cl, 0.125))      # the context still works
+
+
+def test_decode_at_bench_size_properties(ctx):
+    """The largest decode shape of the benchmark that a test can afford (8 sequences x 4096 keys, Llama-3-8B
+    heads, 268 MB of KV cache): the oracle on every row, and properties that do not depend on the size --
+    weights that sum to one, the paged kernel path giving the SAME BITS as the contiguous one when the
+    pages hold the same keys in the same order, and independence of the sequences."""
+    rng = np.random.default_rng(99)
+    B_, H, Hkv, D, L = 8, 32, 8, 128, 4096
+    kc = rng.standard_normal((B_, Hkv, L, D), np.float32)
+    vc = rng.standard_normal((B_, Hkv, L, D), np.float32)
+    q = rng.standard_normal((B_, H, 1, D), np.float32)
+    scale = 1.0 / np.sqrt(D)
+    kcb, vcb, qb, ob = ctx.upload(kc), ctx.upload(vc), ctx.upload(q), ctx.alloc(q.nbytes)
+    ctx.sdpa_kv_cache(qb, kcb, vcb, ob, B_, H, Hkv, 1, L - 1, L, D, scale)
+    out = ob.to_host(np.float32, q.shape)
+    _close(out, orc.sdpa_kv_cache(q, kc, vc, L - 1, scale))
+    # softmax weights sum to one: with V = 1 every output is 1
+    ones = ctx.upload(np.ones_like(vc))
+    ctx.sdpa_kv_cache(qb, kcb, ones, ob, B_, H, Hkv, 1, L - 1, L, D, scale)
+    np.testing.assert_allclose(ob.to_host(np.float32, q.shape), 1.0, rtol=0, atol=2e-6)
+    # the same keys as 16-token pages, in order: [seq, head, page, token, d] -> [seq * pages + page, head, token, d]
+    bs = 16
+    nblk = L // bs
+    kp = np.ascontiguousarray(kc.reshape(B_, Hkv, nblk, bs, D).transpose(0, 2, 1, 3, 4)).reshape(B_ * nblk, Hkv, bs, D)
+    vp = np.ascontiguousarray(vc.reshape(B_, Hkv, nblk, bs, D).transpose(0, 2, 1, 3, 4)).reshape(B_ * nblk, Hkv, bs, D)
+    table = (np.arange(B_ * nblk, dtype=np.int32)).reshape(B_, nblk)
+    lens = np.full(B_, L, np.int32)
+    pb = ctx.alloc(q.nbytes)
+    ctx.paged_attention(qb, ctx.upload(kp), ctx.upload(vp), ctx.upload(table), ctx.upload(lens), pb, B_, H, Hkv, D, bs, nblk, scale)
+    paged = pb.to_host(np.float32, (B_, H, D))
+    assert np.array_equal(paged.view(np.uint32), out.reshape(B_, H, D).view(np.uint32))
+    # a sequence's output does not depend on the others: sequence 3 alone
+    one = ctx.alloc(H * D * 4)
+    ctx.sdpa_kv_cache(ctx.upload(q[3:4]), ctx.upload(kc[3:4]), ctx.upload(vc[3:4]), one, 1, H, Hkv, 1, L - 1, L, D, scale)
+    _close(one.to_host(np.float32, (1, H, 1, D)), out[3:4])
