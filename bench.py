@@ -536,12 +536,12 @@ def ffn_flops(M, d, world=1):
 def ffn_parity(x, gate_up, down, y, world, M):
     """rel-L2 of the GPU result y[M, H] against the oracle's sharded FFN (partials narrowed to f16
     per rank and summed in rank order); for batches above four rows on a subset of the rows (rows
-    are independent).  From 12 rows on the kernels multiply weights rounded to f16."""
+    are independent).  From 5 rows on the kernels multiply weights rounded to f16."""
     from oracle import oracle as orc      # checker only, outside every timed region
     from webgpu_b200 import tp
     rows = np.arange(M) if M <= 4 else np.unique(np.linspace(0, M - 1, 4).astype(int))
     shards = [tuple(l.triple for l in tp.shard_mlp(gate_up, down, r, world)) for r in range(world)]
-    ref = orc.tp_mlp(np.ascontiguousarray(x[rows]), shards, fused=True, w_round=orc.F16 if M >= 12 else orc.F32)
+    ref = orc.tp_mlp(np.ascontiguousarray(x[rows]), shards, fused=True, w_round=orc.F16 if M >= 5 else orc.F32)
     return orc.rel_l2(np.ascontiguousarray(y[rows]), ref), [int(r) for r in rows]
 
 
@@ -796,8 +796,8 @@ def bench_tp(args, peaks):
             "tp1_us_same_box": tp1["us"] if tp1 else None, "ffn70b_cfg5_tp1": tp1,
             "strong_scaling_efficiency": tp1["us"] / (world * sec * 1e6) if tp1 else None,
         }
-    if line is not None and M >= 12:
-        # From 12 batch rows on both FFN kernels run on the tensor cores: the roofline that bounds
+    if line is not None and M >= 5:
+        # From 5 batch rows on both FFN kernels run on the tensor cores: the roofline that bounds
         # them is the dense 16-bit tensor peak, not HBM (the weights are read once either way).
         tf = ffn_flops(M, d, world) / sec_compute / 1e12
         line["roofline"] = {"bound": "tensor", "achieved": tf, "peak": peaks["bf16"], "unit": "TFLOP/s",

@@ -24,7 +24,7 @@ def _rows(M, n=4):
     return np.unique(np.linspace(0, M - 1, n).astype(int))
 
 
-@pytest.mark.parametrize("M", [16, 64])
+@pytest.mark.parametrize("M", [5, 8, 11, 16, 64])
 @pytest.mark.parametrize("name", list(synth.SWEEP_LAYERS))
 def test_config4_default_route(ctx, backend, name, M):
     x, layer = synth.config4(name, M)

@@ -161,9 +161,10 @@ def test_wa_mlp_m256(ctx, backend):
     assert ctx.last_device_status() == 0
 
 
-@pytest.mark.parametrize("M,expect", [(8, "lux_qgemv_i4_g128_stream"), (12, "lux_qgemm_i4_tc_wa_f16"), (32, "lux_qgemm_i4_tc_wa_f16")])
-def test_small_batches_cross_over_at_12(ctx, backend, M, expect):
-    """Below 12 batch rows the streaming kernels keep the shape, from 12 up the tensor-core
+@pytest.mark.parametrize("M,expect", [(4, "lux_qgemv_i4_g128_units_fx"), (5, "lux_qgemm_i4_tc_wa_f16"), (8, "lux_qgemm_i4_tc_wa_f16"),
+                                      (12, "lux_qgemm_i4_tc_wa_f16"), (32, "lux_qgemm_i4_tc_wa_f16")])
+def test_small_batches_cross_over_at_5(ctx, backend, M, expect):
+    """Up to four batch rows the GEMV kernels keep the shape, from five up the tensor-core
     kernel takes it (config 4's `o` layer); both agree with the oracle."""
     x, layer = synth.config4("o", M)
     y = _run(ctx, x, layer)

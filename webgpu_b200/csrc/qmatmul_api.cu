@@ -98,11 +98,12 @@ LuxBackendError dispatch(Context* ctx, const Checked& c) {
                 LuxBackendError e = launch_qgemv_i4_units(ctx, a);
                 if (e != LUX_BACKEND_ERROR_NOT_SUPPORTED || g_tune.gemv_i4_kernel == 3) return e;
             }
-            // From a handful of batch rows on, the tensor-core kernel with the weights in tensor
-            // memory streams the weights faster than the mma.sync kernels below, whose unpacking
-            // grows with the batch: config 4 gate_up / o at batch 12: 41 / 12.7 us against 47 / 13.4 us, at batch
-            // 32: 41 / 12.8 us against 138 / 37 us; below 12 the streaming kernels win.
-            const int min_m = g_tune.gemm_min_m > 0 ? g_tune.gemm_min_m : 12;
+            // From five batch rows on, the tensor-core kernel with the weights in tensor memory streams
+            // the weights faster than the mma.sync kernels below, whose unpacking grows with the batch
+            // (config 4 gate_up / down at batch 5: 27.4 / 19.8 us against 31.4 / 25.7 us, at batch 11:
+            // 27.5 / 19.9 us against 46.3 / 69.6 us; its time does not depend on the batch up to 64).  Three
+            // and four rows stay with the fixed-point kernel above (gate_up 19.1 us) or the ring kernel.
+            const int min_m = g_tune.gemm_min_m > 0 ? g_tune.gemm_min_m : 5;
             if (a.M >= min_m && g_tune.gemv_i4_kernel == 0 && g_tune.gemm_tc_kernel != 1 && !a.push) {
                 LuxBackendError e = launch_qgemm_i4_tc_wa(ctx, a);
                 if (e != LUX_BACKEND_ERROR_NOT_SUPPORTED) return e;
