@@ -124,6 +124,7 @@ struct Tunables {
     int attn_splits = 0;         // attention: slices of the keys per (sequence, KV head, row block); 0 = choose
     int gemm_wa_narrow = 0;      // weights-in-TMEM GEMM, batch <= 64: 0 narrow tile (two CTAs per SM) when the launch has more CTAs
                                  // than SMs, 1 always, 2 never
+    int gemm_wa_prefetch = 0;    // weights-in-TMEM GEMM: L2 prefetch distance of the weight rows in 128-K units (0 = 2, -1 = off)
     int gemm_tc_ma = 0;          // GEMM: batch tiles (128 rows) per CTA, 1 or 2 (0 = choose)
 };
 extern Tunables g_tune;

@@ -76,6 +76,7 @@ struct WaParams {
     int groups;               // converter groups of four warps, <= stages
     int up_row_offset;        // SwiGLU: weight row of `up` = weight row of `gate` + this (= number of outputs)
     int ncols;                // batch rows per tile = UMMA N: 256, or the batch rounded up to 16 when it is smaller
+    int prefetch;             // units ahead of the register fetch at which a thread asks L2 for its row's line (0 = off)
 };
 
 // Group constants of one weight row: zero-point pair and the scale (bf16: split in two).
@@ -167,6 +168,9 @@ lux_qgemm_i4_tc_wa(const __grid_constant__ CUtensorMap map_x, const WaParams p) 
         const uint4* src = reinterpret_cast<const uint4*>(wp + (size_t)u * (WA_UNIT_K / 2));
 #pragma unroll
         for (int i = 0; i < 4; i++) nq[i] = __ldg(src + i);
+        // the line two fetches ahead is asked for now, so that the register fetch finds it in L2
+        if (p.prefetch && u + p.prefetch < U)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(wp + (size_t)(u + p.prefetch) * (WA_UNIT_K / 2)));
         nsh = __ldg(sp + u);
         if (zrow) nzb = (uint32_t)__ldg(zrow + ((g_base + u) >> 1));
     };
@@ -542,6 +546,7 @@ LuxBackendError launch_qgemm_i4_tc_wa(Context* ctx, const QArgs& a) {
     p.stages = stages;
     p.groups = groups;
     p.ncols = ncols;
+    p.prefetch = g_tune.gemm_wa_prefetch < 0 ? 0 : (g_tune.gemm_wa_prefetch > 0 ? g_tune.gemm_wa_prefetch : 2);
 
     dim3 grid(nout / out_w, (a.M + bn - 1) / bn, ks);
     const int threads = (2 + 4 * groups) * 32;                  // groups >= 2: the epilogue needs warps 2..9

@@ -379,7 +379,7 @@ LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_tune_set(const char* key, int val
         {"gemv_i4_kernel", &g_tune.gemv_i4_kernel}, {"gemv_stream_cg", &g_tune.gemv_stream_cg},
         {"gemv_stream_stages", &g_tune.gemv_stream_stages}, {"gemv_stream_warps", &g_tune.gemv_stream_warps},
         {"gemv_units_ks", &g_tune.gemv_units_ks}, {"gemv_units_stages", &g_tune.gemv_units_stages}, {"gemv_units_cg", &g_tune.gemv_units_cg}, {"gemv_units_pre", &g_tune.gemv_units_pre}, {"gemv_units_fx", &g_tune.gemv_units_fx}, {"gemv_units_warps", &g_tune.gemv_units_warps}, {"gemv_units_planes", &g_tune.gemv_units_planes}, {"host_pageable", &g_tune.host_pageable},
-        {"gemm_tc_stages", &g_tune.gemm_tc_stages}, {"gemm_tc_splitk", &g_tune.gemm_tc_splitk}, {"gemm_tc_ma", &g_tune.gemm_tc_ma}, {"gemm_wa_narrow", &g_tune.gemm_wa_narrow}, {"attn_splits", &g_tune.attn_splits}, {"int_matmul_kernel", &g_tune.int_matmul_kernel}, {"gemm_tc_groups", &g_tune.gemm_tc_groups}, {"gemm_tc_kernel", &g_tune.gemm_tc_kernel}, {"gemm_min_m", &g_tune.gemm_min_m}, {"pdl", &g_tune.pdl},
+        {"gemm_tc_stages", &g_tune.gemm_tc_stages}, {"gemm_tc_splitk", &g_tune.gemm_tc_splitk}, {"gemm_tc_ma", &g_tune.gemm_tc_ma}, {"gemm_wa_narrow", &g_tune.gemm_wa_narrow}, {"gemm_wa_prefetch", &g_tune.gemm_wa_prefetch}, {"attn_splits", &g_tune.attn_splits}, {"int_matmul_kernel", &g_tune.int_matmul_kernel}, {"gemm_tc_groups", &g_tune.gemm_tc_groups}, {"gemm_tc_kernel", &g_tune.gemm_tc_kernel}, {"gemm_min_m", &g_tune.gemm_min_m}, {"pdl", &g_tune.pdl},
     };
     for (auto& t : table)
         if (std::strcmp(t.k, key) == 0) { *t.v = value; return LUX_BACKEND_OK; }
