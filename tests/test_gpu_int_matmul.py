@@ -36,14 +36,17 @@ def test_matmul_int8_bit_exact(ctx, backend, M, N, K):
     assert np.array_equal(got, want.astype(np.int32))
     if M * N >= 128 * 256 and K >= 256 and K % 16 == 0:
         assert backend.last_kernel_name() == "lux_matmul_int8_tcgen05"
-        # the mma.sync kernel gives the same bits
-        backend.tune("int_matmul_kernel", 1)
-        try:
-            ctx.matmul_int8(ab, bb, cb, M, N, K)
-            assert backend.last_kernel_name() == "lux_matmul_int8"
-        finally:
-            backend.tune("int_matmul_kernel", 0)
-        assert np.array_equal(cb.to_host(np.int32, (M, N)), got)
+        # the mma.sync kernel gives the same bits, and so does the tcgen05 kernel fed through a
+        # transposed copy of B (what it does by itself when N is not a multiple of 16) instead of
+        # reading B as it lies
+        for choice, name in ((1, "lux_matmul_int8"), (2, "lux_matmul_int8_tcgen05")):
+            backend.tune("int_matmul_kernel", choice)
+            try:
+                ctx.matmul_int8(ab, bb, cb, M, N, K)
+                assert backend.last_kernel_name() == name
+            finally:
+                backend.tune("int_matmul_kernel", 0)
+            assert np.array_equal(cb.to_host(np.int32, (M, N)), got)
     if M * N * K <= 1 << 22:
         assert np.array_equal(got, orc.matmul_int(a, b, M, N, K, 8))
 

@@ -120,7 +120,7 @@ struct Tunables {
     int pdl = 0;                 // programmatic dependent launch of the persistent kernels: 0/1 on, 2 off
     int gemm_min_m = 0;          // smallest batch the weights-in-TMEM GEMM takes from the streaming kernels (0 = built-in)
     int gemm_tc_kernel = 0;      // 0 auto, 1 lux_qgemm_i4_tc, 2 lux_qgemm_i4_tc_wa wherever it applies
-    int int_matmul_kernel = 0;   // lux_cuda_matmul_int8 / _int4_int8: 0 tcgen05 for large shapes, 1 mma.sync kernels only
+    int int_matmul_kernel = 0;   // lux_cuda_matmul_int8 / _int4_int8: 0 tcgen05 for large shapes, 1 mma.sync kernels only, 2 tcgen05 always through B^T
     int attn_splits = 0;         // attention: slices of the keys per (sequence, KV head, row block); 0 = choose
     int gemm_wa_narrow = 0;      // weights-in-TMEM GEMM, batch <= 64: 0 narrow tile (two CTAs per SM) when the launch has more CTAs
                                  // than SMs, 1 always, 2 never

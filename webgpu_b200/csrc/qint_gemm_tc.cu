@@ -8,15 +8,18 @@
 // (int32 accumulation, wrapping like the shader's i32), so the result is bit-identical either way.
 //
 // C[M, N] = A[M, K] . B[K, N]:
-//   * both operands must reach the tensor core K-major.  A is (row-major, K contiguous).  B is
-//     row-major [K, N], N contiguous, so a first kernel writes B^T [N, K] into the context's scratch
-//     (64 x 64 byte tiles through shared memory); for int4 x int8 another sign-extends A's two's
-//     complement nibbles (quantized.wgsl:150-158) to bytes.  Both passes move K*N (+ M*K) bytes,
-//     a few percent of the matmul's time;
+//   * A is row-major with K contiguous: a K-major operand.  B is row-major [K, N] with N contiguous:
+//     an MN-major operand, which kind::i8 accepts (bit 16 of the instruction descriptor), so B is read
+//     as it lies -- two TMA boxes of 128 columns x 128 rows of k per stage, each box one column of
+//     128-byte swizzle atoms.  When N is not a multiple of 16 bytes a row of B cannot be a tensor
+//     map's row, and a first kernel writes B^T [N, K] into the context's scratch (64 x 64 byte tiles
+//     through shared memory), which is then read K-major (measured, 4096^3: 83.5 us through B^T,
+//     73.0 us without; 256 x 28672 x 4096: 103.8 -> 48.5 us).  For int4 x int8 another kernel
+//     sign-extends A's two's complement nibbles (quantized.wgsl:150-158) to bytes;
 //   * a CTA owns a 256 x 256 tile of C (128 x 256 when M <= 128): two int32 accumulators of 256
 //     columns each in tensor memory, fed by the same B tile;
-//   * warp 0 (one thread): TMA producer, one 256 x 128-byte box of A and one 256 x 128-byte box of
-//     B^T per stage (128 k; 128-byte swizzle), three stages (four with one accumulator);
+//   * warp 0 (one thread): TMA producer, one 256 x 128-byte box of A and 32 KB of B per stage
+//     (128 k; 128-byte swizzle), three stages (four with one accumulator);
 //   * warp 1 (one thread): per stage one wait, four tcgen05.mma.kind::i8 (128 x 256 x 32) per
 //     accumulator and one tcgen05.commit that frees the stage;
 //   * warps 2-5: epilogue, tcgen05.ld 32 columns at a time, 128-byte stores per thread.
@@ -64,7 +67,19 @@ struct I8Params {
     int* c;
     uint32_t* status;
     int M, N, K;
+    int b_mn;      // B is read as it lies, [K, N] with N contiguous (an MN-major operand); 0: map_b describes B^T
 };
+
+// Shared-memory descriptor of the B stage as an MN-major operand under the 128-byte swizzle.  In
+// 16-byte units the canonical layout is ((8, n), (8, k)) : ((1, LBO), (8, SBO)): 128 contiguous
+// bytes of N, eight rows of K 128 bytes apart (one swizzle atom, which is what a TMA box of
+// 128 bytes x rows writes), the next eight rows of K SBO = 1024 bytes on, the next 128 columns of N
+// LBO = one box (128 rows x 128 bytes) on.
+__device__ __forceinline__ uint64_t make_mnmajor_sw128_desc(uint32_t smem_addr) {
+    const uint32_t lo = ((smem_addr & 0x3FFFFu) >> 4) | ((uint32_t)((I8_KB * 128) >> 4) << 16);
+    const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+    return ((uint64_t)hi << 32) | lo;
+}
 
 template <int MA>
 __global__ void __launch_bounds__(I8_THREADS, 1)
@@ -113,26 +128,34 @@ lux_matmul_int8_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_
                 if (kb >= I8_STAGES && !mbar_wait_relaxed(empty(s), (uint32_t)((kb / I8_STAGES) - 1) & 1u, abort_flag)) break;
                 mbar_expect_tx(full(s), (uint32_t)(A_STAGE + I8_B_BYTES));        // boxes past an edge are zero-filled and still counted
                 tma_load_2d(smem_u32(a_ring + (size_t)s * A_STAGE), &map_a, kb * I8_KB, m0, full(s));
-                tma_load_2d(smem_u32(b_ring + (size_t)s * I8_B_BYTES), &map_b, kb * I8_KB, n0, full(s));
+                if (p.b_mn) {
+                    // two boxes of 128 columns of N x 128 rows of K, as they lie in B
+                    tma_load_2d(smem_u32(b_ring + (size_t)s * I8_B_BYTES), &map_b, n0, kb * I8_KB, full(s));
+                    tma_load_2d(smem_u32(b_ring + (size_t)s * I8_B_BYTES + I8_B_BYTES / 2), &map_b, n0 + 128, kb * I8_KB, full(s));
+                } else {
+                    tma_load_2d(smem_u32(b_ring + (size_t)s * I8_B_BYTES), &map_b, kb * I8_KB, n0, full(s));
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            constexpr uint32_t idesc = i8_idesc();
+            const uint32_t idesc = i8_idesc() | (p.b_mn ? (1u << 16) : 0u);       // bit 16: B is MN-major
+            const uint64_t b_step = p.b_mn ? (uint64_t)((32 * 128) >> 4) : 2u;     // 32 k: 32 rows of the box, or 32 bytes of the swizzle row
             bool ok = true;
             for (int kb = 0; kb < KB; kb++) {
                 const int s = kb % I8_STAGES;
                 ok = mbar_wait(full(s), (uint32_t)(kb / I8_STAGES) & 1u, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
-                const uint64_t b_desc = make_kmajor_sw128_desc(smem_u32(b_ring + (size_t)s * I8_B_BYTES));
+                const uint32_t b_addr = smem_u32(b_ring + (size_t)s * I8_B_BYTES);
+                const uint64_t b_desc = p.b_mn ? make_mnmajor_sw128_desc(b_addr) : make_kmajor_sw128_desc(b_addr);
 #pragma unroll
                 for (int a = 0; a < MA; a++) {
                     // accumulator a: rows a * 128 .. of the A box, TMEM columns a * 256 ..
                     const uint64_t a_desc = make_kmajor_sw128_desc(smem_u32(a_ring + (size_t)s * A_STAGE + (size_t)a * I8_A_BYTES));
 #pragma unroll
                     for (int k = 0; k < I8_KB / 32; k++)  // 32 k = 32 bytes inside the 128-byte swizzle row: +2 in the address field
-                        umma_i8(tmem_base + (uint32_t)(a * 256), a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
+                        umma_i8(tmem_base + (uint32_t)(a * 256), a_desc + (uint64_t)(2 * k), b_desc + b_step * (uint64_t)k, idesc, (kb | k) != 0 ? 1u : 0u);
                 }
                 umma_commit(empty(s));
             }
@@ -250,8 +273,10 @@ __global__ void __launch_bounds__(256) lux_unpack_s4_s8(const uint8_t* __restric
 LuxBackendError launch_matmul_int8_tcgen05(Context* ctx, const void* a, const void* b, int* c, int M, int N, int K, bool a_int4) {
     if (K % 16 || (size_t)M * N < (size_t)I8_BM * I8_BN || K < 256) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
     if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c)) & 15u) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
-    const size_t bt_bytes = ((size_t)N * K + 255) & ~(size_t)255, a8_bytes = a_int4 ? (((size_t)M * K + 255) & ~(size_t)255) : 0;
-    {
+    // B as it lies when its rows can be a tensor map's (N a multiple of 16 bytes); else through B^T
+    const bool b_mn = N % 16 == 0 && g_tune.int_matmul_kernel != 2;
+    const size_t bt_bytes = b_mn ? 0 : (((size_t)N * K + 255) & ~(size_t)255), a8_bytes = a_int4 ? (((size_t)M * K + 255) & ~(size_t)255) : 0;
+    if (bt_bytes + a8_bytes) {
         // scratch for B^T (and the unpacked A): grown on demand, kept with the context
         std::lock_guard<std::mutex> lock(ctx->mu);
         if (ctx->d_int_bytes < bt_bytes + a8_bytes) {
@@ -268,8 +293,10 @@ LuxBackendError launch_matmul_int8_tcgen05(Context* ctx, const void* a, const vo
     }
     uint8_t* bt = (uint8_t*)ctx->d_int;
     uint8_t* a8 = bt + bt_bytes;
-    lux_transpose_i8<<<dim3((N + 63) / 64, (K + 63) / 64), 256, 0, ctx->stream>>>((const uint8_t*)b, bt, K, N);
-    count_launch();
+    if (!b_mn) {
+        lux_transpose_i8<<<dim3((N + 63) / 64, (K + 63) / 64), 256, 0, ctx->stream>>>((const uint8_t*)b, bt, K, N);
+        count_launch();
+    }
     if (a_int4) {
         const size_t bytes = (size_t)M * K / 2;
         lux_unpack_s4_s8<<<(unsigned)std::min<size_t>((bytes + 255) / 256, (size_t)ctx->sm_count * 16), 256, 0, ctx->stream>>>((const uint8_t*)a, a8, bytes);
@@ -281,7 +308,13 @@ LuxBackendError launch_matmul_int8_tcgen05(Context* ctx, const void* a, const vo
     const int ma = M > I8_BM ? 2 : 1;
     const uint32_t abox[2] = {(uint32_t)I8_KB, (uint32_t)(ma * I8_BM)}, bbox[2] = {(uint32_t)I8_KB, (uint32_t)I8_BN};
     if (!encode_tensor_map_u8(&ma_map, 2, a_int4 ? (const void*)a8 : a, adims, strides, abox, true)) return LUX_BACKEND_ERROR_INTERNAL;
-    if (!encode_tensor_map_u8(&mb, 2, bt, bdims, strides, bbox, true)) return LUX_BACKEND_ERROR_INTERNAL;
+    if (b_mn) {
+        const uint64_t dims_mn[2] = {(uint64_t)N, (uint64_t)K}, strides_mn[1] = {(uint64_t)N};
+        const uint32_t box_mn[2] = {128u, (uint32_t)I8_KB};
+        if (!encode_tensor_map_u8(&mb, 2, b, dims_mn, strides_mn, box_mn, true)) return LUX_BACKEND_ERROR_INTERNAL;
+    } else if (!encode_tensor_map_u8(&mb, 2, bt, bdims, strides, bbox, true)) {
+        return LUX_BACKEND_ERROR_INTERNAL;
+    }
     static std::atomic<bool> configured[64];
     int dev = ctx->device & 63;
     if (!configured[dev].load(std::memory_order_relaxed)) {
@@ -290,7 +323,7 @@ LuxBackendError launch_matmul_int8_tcgen05(Context* ctx, const void* a, const vo
             return map_cuda(cudaGetLastError(), "lux_matmul_int8_tcgen05");
         configured[dev].store(true, std::memory_order_relaxed);
     }
-    I8Params p{c, ctx->d_status, M, N, K};
+    I8Params p{c, ctx->d_status, M, N, K, b_mn ? 1 : 0};
     const dim3 grid((N + I8_BN - 1) / I8_BN, (M + ma * I8_BM - 1) / (ma * I8_BM));
     if (ma == 2) lux_matmul_int8_tcgen05<2><<<grid, I8_THREADS, i8_smem(2), ctx->stream>>>(ma_map, mb, p);
     else lux_matmul_int8_tcgen05<1><<<grid, I8_THREADS, i8_smem(1), ctx->stream>>>(ma_map, mb, p);
