@@ -87,7 +87,8 @@ typedef enum LuxQMatmulRoute {
     LUX_QROUTE_NONE        = 0,
     LUX_QROUTE_GEMV_I8     = 1,   /* int8 g32, f32 in/out, streaming GEMV              */
     LUX_QROUTE_SKINNY_I4   = 2,   /* int4 g128, M <= 32, streaming GEMV / skinny GEMM  */
-    LUX_QROUTE_GEMM_I4_TC  = 3    /* int4 g128, M >= 33, tcgen05 / TMEM GEMM           */
+    LUX_QROUTE_GEMM_I4_TC  = 3    /* int4 g128, M >= 33 (bf16: any M), tcgen05 / TMEM GEMM; bf16 at
+                                     M <= 4 is served by the fixed-point GEMV where its plan fits */
 } LuxQMatmulRoute;
 
 /* y = x . dequant(W)^T.  Replaces the role of matmul_nax_grouped

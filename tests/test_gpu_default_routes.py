@@ -137,3 +137,25 @@ def test_matmul_behind_an_unsynchronised_unpack_sees_its_output(ctx, backend):
     assert np.abs(ref).max() > 0
     for _ in range(3):
         assert np.array_equal(run(True).view(np.uint32), ref.view(np.uint32))
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 4])
+@pytest.mark.parametrize("name", ["qkv", "gate_up"])
+def test_bf16_decode_takes_the_fixed_point_gemv(ctx, backend, name, M):
+    """bf16 activations at decode batches run on the same fixed-point GEMV as f16 ones (exact
+    weights, f32 sums, one rounding to bf16), not on the tensor-core kernels that round the weights."""
+    x16, layer = synth.config4(name, M)
+    x = synth.f32_to_bf16_bits(x16.astype(np.float32))
+    L, xb = ctx.upload_layer(layer), ctx.upload(x)
+    yb = ctx.alloc(M * layer.N * 2)
+    ctx.qmatmul(xb, L, yb, M, B.BF16)
+    assert backend.last_kernel_name() == "lux_qgemv_i4_g128_units_fx"
+    y = synth.bf16_bits_to_f32(yb.to_host(np.uint16, (M, layer.N)))
+    ref = synth.bf16_bits_to_f32(orc.qmatmul(x, *layer.triple, bits=4, group=128))
+    assert orc.rel_l2(y, ref) < 2.5e-3          # the output's own rounding to 8 bits; the weights are exact
+    assert ctx.last_device_status() == 0
+    # the f16 run on the same activation values (a bf16 value is an f16 value unless it is tiny) gives the
+    # same sums; the two differ by their output roundings only
+    yh = ctx.alloc(M * layer.N * 2)
+    ctx.qmatmul(ctx.upload(synth.bf16_bits_to_f32(x).astype(np.float16)), L, yh, M, B.F16)
+    assert orc.rel_l2(y, yh.to_host(np.float16, (M, layer.N)).astype(np.float32)) < 2.5e-3

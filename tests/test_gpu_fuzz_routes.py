@@ -110,10 +110,11 @@ def test_random_integer_matmul_shapes_bit_exact(ctx, backend, seed):
 def test_random_ffn_shapes(ctx, backend, seed):
     """lux_cuda_qmlp and lux_cuda_qmlp_noalloc over random (batch, K, I, H): the two entry points
     agree bit for bit, and the result meets the oracle's FFN with the SwiGLU applied to the f32 sums.
-    f16: 5e-3 against the oracle with f32 weights.  bf16: the tensor-core kernels multiply weights
-    rounded to bf16, so the bar of one layer is not the bar of two in a row; the check is 1e-3
-    against the oracle doing exactly that (weights rounded, f32 accumulate) and 8e-3 against f32
-    weights (measured 3e-3 .. 6e-3: two weight roundings and two output roundings of 8 bits)."""
+    f16: 5e-3 against the oracle with f32 weights.  bf16 from five rows up: the tensor-core kernels
+    multiply weights rounded to bf16, so the bar of one layer is not the bar of two in a row; the
+    check is 1e-3 against the oracle doing exactly that (weights rounded, f32 accumulate) and 8e-3
+    against f32 weights (measured 3e-3 .. 6e-3: two weight roundings and two output roundings of
+    8 bits).  bf16 up to four rows runs on the fixed-point GEMV with exact weights."""
     rng = np.random.default_rng(seed)
     for case in range(60):
         M = int(rng.choice([1, 2, 3, 4, 5, 8, 9, 16, 17, 32, 33, 64, 65, 128, 200, 256, 300]))
@@ -143,10 +144,11 @@ def test_random_ffn_shapes(ctx, backend, seed):
         if dtype == "f16":
             assert orc.rel_l2(y[rows], exact) < 5e-3, what
         else:
-            rounded = orc.mlp(xr, gate_up.triple, down.triple, fused=True, w_round=orc.BF16)
             got = synth.bf16_bits_to_f32(y[rows])
-            assert orc.rel_l2(got, synth.bf16_bits_to_f32(rounded)) < 1e-3, what
             assert orc.rel_l2(got, synth.bf16_bits_to_f32(exact)) < 8e-3, what
+            if M >= 5:                       # up to four rows the fixed-point GEMV keeps the weights exact
+                rounded = orc.mlp(xr, gate_up.triple, down.triple, fused=True, w_round=orc.BF16)
+                assert orc.rel_l2(got, synth.bf16_bits_to_f32(rounded)) < 1e-3, what
         for buf in (xb, hb, yb, yb2, G.w, G.scales, G.zeros, D.w, D.scales, D.zeros):
             if buf is not None:
                 buf.free()

@@ -129,6 +129,7 @@ struct UnitsParams {
     uint32_t* status;       // device status word for a wait that gave up (may be null)
     uint32_t inv_upt, inv_U; // ceil(2^32 / (units per tile)), ceil(2^32 / U): division-free unit table
     int planes;             // fixed-point variant: signed byte planes of the activations, 4 or 3
+    int bf16;               // fixed-point variant: x and y are bf16 instead of f16
     PushTarget push;        // world > 1: the outputs go to the peers' all-reduce windows instead of y
 };
 
@@ -609,24 +610,32 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
         const int m = MM == 1 ? 0 : c / (p.G * 16), cg16 = c - m * p.G * 16;
         const int grp = cg16 >> 4, l16 = cg16 & 15;
         float v[8];
-        {
+        if (p.bf16) {
+            // a bf16 is the upper half of the f32 of the same value
+            v[0] = __uint_as_float(s4.x << 16); v[1] = __uint_as_float(s4.x & 0xffff0000u);
+            v[2] = __uint_as_float(s4.y << 16); v[3] = __uint_as_float(s4.y & 0xffff0000u);
+            v[4] = __uint_as_float(s4.z << 16); v[5] = __uint_as_float(s4.z & 0xffff0000u);
+            v[6] = __uint_as_float(s4.w << 16); v[7] = __uint_as_float(s4.w & 0xffff0000u);
+        } else {
             const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&s4.x));
             const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&s4.y));
             const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&s4.z));
             const float2 f3 = __half22float2(*reinterpret_cast<const __half2*>(&s4.w));
             v[0] = f0.x; v[1] = f0.y; v[2] = f1.x; v[3] = f1.y; v[4] = f2.x; v[5] = f2.y; v[6] = f3.x; v[7] = f3.y;
         }
-        // largest |x| of the group as an f16 bit pattern (monotonic for non-negative values;
-        // inf and NaN, exponent field all ones, compare above every finite value)
+        // largest |x| of the group as a 16-bit pattern (monotonic for non-negative values in f16 and
+        // in bf16 alike; inf and NaN, exponent field all ones, compare above every finite value)
         uint32_t mb = __vmaxu2(__vmaxu2(s4.x & 0x7fff7fffu, s4.y & 0x7fff7fffu),
                                __vmaxu2(s4.z & 0x7fff7fffu, s4.w & 0x7fff7fffu));
         mb = max(mb & 0xffffu, mb >> 16);
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) mb = max(mb, __shfl_xor_sync(0xffffffffu, mb, o));
-        const bool bad = mb >= 0x7C00u;
-        const float amax = __half2float(__ushort_as_half((unsigned short)mb));
+        const bool bad = mb >= (p.bf16 ? 0x7F80u : 0x7C00u);
+        const float amax = p.bf16 ? __uint_as_float(mb << 16) : __half2float(__ushort_as_half((unsigned short)mb));
         // amax = f * 2^E with f in [0.5, 1): biased exponent eb = E + 126.  x * 2^(30-E) is exact.
-        const unsigned eb = __float_as_uint(amax) >> 23;
+        // (bf16 reaches exponents f16 does not: below 2^-86 the block exponent stops following the
+        // group, so that both powers of two below stay normal; such a group keeps fewer bits.)
+        const unsigned eb = max(__float_as_uint(amax) >> 23, 40u);
         // four planes: 30 bits below the block exponent; three (rows too long for four): 22
         const unsigned sh = p.planes == 4 ? 30u : 22u;
         const float up = (mb != 0u && !bad) ? __uint_as_float((253u + sh - eb) << 23) : 0.0f;   // 2^(sh-E)
@@ -961,7 +970,9 @@ lux_qgemv_i4_g128_units_fx(const __grid_constant__ CUtensorMap map_w, const Unit
             sum[a] = acc1;
         }
         const float out = SWIGLU ? silu_f32(sum[0]) * sum[NACC - 1] : sum[0];
-        p.y[(size_t)m * p.Nout + (tile_lo + tl) * 16 + r] = __float2half_rn(out);
+        const size_t at = (size_t)m * p.Nout + (tile_lo + tl) * 16 + r;
+        if (p.bf16) reinterpret_cast<__nv_bfloat16*>(p.y)[at] = __float2bfloat16_rn(out);
+        else p.y[at] = __float2half_rn(out);
     }
 }
 
@@ -1033,6 +1044,8 @@ LuxBackendError launch_qgemv_i4_units(Context* ctx, const QArgs& a) {
     // batch 1..4 use the block-fixed-point variant (three rows run as four) unless the tunable says
     // otherwise; a batch of 3 or 4 whose activations do not fit beside the FIFOs falls back to the f16 form
     bool fx = a.M <= 4 && g_tune.gemv_units_fx != 2;
+    const bool bf16 = a.x_dtype == LUX_QDTYPE_BF16;        // only the fixed-point variant reads and writes bf16
+    if (bf16 && (!fx || a.push)) return LUX_BACKEND_ERROR_NOT_SUPPORTED;
     const int mm = a.M == 3 ? 4 : a.M;                    // batch rows the fixed-point kernel is instantiated for
 
     // Chunk size: 4 groups when the group count allows, else 2.
@@ -1129,7 +1142,7 @@ LuxBackendError launch_qgemv_i4_units(Context* ctx, const QArgs& a) {
     if (fx && g_tune.gemv_units_warps == 8) planned = plan_planes(8, (size_t)113 * 1024, 2);
     if (!planned && (!fx || g_tune.gemv_units_warps != 8)) planned = plan_planes(UW, (size_t)227 * 1024, fx ? (mm == 4 ? 2 : 1) : 2);
     if (!planned && fx && a.M > 2) {
-        if (g_tune.gemv_i4_kernel != 3) return LUX_BACKEND_ERROR_NOT_SUPPORTED;     // the caller has faster kernels for this shape
+        if (g_tune.gemv_i4_kernel != 3 || bf16) return LUX_BACKEND_ERROR_NOT_SUPPORTED;     // the caller has faster kernels for this shape
         fx = false;
         planned = plan_planes(UW, (size_t)227 * 1024, 2);
     }
@@ -1138,6 +1151,7 @@ LuxBackendError launch_qgemv_i4_units(Context* ctx, const QArgs& a) {
     const int grid = pl.grid;
     const size_t smem = pl.smem;
     p.status = ctx->d_status;
+    p.bf16 = bf16 ? 1 : 0;
     p.push = PushTarget{};
     if (a.push) {
         // only the fixed-point variant pushes, and only plain (non-SwiGLU) outputs with an even row count

@@ -117,6 +117,13 @@ LuxBackendError dispatch(Context* ctx, const Checked& c) {
             return launch_qskinny_i4(ctx, a);
         }
         case LUX_QROUTE_GEMM_I4_TC: {
+            // bf16 decode (up to four rows): the fixed-point GEMV takes bf16 activations as it takes
+            // f16 ones, streams the weights at the same rate and keeps the weights exact, where the
+            // tensor-core kernels below round them to bf16
+            if (c.a.x_dtype == LUX_QDTYPE_BF16 && c.a.M <= 4 && g_tune.gemv_i4_kernel == 0 && g_tune.gemm_tc_kernel == 0 && !c.a.push) {
+                LuxBackendError e = launch_qgemv_i4_units(ctx, c.a);
+                if (e != LUX_BACKEND_ERROR_NOT_SUPPORTED) return e;
+            }
             // The kernel that keeps the converted weights in tensor memory (one conversion per 256
             // batch rows, 128 x 256 MMAs; for smaller batches 128 x M) wherever the shape fits it:
             // measured faster than the B-operand kernel at every batch from 64 up (config 4 layers at
