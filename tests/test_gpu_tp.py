@@ -75,6 +75,25 @@ for M in (1, 8, 64):
         err = orc.rel_l2(outs[0].astype(np.float16), ref)
         assert err < 5e-3, (M, err)
         print("PUSH_OK", M, err)
+# ---- bf16 activations: up to four rows on the fixed-point GEMV, more on the tensor-core GEMM; the push
+# all-reduce sums bf16 partial outputs ------------------------------------------------------------
+for M in (1, 8):
+    x = synth.activations(M, K, "bf16", 51, f"tp2.xb{M}")
+    mlp = tp.TPMlp(ctx, gate_up, down, rank, world, M, "bf16", peer=peer)
+    mlp.x[:M].copy_(torch.from_numpy(x.view(np.int16)).cuda().view(torch.bfloat16))
+    y = mlp.forward(M).float().cpu().numpy().copy()
+    ctx.sync()
+    assert ctx.last_device_status() == 0
+    gathered = [None] * world
+    dist.all_gather_object(gathered, y.tobytes())
+    assert all(g == gathered[0] for g in gathered), "ranks disagree (bf16)"
+    if rank == 0:
+        from oracle import oracle as orc
+        shards = [tuple(l.triple for l in tp.shard_mlp(gate_up, down, r, world)) for r in range(world)]
+        ref = synth.bf16_bits_to_f32(orc.tp_mlp(x, shards, fused=True, w_round=orc.F32 if M <= 4 else orc.BF16))
+        err = orc.rel_l2(y, ref)
+        assert err < 5e-3, (M, err)
+        print("BF16_OK", M, err)
 peer.close()
 dist.barrier()
 dist.destroy_process_group()
@@ -99,3 +118,4 @@ def test_tp_two_gpus(tmp_path, backend):
     assert all(p.returncode == 0 for p in procs), "\n".join(outs)
     assert outs[0].count("TP_OK") == 3, outs[0]
     assert outs[0].count("PUSH_OK") == 3, outs[0]
+    assert outs[0].count("BF16_OK") == 2, outs[0]
