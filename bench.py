@@ -384,7 +384,7 @@ def bench_single(args, peaks):
 
 # ----------------------------------------------------------------------------------------
 # --workload sweep: configuration 4 (Llama-3-8B decode linears at batch 1, 4, 16, 64) and the
-# kernels either side of the linear layers.  Not the headline: the numbers DESIGN.md quotes.
+# kernels either side of the linear layers.  Not the headline: the supporting figures.
 # ----------------------------------------------------------------------------------------
 
 def bench_sweep(args, peaks):
@@ -633,9 +633,6 @@ def bench_tp(args, peaks):
             collective = "NCCL all-reduce of f16 partials (torch.distributed)"
     note = f"[bench] rank {rank}/{world}: batch {M}, collective = {collective}"
     print(note, file=sys.stderr, flush=True)
-    if os.path.isdir(os.path.join(ROOT, "gpurun_out")):
-        with open(os.path.join(ROOT, "gpurun_out", f"bench_tp_collective_rank{rank}.txt"), "w") as f:
-            f.write(note + "\n")
     mlps = [tp.TPMlp(ctx, g_sh, d_sh, rank, world, M, "f16", presharded=True, peer=peer) for _ in range(copies)]
     xt = torch.from_numpy(x).cuda()
     for m in mlps:
