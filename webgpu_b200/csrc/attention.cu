@@ -658,6 +658,7 @@ LuxBackendError attn_launch(Context* ctx, AttnParams& p, uint32_t max_keys, uint
     const uint32_t R = p.group * p.seq_q;
     // two query rows per lane: more would halve the shared-memory reads per row, but the registers
     // of four rows leave one CTA of nine warps per SM, too few to hide the latency of each step
+    // (measured: causal prefill of 2048 tokens, Llama-3-8B heads, 15.2 TFLOP/s against 20.4)
     const int rt = R >= 2 && vpl <= 4 ? 2 : 1;
     p.rgp = pow2ceil(std::min<uint32_t>((R + rt - 1) / rt, ATT_CW));
     const uint32_t rpb = rt * p.rgp;
