@@ -294,7 +294,7 @@ LUX_GPU_PLUGIN_EXPORT const char* lux_cuda_last_kernel_name(void);
  * (1 register-staged, 2 bulk-copy ring, 3 warp-autonomous units), gemv_i4_warps, gemv_i4_row_tiles, gemv_stream_warps, gemv_stream_cg, gemv_stream_stages,
  * gemv_units_ks, gemv_units_stages, gemv_units_cg, gemv_units_pre, gemv_units_fx, gemv_i8_warps, gemm_tc_bn,
  * gemm_tc_stages, gemm_tc_ma, gemm_tc_kernel (1 lux_qgemm_i4_tc, 2 lux_qgemm_i4_tc_wa wherever it applies), gemm_tc_splitk (1, 2, 4),
- * gemm_tc_groups, gemm_min_m (smallest batch handed to lux_qgemm_i4_tc_wa, default 5), pdl (2: no programmatic dependent launch), peer_wait_limit, tp_fused_push,
+ * gemm_tc_groups, gemm_min_m (smallest batch handed to lux_qgemm_i4_tc_wa, default 5), pdl (2: no programmatic dependent launch), peer_wait_limit, tp_fused_push, tp_reduce_early,
  * gemv_units_warps, gemv_units_planes, gemm_wa_narrow, gemm_wa_prefetch (-1 off), host_pageable, attn_splits, int_matmul_kernel (1 mma.sync kernels only, 2 tcgen05 through a transposed copy of B).  Unknown keys return INVALID_ARGUMENT.  Process-wide;
  * not part of the drop-in surface. */
 LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_tune_set(const char* key, int value);

@@ -67,6 +67,7 @@ struct PushParams {
     unsigned long long count;                 // 16-bit elements
     unsigned long long wait_ns;               // deadline of the whole call
     int rank, world;
+    int early;                                // PUSH = false only: do not wait for the producer kernel to end before polling
 };
 
 // a slot holds max_bytes of payload as 8-byte words {4 bytes of payload, 4 bytes of epoch}
@@ -118,7 +119,9 @@ __global__ void __launch_bounds__(AR_THREADS) lux_peer_allreduce_push(const Push
     const int tid = threadIdx.x;
     if (tid == 0) s_failed = 0;
     pdl_launch_dependents();
-    pdl_wait();                                                   // the producer of buf has finished
+    // With PUSH the producer of buf must have finished.  Without, every word this kernel reads carries
+    // its epoch and buf is only written: it may start polling while the producer still runs.
+    if (PUSH || !p.early) pdl_wait();
     const uint32_t epoch = peer_ctl_load(p.ctl + PEER_CTL_EPOCH) + 1u;   // the same value in every CTA
     if (peer_ctl_load(p.ctl + PEER_CTL_FAILED)) {
         // an earlier call gave up: the ranks' epochs may differ, nothing can be trusted any more
@@ -166,6 +169,7 @@ __global__ void __launch_bounds__(AR_THREADS) lux_peer_allreduce_push(const Push
                 if (r < p.world) all = all && lo[r].y == epoch && lo[r].w == epoch && hi[r].y == epoch && hi[r].w == epoch;
             if (all) break;
             if ((it & 15u) == 0u && (*(volatile int*)&s_failed || peer_timer_ns() - t0 > p.wait_ns)) { failed = true; break; }
+            if (!PUSH && p.early) __nanosleep(200);          // beside a producer that still computes
         }
         if (failed) break;
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -237,6 +241,7 @@ LuxBackendError peer_allreduce_launch(Context* ctx, LuxPeerComm* comm, void* buf
     p.rank = c->rank;
     p.world = c->world;
     p.wait_ns = peer_wait_ns();
+    p.early = !push && g_tune.tp_reduce_early == 1 ? 1 : 0;
     // one CTA per 4 KB of the tensor, at most one per SM: 16 KB (batch 1) takes 4 CTAs, 4 MB all SMs
     const size_t pieces = count / 8;
     const unsigned grid = (unsigned)std::min<size_t>((size_t)ctx->sm_count, (pieces + AR_THREADS - 1) / AR_THREADS);

@@ -97,6 +97,7 @@ struct Tunables {
     int gemv_i4_warps = 0;       // warps per CTA of the int4 skinny kernel
     int gemv_i4_row_tiles = 0;   // 16-row tiles per CTA
     int gemv_i8_warps = 0;
+    int tp_reduce_early = 0;     // reduce-only all-reduce kernel: 1 = poll without waiting for the producer kernel to end
     int tp_fused_push = 0;       // lux_cuda_qmlp_tp at batch <= 2: 0 the down kernel pushes and a reduce-only kernel follows;
                                  // 1 the down kernel pushes, waits and sums itself; 2 separate all-reduce kernel
     int peer_wait_limit = 0;     // push all-reduce: microseconds before a call's wait for its peers gives up (default 10^6)

@@ -382,7 +382,7 @@ LUX_GPU_PLUGIN_EXPORT LuxBackendError lux_cuda_tune_set(const char* key, int val
     if (!key) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
     struct { const char* k; int* v; } table[] = {
         {"gemv_i4_warps", &g_tune.gemv_i4_warps},   {"gemv_i4_row_tiles", &g_tune.gemv_i4_row_tiles},
-        {"gemv_i8_warps", &g_tune.gemv_i8_warps},   {"gemv_i8_kernel", &g_tune.gemv_i8_kernel}, {"peer_wait_limit", &g_tune.peer_wait_limit}, {"tp_fused_push", &g_tune.tp_fused_push},   {"gemm_tc_bn", &g_tune.gemm_tc_bn},
+        {"gemv_i8_warps", &g_tune.gemv_i8_warps},   {"gemv_i8_kernel", &g_tune.gemv_i8_kernel}, {"peer_wait_limit", &g_tune.peer_wait_limit}, {"tp_fused_push", &g_tune.tp_fused_push}, {"tp_reduce_early", &g_tune.tp_reduce_early},   {"gemm_tc_bn", &g_tune.gemm_tc_bn},
         {"gemv_i4_kernel", &g_tune.gemv_i4_kernel}, {"gemv_stream_cg", &g_tune.gemv_stream_cg},
         {"gemv_stream_stages", &g_tune.gemv_stream_stages}, {"gemv_stream_warps", &g_tune.gemv_stream_warps},
         {"gemv_units_ks", &g_tune.gemv_units_ks}, {"gemv_units_stages", &g_tune.gemv_units_stages}, {"gemv_units_cg", &g_tune.gemv_units_cg}, {"gemv_units_pre", &g_tune.gemv_units_pre}, {"gemv_units_fx", &g_tune.gemv_units_fx}, {"gemv_units_warps", &g_tune.gemv_units_warps}, {"gemv_units_planes", &g_tune.gemv_units_planes}, {"host_pageable", &g_tune.host_pageable},
